@@ -1,0 +1,706 @@
+// Log-space HMM forward algorithm over a k-mer x 16-duration-layer state space
+// for sm_100a. Two implementations behind one entry point:
+//
+//  * resident kernel  — a persistent thread-block cluster owns one sequence at
+//    a time; every thread keeps the 16 duration layers of its k-mers in
+//    registers for the whole sequence, only layer 0 (K floats) is exchanged per
+//    time step through distributed shared memory, with one split
+//    barrier.cluster arrive/wait per step hidden behind layers 1..15.
+//  * streaming kernel — alpha ping-pongs through caller scratch in global
+//    memory, one launch per time step, the reference's literal five-term
+//    log-sum-exp. Covers state spaces the resident kernel cannot hold and is
+//    the structural twin of what the reference's compiler emits.
+//
+// The recurrence (benchmarks/forward.py:103-158), with state = d*K + s:
+//   alpha'[d,s] = LSE( trans1[p_j, s%4] + trans2[d] + alpha[0,p_j]  (j=0..3),
+//                      c[d] + alpha[min(d+1,15), s] ) + output_prob[o_t, s]
+//   p_j = j*K/4 + s/4,  c[15] = gamma, c[14] = synthetic_248, else 0.
+// The four k-mer terms do not depend on d apart from the additive trans2[d],
+// so the resident kernel evaluates q[s] = LSE_j(trans1[p_j,s%4] + alpha[0,p_j])
+// once per k-mer and alpha'[d,s] = LSE2(trans2[d] + q[s], c[d] + alpha[d+1,s]).
+#include <cooperative_groups.h>
+
+#include <algorithm>
+#include <atomic>
+
+#include "../../include/parpy_b200.h"
+#include "common.cuh"
+
+namespace {
+
+constexpr int kLayers = 16;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr int kModelSlots = 16;
+constexpr int kSortLimit = 4096;  // sequences sorted by length up to this batch size
+
+// Per-call model scalars, read through the constant bank so that they cost no
+// registers: trans2[0..15], gamma, synthetic_248.
+struct ModelConsts {
+    float trans2[kLayers];
+};
+__constant__ ModelConsts c_model[kModelSlots];
+
+// Device status word. Bit 0: a sequence length outside [1, maxlen] was clamped.
+__device__ unsigned g_status;
+
+struct FwdParams {
+    const float *initial_prob;  // [16*K]
+    const float *output_prob;   // [n_obs, K]
+    const float *trans1;        // [K, 4]
+    const uint8_t *data;        // [B, maxlen]
+    const int64_t *lens;        // [B]
+    float *result;              // [B]
+    float *alpha1;              // optional [B, 16*K]
+    float *alpha2;              // optional [B, 16*K]
+    const int *order;           // [B] sequence ids, longest first
+    int *counter;               // work-queue head
+    long long maxlen;
+    int B;
+    int K;
+    int slot;                   // index into c_model
+    int write_alpha;
+    float gamma;
+    float synthetic;
+};
+
+// ---- cluster primitives (PTX) ----------------------------------------------
+__device__ __forceinline__ unsigned cluster_ctarank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ unsigned cluster_nctarank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_arrive() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ unsigned smem_u32(const void *p) {
+    return static_cast<unsigned>(__cvta_generic_to_shared(p));
+}
+// Address of the same shared-memory offset inside CTA `rank` of this cluster.
+__device__ __forceinline__ unsigned map_to_rank(unsigned saddr, unsigned rank) {
+    unsigned r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void st_cluster_f32(unsigned addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void st_cluster_v4(unsigned addr, float a, float b, float c, float d) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b),
+                 "f"(c), "f"(d)
+                 : "memory");
+}
+__device__ __forceinline__ void st_cluster_s32(unsigned addr, int v) {
+    asm volatile("st.shared::cluster.s32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+
+// ---- log-sum-exp building blocks -------------------------------------------
+// exp and log are the fast intrinsics the reference's CUDA backend prints for
+// fp32 (src/cuda/pprint.rs:185-191): ex2.approx(x*log2e), lg2.approx(x)*ln2.
+__device__ __forceinline__ float fast_exp(float x) { return pb::ex2_approx(x * kLog2e); }
+__device__ __forceinline__ float fast_log(float x) { return pb::lg2_approx(x) * kLn2; }
+
+// log(exp(u) + exp(v)); NaN from (-inf)-(-inf) is folded back to -inf the way
+// the reference's trailing max(lsexp, -inf) does (benchmarks/forward.py:156).
+__device__ __forceinline__ float lse2(float u, float v) {
+    const float mx = fmaxf(u, v);
+    const float d = u - v;
+    const float ex = pb::ex2_approx(-fabsf(d) * kLog2e);
+    const float l = pb::lg2_approx(1.0f + ex);
+    return fmaxf(fmaf(l, kLn2, mx), -INFINITY);
+}
+
+__device__ __forceinline__ float lse4(float p0, float p1, float p2, float p3) {
+    const float m = fmaxf(fmaxf(p0, p1), fmaxf(p2, p3));
+    const float s = fast_exp(p0 - m) + fast_exp(p1 - m) + fast_exp(p2 - m) + fast_exp(p3 - m);
+    return fmaxf(fmaf(pb::lg2_approx(s), kLn2, m), -INFINITY);
+}
+
+// The reference's five-term form, operand order as written there
+// (benchmarks/forward.py:145-156).
+__device__ __forceinline__ float lse5_reference(float p1, float p2, float p3, float p4, float p5) {
+    float maxp = fmaxf(p1, p2);
+    maxp = fmaxf(maxp, p3);
+    maxp = fmaxf(maxp, p4);
+    maxp = fmaxf(maxp, p5);
+    float lsexp = maxp + fast_log(fast_exp(p1 - maxp) + fast_exp(p2 - maxp) + fast_exp(p3 - maxp) +
+                                  fast_exp(p4 - maxp) + fast_exp(p5 - maxp));
+    return fmaxf(lsexp, -INFINITY);
+}
+
+// ---- scheduling prologue ----------------------------------------------------
+// Orders sequences longest-first (rank by counting) so that the persistent
+// clusters pop long sequences first, and resets the work-queue head.
+__global__ void hmm_schedule(const int64_t *__restrict__ lens, int B, int *__restrict__ order,
+                             int *__restrict__ counter) {
+    extern __shared__ int s_len[];
+    const bool sort = B <= kSortLimit;
+    if (sort) {
+        for (int i = threadIdx.x; i < B; i += blockDim.x) {
+            long long l = lens[i];
+            s_len[i] = l > 0x7fffffffLL ? 0x7fffffff : (l < 0 ? 0 : static_cast<int>(l));
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < B; i += blockDim.x) {
+            const int li = s_len[i];
+            int rank = 0;
+            for (int j = 0; j < B; ++j) {
+                const int lj = s_len[j];
+                rank += (lj > li) || (lj == li && j < i);
+            }
+            order[rank] = i;
+        }
+    } else {
+        for (int i = threadIdx.x; i < B; i += blockDim.x) order[i] = i;
+    }
+    if (threadIdx.x == 0) *counter = 0;
+}
+
+// ---- resident kernel ---------------------------------------------------------
+// KPT: consecutive k-mers per thread (4 or 1). FIVE: literal five-term LSE.
+// A cluster of CS CTAs x NT threads covers K = CS*NT*KPT k-mers.
+template <int KPT, bool FIVE>
+__global__ void __launch_bounds__(KPT == 4 ? 512 : 1024, 1)
+hmm_forward_resident(const FwdParams p) {
+    extern __shared__ __align__(16) float a0s[];  // [2][4][M] layer-0 values this CTA consumes
+    __shared__ int s_seq;
+    __shared__ float s_warp[32];
+    __shared__ float s_cl[16];
+
+    const int tid = threadIdx.x;
+    const int NT = blockDim.x;
+    const unsigned rank = cluster_ctarank();
+    const unsigned CS = cluster_nctarank();
+    const int K = p.K;
+    const int Kq = K >> 2;
+    const int M = (NT * KPT) >> 2;     // predecessor groups per CTA
+    const int lk = tid * KPT;          // first local k-mer
+    const int g = (rank * NT + tid) * KPT;  // first global k-mer
+    const int lane = tid & 31, warp = tid >> 5, nwarps = (NT + 31) >> 5;
+    const ModelConsts &mc = c_model[p.slot];
+
+    // Transition log-probs into my k-mers: T[j][c] = trans1[p_j, (g+c)%4].
+    float T[4][KPT];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int pj = j * Kq + (g >> 2);
+        if constexpr (KPT == 4) {
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(p.trans1) + pj);
+            T[j][0] = v.x;
+            T[j][1] = v.y;
+            T[j][2] = v.z;
+            T[j][3] = v.w;
+        } else {
+            T[j][0] = __ldg(p.trans1 + pj * 4 + (g & 3));
+        }
+    }
+
+    // Where my new layer-0 values go: k-mer g is predecessor j=g/Kq of group
+    // (g%Kq), which lives in CTA (g%Kq)/M at slot [j][(g%Kq)%M].
+    const unsigned a0_base = smem_u32(a0s);
+    unsigned dst0;
+    {
+        const int dj = g / Kq, rem = g % Kq;
+        const int dr = rem / M, di = rem % M;
+        dst0 = map_to_rank(a0_base + 4u * (dj * M + di), dr);
+    }
+    const unsigned buf_bytes = 16u * M;  // 4 segments * M floats
+    const unsigned seq_addr = smem_u32(&s_seq);
+    const unsigned cl_addr = smem_u32(s_cl);
+
+    for (;;) {
+        // ---- pop the next sequence (cluster leader) and broadcast it ----------
+        if (rank == 0 && tid == 0) {
+            const int i = atomicAdd(p.counter, 1);
+            const int seq = i < p.B ? p.order[i] : -1;
+            for (unsigned r = 0; r < CS; ++r) st_cluster_s32(map_to_rank(seq_addr, r), seq);
+        }
+        cluster_arrive();
+        cluster_wait();
+        const int seq = s_seq;
+        if (seq < 0) break;
+
+        long long len = p.lens[seq];
+        if (len < 1 || len > p.maxlen) {
+            if (tid == 0 && rank == 0) atomicOr(&g_status, 1u);
+            len = len < 1 ? 1 : p.maxlen;
+        }
+        const uint8_t *obs = p.data + static_cast<long long>(seq) * p.maxlen;
+        const int T_len = static_cast<int>(len);
+
+        // ---- t = 0 (benchmarks/forward.py:94-101) ------------------------------
+        float a[kLayers][KPT];
+        float e[KPT], e_next[KPT];
+        int o_next;
+        {
+            const int o0 = obs[0];
+            const int o1 = obs[T_len > 1 ? 1 : 0];
+            o_next = obs[T_len > 2 ? 2 : T_len - 1];
+            if constexpr (KPT == 4) {
+                const float4 v0 = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o0 * K + g));
+                const float4 v1 = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o1 * K + g));
+                e[0] = v0.x; e[1] = v0.y; e[2] = v0.z; e[3] = v0.w;
+                e_next[0] = v1.x; e_next[1] = v1.y; e_next[2] = v1.z; e_next[3] = v1.w;
+            } else {
+                e[0] = __ldg(p.output_prob + (long long)o0 * K + g);
+                e_next[0] = __ldg(p.output_prob + (long long)o1 * K + g);
+            }
+#pragma unroll
+            for (int d = 0; d < kLayers; ++d) {
+                if constexpr (KPT == 4) {
+                    const float4 v = __ldg(reinterpret_cast<const float4 *>(p.initial_prob + d * K + g));
+                    a[d][0] = v.x + e[0];
+                    a[d][1] = v.y + e[1];
+                    a[d][2] = v.z + e[2];
+                    a[d][3] = v.w + e[3];
+                } else {
+                    a[d][0] = __ldg(p.initial_prob + d * K + g) + e[0];
+                }
+            }
+        }
+        unsigned buf = 0;
+        if constexpr (KPT == 4) st_cluster_v4(dst0, a[0][0], a[0][1], a[0][2], a[0][3]);
+        else st_cluster_f32(dst0, a[0][0]);
+        cluster_arrive();
+
+        // ---- t = 1 .. len-1 (benchmarks/forward.py:103-158) --------------------
+        for (int t = 1; t < T_len; ++t) {
+            // emission of o_t was fetched a step ago; fetch o_{t+1}'s row and o_{t+2}
+#pragma unroll
+            for (int c = 0; c < KPT; ++c) e[c] = e_next[c];
+            {
+                const float *row = p.output_prob + (long long)o_next * K + g;
+                if constexpr (KPT == 4) {
+                    const float4 v = __ldg(reinterpret_cast<const float4 *>(row));
+                    e_next[0] = v.x; e_next[1] = v.y; e_next[2] = v.z; e_next[3] = v.w;
+                } else {
+                    e_next[0] = __ldg(row);
+                }
+                const int tn = t + 2 < T_len ? t + 2 : T_len - 1;
+                o_next = obs[tn];
+            }
+
+            cluster_wait();  // layer 0 of step t-1 from every CTA has landed
+            const float *seg = a0s + (buf ? 4 * M : 0) + (lk >> 2);
+            const float a0 = seg[0], a1 = seg[M], a2 = seg[2 * M], a3 = seg[3 * M];
+            const unsigned dst = dst0 + (buf ? 0u : buf_bytes);
+
+            if (!FIVE) {
+                float q[KPT];
+#pragma unroll
+                for (int c = 0; c < KPT; ++c)
+                    q[c] = lse4(T[0][c] + a0, T[1][c] + a1, T[2][c] + a2, T[3][c] + a3);
+                // layer 0 first: it is what the other CTAs wait for
+#pragma unroll
+                for (int c = 0; c < KPT; ++c) a[0][c] = lse2(mc.trans2[0] + q[c], a[1][c]) + e[c];
+                if constexpr (KPT == 4) st_cluster_v4(dst, a[0][0], a[0][1], a[0][2], a[0][3]);
+                else st_cluster_f32(dst, a[0][0]);
+                cluster_arrive();
+#pragma unroll
+                for (int d = 1; d < kLayers; ++d) {
+#pragma unroll
+                    for (int c = 0; c < KPT; ++c) {
+                        const float v = d == 15 ? p.gamma + a[15][c]
+                                      : d == 14 ? p.synthetic + a[15][c]
+                                                : a[d + 1 < kLayers ? d + 1 : 15][c];
+                        a[d][c] = lse2(mc.trans2[d] + q[c], v) + e[c];
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int d = 0; d < kLayers; ++d) {
+#pragma unroll
+                    for (int c = 0; c < KPT; ++c) {
+                        const float t2 = mc.trans2[d];
+                        const float p1 = (T[0][c] + t2) + a0;
+                        const float p2 = (T[1][c] + t2) + a1;
+                        const float p3 = (T[2][c] + t2) + a2;
+                        const float p4 = (T[3][c] + t2) + a3;
+                        const float p5 = d == 15 ? p.gamma + a[15][c]
+                                       : d == 14 ? p.synthetic + a[15][c]
+                                                 : 0.0f + a[d + 1 < kLayers ? d + 1 : 15][c];
+                        a[d][c] = lse5_reference(p1, p2, p3, p4, p5) + e[c];
+                    }
+                    if (d == 0) {
+                        if constexpr (KPT == 4) st_cluster_v4(dst, a[0][0], a[0][1], a[0][2], a[0][3]);
+                        else st_cluster_f32(dst, a[0][0]);
+                        cluster_arrive();
+                    }
+                }
+            }
+            buf ^= 1u;
+        }
+        cluster_wait();  // pairs with the last arrive
+
+        // ---- final log-sum-exp over all states (benchmarks/forward.py:160-173) --
+        float tmax = -INFINITY;
+#pragma unroll
+        for (int d = 0; d < kLayers; ++d)
+#pragma unroll
+            for (int c = 0; c < KPT; ++c) tmax = fmaxf(tmax, a[d][c]);
+        tmax = pb::warp_max(tmax);
+        if (lane == 0) s_warp[warp] = tmax;
+        __syncthreads();
+        if (tid < (int)CS) {
+            float m = -INFINITY;
+            for (int w = 0; w < nwarps; ++w) m = fmaxf(m, s_warp[w]);
+            st_cluster_f32(map_to_rank(cl_addr + 4u * rank, tid), m);
+        }
+        cluster_arrive();
+        cluster_wait();
+        float gmax = -INFINITY;
+        for (unsigned r = 0; r < CS; ++r) gmax = fmaxf(gmax, s_cl[r]);
+
+        float tsum = 0.0f;
+#pragma unroll
+        for (int d = 0; d < kLayers; ++d)
+#pragma unroll
+            for (int c = 0; c < KPT; ++c) tsum += fast_exp(a[d][c] - gmax);
+        tsum = pb::warp_sum(tsum);
+        cluster_arrive();  // everyone has read s_cl (max) before it is reused
+        cluster_wait();
+        if (lane == 0) s_warp[warp] = tsum;
+        __syncthreads();
+        if (tid < (int)CS) {
+            float s = 0.0f;
+            for (int w = 0; w < nwarps; ++w) s += s_warp[w];
+            st_cluster_f32(map_to_rank(cl_addr + 4u * rank, tid), s);
+        }
+        cluster_arrive();
+        cluster_wait();
+        if (rank == 0 && tid == 0) {
+            float s = 0.0f;
+            for (unsigned r = 0; r < CS; ++r) s += s_cl[r];
+            p.result[seq] = gmax + fast_log(s);
+        }
+
+        if (p.write_alpha) {
+            float *dst_alpha = ((len & 1) ? p.alpha1 : p.alpha2) + (long long)seq * (kLayers * (long long)K);
+#pragma unroll
+            for (int d = 0; d < kLayers; ++d) {
+                if constexpr (KPT == 4) {
+                    *reinterpret_cast<float4 *>(dst_alpha + (long long)d * K + g) =
+                        make_float4(a[d][0], a[d][1], a[d][2], a[d][3]);
+                } else {
+                    dst_alpha[(long long)d * K + g] = a[d][0];
+                }
+            }
+        }
+        // The pop at the top of the loop starts with a full cluster barrier, so
+        // s_cl / s_warp / s_seq are free to be rewritten there.
+    }
+}
+
+// ---- streaming kernels --------------------------------------------------------
+__global__ void hmm_stream_init(const FwdParams p) {
+    const long long N = (long long)kLayers * p.K;
+    const long long state = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int inst = blockIdx.y;
+    if (state >= N) return;
+    const int o = p.data[(long long)inst * p.maxlen];
+    p.alpha1[inst * N + state] = p.initial_prob[state] + p.output_prob[(long long)o * p.K + state % p.K];
+}
+
+__global__ void hmm_stream_step(const FwdParams p, int t) {
+    const int K = p.K;
+    const long long N = (long long)kLayers * K;
+    const long long state = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int inst = blockIdx.y;
+    if (state >= N) return;
+    if (t >= p.lens[inst]) return;  // benchmarks/forward.py:113: no write past the end
+    const float *src = ((t & 1) ? p.alpha1 : p.alpha2) + inst * N;
+    float *dst = ((t & 1) ? p.alpha2 : p.alpha1) + inst * N;
+    const ModelConsts &mc = c_model[p.slot];
+    const int o = p.data[(long long)inst * p.maxlen + t];
+    const int s = static_cast<int>(state % K);
+    const int d = static_cast<int>(state / K);
+    const int Kq = K >> 2;
+    const int low = s >> 2;
+    const float t2 = mc.trans2[d];
+    const float p1 = (p.trans1[(0 * Kq + low) * 4 + (s & 3)] + t2) + src[0 * Kq + low];
+    const float p2 = (p.trans1[(1 * Kq + low) * 4 + (s & 3)] + t2) + src[1 * Kq + low];
+    const float p3 = (p.trans1[(2 * Kq + low) * 4 + (s & 3)] + t2) + src[2 * Kq + low];
+    const float p4 = (p.trans1[(3 * Kq + low) * 4 + (s & 3)] + t2) + src[3 * Kq + low];
+    float p5;
+    if (d == 15) p5 = p.gamma + src[state];
+    else if (d == 14) p5 = p.synthetic + src[state + K];
+    else p5 = 0.0f + src[state + K];
+    dst[state] = lse5_reference(p1, p2, p3, p4, p5) + p.output_prob[(long long)o * K + s];
+}
+
+__global__ void hmm_stream_final(const FwdParams p) {
+    __shared__ float s_red[32];
+    __shared__ float s_bcast;
+    const int inst = blockIdx.x;
+    const long long N = (long long)kLayers * p.K;
+    long long len = p.lens[inst];
+    const float *alpha = ((len & 1) ? p.alpha1 : p.alpha2) + inst * N;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    float m = -INFINITY;
+    for (long long i = threadIdx.x; i < N; i += blockDim.x) m = fmaxf(m, alpha[i]);
+    m = pb::warp_max(m);
+    if (lane == 0) s_red[warp] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float v = -INFINITY;
+        for (int w = 0; w < nw; ++w) v = fmaxf(v, s_red[w]);
+        s_bcast = v;
+    }
+    __syncthreads();
+    const float gmax = s_bcast;
+    float s = 0.0f;
+    for (long long i = threadIdx.x; i < N; i += blockDim.x) s += fast_exp(alpha[i] - gmax);
+    s = pb::warp_sum(s);
+    __syncthreads();
+    if (lane == 0) s_red[warp] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float v = 0.0f;
+        for (int w = 0; w < nw; ++w) v += s_red[w];
+        p.result[inst] = gmax + fast_log(v);
+    }
+}
+
+// ---- host side ------------------------------------------------------------------
+struct Plan {
+    int kpt = 0, nt = 0, cs = 0;
+};
+
+// Picks (k-mers per thread, threads per CTA, CTAs per cluster) with
+// K = kpt*nt*cs, or returns false when only the streaming kernel applies.
+bool make_plan(long long K, Plan *pl) {
+    if (K < 4 || (K & (K - 1)) != 0) return false;  // K = 4^k
+    long long kpt = K >= 1024 ? 4 : 1;
+    long long threads = K / kpt;
+    long long nt = std::min<long long>(threads, kpt == 4 ? 512 : 1024);
+    // prefer whole warps; tiny state spaces run as one partial warp
+    long long cs = threads / nt;
+    if (cs > 16 || threads < 32) return false;  // whole warps only; tiny spaces stream
+    if (const char *env = getenv("PARPY_B200_FWD_KPT")) {
+        const int v = atoi(env);
+        if ((v == 1 || v == 4) && K >= 16) {
+            kpt = v;
+            threads = K / kpt;
+            nt = std::min<long long>(threads, kpt == 4 ? 512 : 1024);
+            if (const char *e2 = getenv("PARPY_B200_FWD_NT")) {
+                const long long w = atoll(e2);
+                if (w >= 32 && w <= nt && (w & (w - 1)) == 0) nt = w;
+            }
+            cs = threads / nt;
+            if (cs > 16 || threads < 32) return false;
+        }
+    }
+    pl->kpt = (int)kpt;
+    pl->nt = (int)nt;
+    pl->cs = (int)cs;
+    return true;
+}
+
+using ResidentKernel = void (*)(const FwdParams);
+
+ResidentKernel pick_kernel(int kpt, bool five) {
+    if (kpt == 4) return five ? hmm_forward_resident<4, true> : hmm_forward_resident<4, false>;
+    return five ? hmm_forward_resident<1, true> : hmm_forward_resident<1, false>;
+}
+
+int32_t resident_config(const Plan &pl, bool five, cudaLaunchConfig_t *cfg,
+                        cudaLaunchAttribute *attr, int *max_clusters, ResidentKernel *kern) {
+    ResidentKernel k = pick_kernel(pl.kpt, five);
+    const size_t smem = size_t(2) * 4 * (size_t(pl.nt) * pl.kpt / 4) * sizeof(float);
+    if (pl.cs > 8) PB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    PB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    memset(cfg, 0, sizeof(*cfg));
+    cfg->gridDim = dim3(pl.cs, 1, 1);
+    cfg->blockDim = dim3(pl.nt, 1, 1);
+    cfg->dynamicSmemBytes = smem;
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = pl.cs;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg->attrs = attr;
+    cfg->numAttrs = 1;
+    int n = 0;
+    PB_CUDA(cudaOccupancyMaxActiveClusters(&n, k, cfg));
+    if (n < 1) {
+        pb::set_error("no resident cluster of %d CTAs x %d threads fits this device", pl.cs, pl.nt);
+        return PB_ERR_UNSUPPORTED;
+    }
+    *max_clusters = n;
+    *kern = k;
+    return PB_OK;
+}
+
+std::atomic<unsigned> g_slot{0};
+
+int32_t forward_impl(float gamma, const float *initial_prob, int64_t num_states,
+                     const float *output_prob, float synthetic_248, const float *trans1,
+                     const float *trans2, const void *data, const int64_t *lens, int64_t maxlen,
+                     int64_t num_instances, float *result, float *alpha1, float *alpha2,
+                     uint32_t flags, cudaStream_t stream) {
+    PB_REQUIRE(num_states >= 64 && num_states % 64 == 0,
+               "forward: num_states=%lld must be a positive multiple of 64", (long long)num_states);
+    PB_REQUIRE(num_states <= (1LL << 30), "forward: num_states=%lld too large", (long long)num_states);
+    PB_REQUIRE(num_instances >= 0 && num_instances <= 0x7fffffffLL,
+               "forward: num_instances=%lld out of range", (long long)num_instances);
+    PB_REQUIRE(maxlen >= 1 && maxlen <= 0x7fffffffLL, "forward: maxlen=%lld out of range", (long long)maxlen);
+    if (num_instances == 0) return PB_OK;
+    PB_REQUIRE(initial_prob && output_prob && trans1 && trans2 && data && lens && result,
+               "forward: null table, observation or result pointer");
+    const long long K = num_states / kLayers;
+    const bool streaming_forced = flags & PARPY_B200_FWD_STREAMING;
+    const bool write_alpha = flags & PARPY_B200_FWD_WRITE_ALPHA;
+    const bool five = flags & PARPY_B200_FWD_FIVE_TERM;
+    PB_REQUIRE(!write_alpha || (alpha1 && alpha2), "forward: WRITE_ALPHA needs alpha1 and alpha2");
+
+    pb::DeviceInfo dev;
+    int32_t rc = pb::device_info(&dev);
+    if (rc) return rc;
+    PB_REQUIRE(dev.cc_major >= 10, "forward: needs compute capability 10.x, found %d.%d",
+               dev.cc_major, dev.cc_minor);
+
+    FwdParams p{};
+    p.initial_prob = initial_prob;
+    p.output_prob = output_prob;
+    p.trans1 = trans1;
+    p.data = static_cast<const uint8_t *>(data);
+    p.lens = lens;
+    p.result = result;
+    p.alpha1 = alpha1;
+    p.alpha2 = alpha2;
+    p.maxlen = maxlen;
+    p.B = static_cast<int>(num_instances);
+    p.K = static_cast<int>(K);
+    p.gamma = gamma;
+    p.synthetic = synthetic_248;
+    p.write_alpha = write_alpha ? 1 : 0;
+    p.slot = static_cast<int>(g_slot.fetch_add(1) % kModelSlots);
+    PB_CUDA(cudaMemcpyToSymbolAsync(c_model, trans2, sizeof(ModelConsts),
+                                    size_t(p.slot) * sizeof(ModelConsts), cudaMemcpyDeviceToDevice,
+                                    stream));
+
+    Plan pl;
+    const bool resident = !streaming_forced && make_plan(K, &pl);
+    if (resident) {
+        PB_REQUIRE(pl.kpt == 1 || (pb::aligned16(initial_prob) && pb::aligned16(output_prob) &&
+                                   pb::aligned16(trans1) &&
+                                   (!write_alpha || (pb::aligned16(alpha1) && pb::aligned16(alpha2)))),
+                   "forward: tables must be 16-byte aligned");
+        cudaLaunchConfig_t cfg;
+        cudaLaunchAttribute attr[1];
+        int max_clusters = 0;
+        ResidentKernel kern = nullptr;
+        rc = resident_config(pl, five, &cfg, attr, &max_clusters, &kern);
+        if (rc) return rc;
+        // scratch: order[B] + counter, from the library workspace
+        void *ws = nullptr;
+        const size_t order_bytes = (size_t(p.B) * sizeof(int) + 255) & ~size_t(255);
+        rc = pb::workspace(order_bytes + 512, &ws);
+        if (rc) return rc;
+        int *order = static_cast<int *>(ws);
+        int *counter = reinterpret_cast<int *>(static_cast<char *>(ws) + order_bytes);
+        p.order = order;
+        p.counter = counter;
+        const size_t sched_smem = p.B <= kSortLimit ? size_t(p.B) * sizeof(int) : 0;
+        hmm_schedule<<<1, 1024, sched_smem, stream>>>(lens, p.B, order, counter);
+        PB_CUDA(cudaGetLastError());
+        int clusters = std::min(max_clusters, p.B);
+        if (const char *env = getenv("PARPY_B200_FWD_CLUSTERS")) {
+            const int v = atoi(env);
+            if (v >= 1 && v <= clusters) clusters = v;
+        }
+        cfg.gridDim = dim3(pl.cs * clusters, 1, 1);
+        cfg.stream = stream;
+        PB_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
+        return PB_OK;
+    }
+
+    // streaming path
+    PB_REQUIRE(alpha1 && alpha2, "forward: the streaming kernel needs alpha1 and alpha2 scratch "
+                                 "(num_states=%lld has no resident mapping)", (long long)num_states);
+    PB_REQUIRE(num_instances <= 65535, "forward: streaming kernel supports at most 65535 sequences");
+    const int tpb = 256;
+    dim3 grid((unsigned)((num_states + tpb - 1) / tpb), (unsigned)num_instances, 1);
+    hmm_stream_init<<<grid, tpb, 0, stream>>>(p);
+    PB_CUDA(cudaGetLastError());
+    for (int t = 1; t < maxlen; ++t) {
+        hmm_stream_step<<<grid, tpb, 0, stream>>>(p, t);
+        PB_CUDA(cudaGetLastError());
+    }
+    hmm_stream_final<<<(unsigned)num_instances, 512, 0, stream>>>(p);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t parpy_b200_forward(float gamma, const float *initial_prob, int64_t num_states,
+                           const float *output_prob, float synthetic_248, const float *trans1,
+                           const float *trans2, const void *data, const int64_t *lens,
+                           int64_t maxlen, int64_t num_instances, float *result, float *alpha1,
+                           float *alpha2, uint32_t flags, void *stream) {
+    return forward_impl(gamma, initial_prob, num_states, output_prob, synthetic_248, trans1, trans2,
+                        data, lens, maxlen, num_instances, result, alpha1, alpha2, flags,
+                        static_cast<cudaStream_t>(stream));
+}
+
+int32_t forward_kernel(float gamma, float *initial_prob, int64_t num_states, float *output_prob,
+                       float synthetic_248, float *trans1, float *trans2, int8_t *data,
+                       int64_t *lens, int64_t maxlen, int64_t num_instances, float *result,
+                       float *alpha1, float *alpha2) {
+    return forward_impl(gamma, initial_prob, num_states, output_prob, synthetic_248, trans1, trans2,
+                        data, lens, maxlen, num_instances, result, alpha1, alpha2,
+                        PARPY_B200_FWD_AUTO, nullptr);
+}
+
+int32_t forward_kernel_scratch_first(float gamma, float *initial_prob, int64_t num_states,
+                                     float *output_prob, float synthetic_248, float *trans1,
+                                     float *trans2, int8_t *data, int64_t *lens, int64_t maxlen,
+                                     int64_t num_instances, float *alpha1, float *alpha2,
+                                     float *result) {
+    return forward_impl(gamma, initial_prob, num_states, output_prob, synthetic_248, trans1, trans2,
+                        data, lens, maxlen, num_instances, result, alpha1, alpha2,
+                        PARPY_B200_FWD_AUTO, nullptr);
+}
+
+int32_t parpy_b200_forward_plan(int64_t num_states, int64_t num_instances, int32_t *kmers_per_thread,
+                                int32_t *threads_per_cta, int32_t *ctas_per_cluster,
+                                int32_t *clusters) {
+    Plan pl;
+    if (num_states < 64 || num_states % 64 != 0 || !make_plan(num_states / kLayers, &pl)) {
+        pb::set_error("forward_plan: num_states=%lld has no resident mapping", (long long)num_states);
+        return PB_ERR_UNSUPPORTED;
+    }
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[1];
+    int max_clusters = 0;
+    ResidentKernel kern = nullptr;
+    int32_t rc = resident_config(pl, false, &cfg, attr, &max_clusters, &kern);
+    if (rc) return rc;
+    if (kmers_per_thread) *kmers_per_thread = pl.kpt;
+    if (threads_per_cta) *threads_per_cta = pl.nt;
+    if (ctas_per_cluster) *ctas_per_cluster = pl.cs;
+    if (clusters) *clusters = (int32_t)std::min<int64_t>(max_clusters, std::max<int64_t>(num_instances, 1));
+    return PB_OK;
+}
+
+int32_t parpy_b200_forward_status(uint32_t *status) {
+    PB_REQUIRE(status != nullptr, "forward_status: null output pointer");
+    unsigned v = 0, zero = 0;
+    PB_CUDA(cudaDeviceSynchronize());
+    PB_CUDA(cudaMemcpyFromSymbol(&v, g_status, sizeof(v)));
+    PB_CUDA(cudaMemcpyToSymbol(g_status, &zero, sizeof(zero)));
+    *status = v;
+    return PB_OK;
+}
+
+}  // extern "C"
