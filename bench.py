@@ -1,0 +1,393 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: 7-mer HMM forward, 500 ragged sequences per GPU.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one forward pass over the whole batch (all sequences, all time
+steps). Prints ONE JSON line on rank 0. Under torchrun every rank drives its own
+GPU on its own shard; the only collective is the final all-gather of the
+per-sequence log-likelihoods, inside the timed step.
+
+  value     state-steps/s, whole job, inputs resident in HBM (device-timed)
+  e2e       the same metric through the Python call surface with pinned HOST
+            arrays: host->device copies of tables and observations and the
+            device->host copy of the result inside the timed region
+  roofline  algorithmic bytes (8.25 B per state-step: alpha read+write, one
+            emission row and one observation byte per sequence-step) over the
+            live-measured duration, against the measured HBM copy bandwidth
+  cpu_baseline / --impl reference
+            the CPU restatement of the reference algorithm (oracle/) on the
+            host cores, on a bounded sample of the same workload
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "hmm_forward_7mer_state_steps_per_s"
+UNIT = "state-steps/s"
+KMER = 7
+BATCH = 500
+MIN_LEN, MAX_LEN = 1000, 4000
+SEED = 1234
+FALLBACK_HBM_GBS = 6650.0
+L2_FLUSH_BYTES = 256 << 20
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak",
+                    help="weak: 500 sequences per GPU; strong: 500 sequences sharded over the GPUs")
+    ap.add_argument("--variant", choices=["auto", "five_term", "streaming"], default="auto")
+    ap.add_argument("--ref-cuda", action="store_true",
+                    help="also time the reference's own CUDA implementation (oracle/_ref), once")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=BATCH, help=argparse.SUPPRESS)
+    ap.add_argument("--kmer", type=int, default=KMER, help=argparse.SUPPRESS)
+    ap.add_argument("--min-len", type=int, default=MIN_LEN, help=argparse.SUPPRESS)
+    ap.add_argument("--max-len", type=int, default=MAX_LEN, help=argparse.SUPPRESS)
+    return ap.parse_args()
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+def workload_config(args, world):
+    return {
+        "workload": f"hmm_forward_{args.kmer}mer",
+        "num_states": 16 * 4 ** args.kmer,
+        "batch_per_gpu": args.batch if args.scaling == "weak" else None,
+        "global_batch": args.batch * (world if args.scaling == "weak" else 1),
+        "seq_len": f"uniform[{args.min_len},{args.max_len}]",
+        "obs_levels": 101,
+        "parallelism": f"sequence-sharded x{world}",
+        "cache": "L2 flushed between timed steps (256 MiB write)",
+        "variant": args.variant,
+    }
+
+
+# ---- CPU baseline: the oracle port on the host cores -------------------------------
+def cpu_sample(hmm, seqs, cores):
+    """A bounded sample of the workload: the first 2*cores sequences cut to 256
+    time steps each (about 10 s of CPU work at ~2e7 state-steps/s/core)."""
+    import torch
+    n = max(2, 2 * cores)
+    steps = 256
+    sub = {
+        "data": seqs["data"][:n, :steps].contiguous(),
+        "lens": torch.clamp(seqs["lens"][:n], max=steps).contiguous(),
+    }
+    desc = f"first {n} sequences of the batch, cut to {steps} time steps, {cores} OpenMP threads"
+    return sub, desc
+
+
+def time_cpu_once(hmm, sub, cores):
+    from oracle import oracle
+    t0 = time.perf_counter()
+    oracle.forward(hmm, sub, num_threads=cores)
+    dt = time.perf_counter() - t0
+    work = int(hmm["num_states"]) * int(sub["lens"].sum())
+    return work, dt
+
+
+def run_reference_arm(args, rank, world):
+    if rank != 0:
+        return
+    from oracle import oracle
+    from parpy_b200 import synthetic
+    cores = oracle.max_threads()
+    hmm = synthetic.hmm_model(args.kmer, seed=SEED)
+    seqs = synthetic.hmm_sequences(args.batch, args.min_len, args.max_len, seed=SEED)
+    sub, desc = cpu_sample(hmm, seqs, cores)
+    for _ in range(args.warmup):
+        time_cpu_once(hmm, sub, cores)
+    times, work = [], 0
+    for _ in range(args.steps):
+        work, dt = time_cpu_once(hmm, sub, cores)
+        times.append(dt)
+    total = sum(times)
+    value = work * args.steps / total
+    cfg = workload_config(args, 1)
+    cfg["cache"] = "n/a (CPU)"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": cfg,
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---- clocks -------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for ln in open(self.path):
+                f = [x.strip() for x in ln.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                      "sw_power_cap"), f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons),
+                       samples=len(sm))
+        return out
+
+
+# ---- our arm ---------------------------------------------------------------------------
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as td
+    import parpy_b200 as parpy
+    from parpy_b200 import _native, dist, hmm as hmm_mod, synthetic
+
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} does not match WORLD_SIZE {world}")
+    if args.gpus > 1 and world == 1:
+        raise SystemExit("launch multi-GPU runs with torchrun (one process per GPU)")
+    torch.cuda.set_device(local_rank)
+    _native.lib()  # fail loudly if the CUDA library is missing
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        td.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    # ---- inputs: identical tables on every rank, per-rank sequences -------------------
+    hmm = synthetic.hmm_model(args.kmer, seed=SEED)
+    if args.scaling == "weak":
+        seqs = synthetic.hmm_sequences(args.batch, args.min_len, args.max_len, seed=SEED + 17 * rank)
+        global_lens = None
+    else:
+        all_seqs = synthetic.hmm_sequences(args.batch, args.min_len, args.max_len, seed=SEED)
+        global_lens = all_seqs["lens"].numpy()
+        seqs, _ = dist.shard_sequences(all_seqs, rank, world)
+    local_work = synthetic.state_steps(hmm, seqs)
+    local_bytes = synthetic.forward_algorithmic_bytes(hmm, seqs)
+    batch = int(seqs["num_instances"])
+
+    dev_hmm = hmm_mod.to_device(hmm)
+    dev_seqs = hmm_mod.to_device(seqs)
+    opts = parpy.par({"inst": parpy.threads(batch)})
+    if args.variant != "auto":
+        opts.b200 = {"forward": args.variant}
+    alpha = None
+    if args.variant == "streaming":
+        n = int(hmm["num_states"])
+        alpha = (torch.zeros(batch, n, device="cuda"), torch.zeros(batch, n, device="cuda"))
+    result = torch.zeros(batch, dtype=torch.float32, device="cuda")
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device="cuda")
+    gather_buf = [torch.empty_like(result) for _ in range(world)] if world > 1 and args.scaling == "weak" else None
+
+    def step_device():
+        a1, a2 = alpha if alpha is not None else (None, None)
+        hmm_mod.forward_kernel(dev_hmm, dev_seqs, result, a1, a2, opts=opts)
+        if world > 1:
+            if args.scaling == "weak":
+                td.all_gather(gather_buf, result)
+            else:
+                dist.gather_results(result, global_lens)
+
+    def barrier():
+        if world > 1:
+            td.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 0)):
+        step_device()
+    barrier()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    events = []
+    barrier()
+    for _ in range(args.steps):
+        flush.fill_(1)                      # evict L2 between timed steps (untimed)
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        step_device()
+        e1.record()
+        events.append((e0, e1))
+    barrier()
+    step_ms = [a.elapsed_time(b) for a, b in events]
+    total_ms = sum(step_ms)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- end to end: pinned host arrays through the public call ----------------------
+    pin_hmm = {k: (v.pin_memory() if isinstance(v, torch.Tensor) and v.dim() > 0 else v) for k, v in hmm.items()}
+    pin_seqs = {k: (v.pin_memory() if isinstance(v, torch.Tensor) and v.dim() > 0 else v) for k, v in seqs.items()}
+    host_result = torch.zeros(batch, dtype=torch.float32).pin_memory()
+    h2d = sum(v.numel() * v.element_size() for d in (pin_hmm, pin_seqs) for v in d.values()
+              if isinstance(v, torch.Tensor) and v.dim() > 0)
+    d2h = host_result.numel() * 4
+
+    def step_e2e():
+        hmm_mod.forward_kernel(pin_hmm, pin_seqs, host_result, None, None, opts=opts)
+        if world > 1 and args.scaling == "weak":
+            td.all_gather(gather_buf, host_result.cuda(non_blocking=True))
+
+    for _ in range(min(args.warmup, 2)):
+        step_e2e()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step_e2e()
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    assert torch.equal(host_result.cuda(), result), "end-to-end result differs from the device-resident run"
+
+    # ---- reduce over ranks: max time, summed work ---------------------------------------
+    stats = torch.tensor([total_ms, e2e_s, float(local_work), float(local_bytes)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        mx = stats.clone()
+        td.all_reduce(mx, op=td.ReduceOp.MAX)
+        sm = stats.clone()
+        td.all_reduce(sm, op=td.ReduceOp.SUM)
+        total_ms, e2e_s = float(mx[0]), float(mx[1])
+        work, nbytes = float(sm[2]), float(sm[3])
+    else:
+        work, nbytes = float(local_work), float(local_bytes)
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        value = work * args.steps / (total_ms * 1e-3)
+        # dominant kernel: the resident forward kernel, one launch per step per rank;
+        # the step also holds a one-CTA scheduling prologue of a few microseconds
+        launch_s = statistics.mean(step_ms) * 1e-3
+        achieved = local_bytes / launch_s / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+            "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args, world),
+            "e2e": {"value": work * args.steps / e2e_s, "unit": UNIT,
+                    "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
+            "gpu_launches": 2 * args.steps * world,
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": ncu_traffic_bytes(args),
+                         "peak_source": peak_kind,
+                         "note": "algorithmic bytes (8.25 B/state-step) per launch over the measured "
+                                 "launch duration; alpha stays on chip, so DRAM traffic is far lower"},
+            "step_ms": step_ms,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            from oracle import oracle
+            cores = oracle.max_threads()
+            sub, desc = cpu_sample(hmm, seqs, cores)
+            w, dt = time_cpu_once(hmm, sub, cores)
+            line["cpu_baseline"] = {"value": w / dt, "unit": UNIT, "cores": cores, "kind": "port",
+                                    "sample": desc}
+        if args.ref_cuda and world == 1:
+            line["reference_cuda"] = time_reference_cuda(args, hmm, seqs, result, local_work)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        td.barrier()
+        td.destroy_process_group()
+
+
+def ncu_traffic_bytes(args):
+    """DRAM bytes per launch of the resident kernel from the committed ncu
+    summary (profiles/), scaled to this workload; None until one is recorded."""
+    path = os.path.join(ROOT, "profiles", "hmm_forward_resident_traffic.json")
+    try:
+        with open(path) as f:
+            rec = json.load(f)
+        if args.variant != "auto" or args.kmer != rec.get("kmer"):
+            return None
+        steps = args.batch * (args.min_len + args.max_len) / 2.0
+        return rec["dram_bytes_per_sequence_step"] * steps
+    except Exception:
+        return None
+
+
+def time_reference_cuda(args, hmm, seqs, ours, work):
+    """The reference's own CUDA implementation (benchmarks/7mer/hmm.cu compiled
+    unmodified into oracle/_ref) on the same batch, host arrays in and out as
+    its ABI requires; one run, wall clock."""
+    import numpy as np
+    import torch
+    from oracle import oracle
+    if not oracle.trellis_available(args.kmer):
+        return {"unavailable": "oracle/_ref has no build for this k"}
+    oracle.trellis_forward(args.kmer, hmm, {"data": seqs["data"][:2], "lens": seqs["lens"][:2]})  # warm-up
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    ref = oracle.trellis_forward(args.kmer, hmm, seqs)
+    dt = time.perf_counter() - t0
+    got = ours.cpu().numpy()
+    rel = float(np.max(np.abs(got - ref) / np.abs(ref)))
+    return {"value": work / dt, "unit": UNIT, "seconds": dt, "max_rel_vs_ours": rel,
+            "what": "benchmarks/7mer/hmm.cu forward(), incl. its cudaMalloc/H2D/D2H per call"}
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,148 @@
+"""Python face of the CPU oracle.
+
+TEST INFRASTRUCTURE ONLY: the checker the CUDA kernels are compared against.
+Only the tests, the smoke check and the CPU-baseline leg of the benchmark may
+import this module; the shipped package never does.
+
+Parity pin: :func:`forward` (the C restatement in ``hmm_oracle.c``) and
+:func:`forward_numpy` reproduce the reference's golden vectors
+test/data/3mer-expected.txt and test/data/5mer-expected.txt; the CPU test suite
+asserts it.
+"""
+import ctypes
+import os
+
+import numpy as np
+
+from . import build as _build
+
+_lib = None
+_P = ctypes.c_void_p
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        path = _build.build_oracle()
+        _lib = ctypes.CDLL(path)
+        _lib.oracle_forward.restype = ctypes.c_int
+        _lib.oracle_forward.argtypes = [ctypes.c_float, _P, ctypes.c_int64, _P, ctypes.c_float, _P,
+                                        _P, _P, _P, ctypes.c_int64, ctypes.c_int64, _P, _P,
+                                        ctypes.c_int32]
+        _lib.oracle_max_threads.restype = ctypes.c_int32
+    return _lib
+
+
+def max_threads():
+    return int(lib().oracle_max_threads())
+
+
+def _np(x, dtype):
+    if hasattr(x, "detach"):
+        x = x.detach().cpu().numpy()
+    return np.ascontiguousarray(np.asarray(x), dtype=dtype)
+
+
+def forward(hmm, seqs, want_alpha=False, num_threads=0):
+    """C restatement of benchmarks/forward.py:94-187 on host arrays. ``hmm`` and
+    ``seqs`` are the reference's dictionaries (torch or numpy values). Returns
+    float32 log-likelihoods [B] (and the final alpha [B, N] when asked)."""
+    n = int(hmm["num_states"])
+    init = _np(hmm["initial_prob"], np.float32)
+    outp = _np(hmm["output_prob"], np.float32)
+    t1 = _np(hmm["trans1"], np.float32)
+    t2 = _np(hmm["trans2"], np.float32)
+    data = _np(seqs["data"], None)
+    if data.dtype not in (np.int8, np.uint8):
+        raise TypeError("observations must be int8 or uint8")
+    lens = _np(seqs["lens"], np.int64)
+    batch, maxlen = data.shape
+    res = np.zeros(batch, dtype=np.float32)
+    alpha = np.zeros((batch, n), dtype=np.float32) if want_alpha else None
+    rc = lib().oracle_forward(
+        float(hmm["gamma"]), init.ctypes.data, n, outp.ctypes.data, float(hmm["synthetic_248"]),
+        t1.ctypes.data, t2.ctypes.data, data.ctypes.data, lens.ctypes.data, maxlen, batch,
+        res.ctypes.data, alpha.ctypes.data if want_alpha else None, int(num_threads))
+    if rc != 0:
+        raise RuntimeError("oracle_forward rejected its arguments")
+    return (res, alpha) if want_alpha else res
+
+
+def forward_numpy(hmm, seqs):
+    """Vectorised float32 NumPy restatement of the same algorithm
+    (benchmarks/forward.py:94-187), independent of the C code: alpha is kept as
+    [B, 16, K]; the five terms are summed in the order p1..p5 (:149-155); a NaN
+    log-sum-exp becomes -inf through fmax (:156); sequences stop at their own
+    length (:113). Small inputs only (pure NumPy)."""
+    n = int(hmm["num_states"])
+    K = n // 16
+    f = np.float32
+    t1 = _np(hmm["trans1"], f)
+    t2 = _np(hmm["trans2"], f)
+    outp = _np(hmm["output_prob"], f)
+    init = _np(hmm["initial_prob"], f).reshape(16, K)
+    gamma = f(float(hmm["gamma"]))
+    syn = f(float(hmm["synthetic_248"]))
+    data = _np(seqs["data"], None).view(np.uint8)
+    lens = _np(seqs["lens"], np.int64)
+    B = data.shape[0]
+    s = np.arange(K)
+    pred = (np.arange(4)[:, None] * (K // 4) + s[None, :] // 4)          # [4, K]  (:117-120)
+    tr = t1[pred, s[None, :] % 4]                                          # [4, K]  (:121-124)
+    c = np.zeros(16, dtype=f)
+    c[14] = syn
+    c[15] = gamma
+    alpha = init[None, :, :] + outp[data[:, 0]][:, None, :]               # (:96-101)
+    alpha = alpha.astype(f)
+    with np.errstate(invalid="ignore", divide="ignore", over="ignore"):
+        for t in range(1, int(lens.max())):
+            live = t < lens
+            if not live.any():
+                break
+            a = alpha[live]
+            a0 = a[:, 0, :][:, pred]                                       # [b, 4, K]
+            p14 = (tr[None, :, None, :] + t2[None, None, :, None]) + a0[:, :, None, :]   # (:126-129)
+            nxt = np.concatenate([a[:, 1:, :], a[:, 15:, :]], axis=1)      # (:131-141)
+            p5 = c[None, :, None] + nxt                                    # (:142)
+            m = np.maximum(np.maximum(np.maximum(np.maximum(p14[:, 0], p14[:, 1]), p14[:, 2]),
+                                      p14[:, 3]), p5)                      # (:145-148)
+            ssum = (np.exp(p14[:, 0] - m) + np.exp(p14[:, 1] - m) + np.exp(p14[:, 2] - m) +
+                    np.exp(p14[:, 3] - m) + np.exp(p5 - m))
+            lse = np.fmax(m + np.log(ssum), f(-np.inf))                    # (:149-156)
+            new = lse + outp[data[live, t]][:, None, :]                    # (:158)
+            alpha[live] = new.astype(f)
+        flat = alpha.reshape(B, n)
+        m = flat.max(axis=1)
+        res = m + np.log(np.exp(flat - m[:, None]).sum(axis=1, dtype=f))   # (:168-173)
+    return res.astype(f)
+
+
+# ---- reference-shipped CUDA (needs a GPU; built by oracle/build.py) -------------
+def trellis_available(k):
+    return os.path.exists(os.path.join(_build.REF_DIR, f"trellis_{k}mer.so"))
+
+
+def trellis_forward(k, hmm, seqs):
+    """Runs the reference's own CUDA implementation (benchmarks/{5,7}mer/hmm.cu,
+    compiled unmodified into oracle/_ref) through the ctypes protocol of
+    benchmarks/7mer/trellis.py:7-23,93-138. Host arrays in, host result out;
+    needs a GPU. Its `init` uploads the tables into __device__ globals."""
+    path = os.path.join(_build.REF_DIR, f"trellis_{k}mer.so")
+    t = ctypes.CDLL(path)
+    t1 = _np(hmm["trans1"], np.float32)
+    t2 = _np(hmm["trans2"], np.float32)
+    outp = _np(hmm["output_prob"], np.float32)
+    init = _np(hmm["initial_prob"], np.float32)
+    t.init.argtypes = [ctypes.c_float, _P, _P, _P, _P, ctypes.c_float]
+    t.init.restype = None
+    t.init(float(hmm["gamma"]), t1.ctypes.data, t2.ctypes.data, outp.ctypes.data, init.ctypes.data,
+           float(hmm["synthetic_248"]))
+    data = _np(seqs["data"], None).view(np.uint8)
+    lens = _np(seqs["lens"], np.int32)
+    batch, maxlen = data.shape
+    t.forward.argtypes = [_P, _P, ctypes.c_int, ctypes.c_int]
+    t.forward.restype = ctypes.POINTER(ctypes.c_float)
+    res_ptr = t.forward(data.ctypes.data, lens.ctypes.data, maxlen, batch)
+    res = np.ctypeslib.as_array(res_ptr, shape=(batch,)).copy()
+    ctypes.CDLL(None).free(res_ptr)
+    return res

@@ -1,0 +1,277 @@
+"""Parity of the CUDA HMM forward kernels with the reference's golden vectors and
+the CPU oracle, through the C ABI and through the Python call surface.
+
+Tolerances: the reference's own test accepts torch.allclose(atol=1e-5) with the
+default rtol=1e-5 (test/test_forward.py:176-178); the target for this library is
+max relative error <= 1e-4 on fp32 log-likelihoods. Both are asserted against
+the golden vectors; comparisons with the oracle use 1e-5.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import load_expected, load_model, load_signals, max_rel, shortest_reads
+from gpu_util import cabi_forward, to_dev
+
+pytestmark = pytest.mark.gpu
+
+REL_TARGET = 1e-4        # library target vs the reference
+REL_ORACLE = 1e-5        # kernel vs fp32 CPU oracle on identical inputs
+FLAGS = {"factored": 0, "five_term": 4, "streaming": 1}
+
+
+@pytest.fixture(scope="module")
+def oracle_mod():
+    from oracle import oracle
+    return oracle
+
+
+@pytest.mark.parametrize("model", ["3mer", "5mer"])
+@pytest.mark.parametrize("variant", ["factored", "five_term", "streaming"])
+def test_golden_vectors_all_reads(native, model, variant):
+    hmm, seqs, exp = to_dev(load_model(model)), to_dev(load_signals()), load_expected(model)
+    rc, res, _, _ = cabi_forward(native, hmm, seqs, FLAGS[variant], alpha=(variant == "streaming"))
+    assert rc == 0, native.error_message()
+    got = res.cpu().numpy()
+    assert max_rel(got, exp) <= REL_TARGET
+    assert np.allclose(got, exp, atol=1e-5, rtol=1e-5), max_rel(got, exp)
+    if variant != "factored":
+        # same operand order as the reference: agreement to a few ulp
+        assert max_rel(got, exp) <= 1e-6
+
+
+@pytest.mark.parametrize("entry", ["forward_kernel", "forward_kernel_scratch_first"])
+def test_reference_shaped_entries_on_default_stream(native, entry):
+    hmm, seqs, exp = to_dev(load_model("3mer")), to_dev(load_signals()), load_expected("3mer")
+    rc, res, _, _ = cabi_forward(native, hmm, seqs, entry=entry)
+    assert rc == 0, native.error_message()
+    torch.cuda.synchronize()
+    assert np.allclose(res.cpu().numpy(), exp, atol=1e-5, rtol=1e-5)
+
+
+def test_5mer_config_against_oracle(native, oracle_mod):
+    # BASELINE config: 5mer, 100 sequences of T=2000 (oracle on a subset to keep CPU time bounded)
+    from parpy_b200 import synthetic
+    hmm = synthetic.hmm_model(5)
+    seqs = synthetic.hmm_sequences(100, 2000, 2000)
+    rc, res, _, _ = cabi_forward(native, to_dev(hmm), to_dev(seqs))
+    assert rc == 0, native.error_message()
+    got = res.cpu().numpy()
+    assert np.isfinite(got).all()
+    idx = np.arange(0, 100, 9)
+    sub = {"data": seqs["data"][idx], "lens": seqs["lens"][idx]}
+    exp = oracle_mod.forward(hmm, sub)
+    assert max_rel(got[idx], exp) <= REL_ORACLE
+
+
+def test_7mer_against_oracle_with_final_alpha(native, oracle_mod):
+    # 7mer state space (262144 states), ragged short sequences so the oracle finishes in seconds;
+    # checks every state of the final alpha vector, not just the scalar.
+    from parpy_b200 import synthetic
+    hmm = synthetic.hmm_model(7)
+    seqs = synthetic.hmm_sequences(5, 1, 120, seed=99)
+    seqs["lens"][0] = 1
+    seqs["lens"][1] = 2
+    exp, exp_alpha = oracle_mod.forward(hmm, seqs, want_alpha=True)
+    for variant in ("factored", "five_term"):
+        rc, res, a1, a2 = cabi_forward(native, to_dev(hmm), to_dev(seqs), FLAGS[variant] | 2, alpha=True)
+        assert rc == 0, native.error_message()
+        assert max_rel(res.cpu().numpy(), exp) <= REL_ORACLE
+        for i in range(5):
+            # the reference leaves the final alpha in alpha1 for odd lengths (forward.py:163-165)
+            a = (a1 if int(seqs["lens"][i]) & 1 else a2)[i].cpu().numpy()
+            other = (a2 if int(seqs["lens"][i]) & 1 else a1)[i].cpu().numpy()
+            assert max_rel(a, exp_alpha[i]) <= REL_ORACLE
+            assert not other.any()
+
+
+def test_7mer_full_config_properties(native):
+    # BASELINE config: 500 sequences, lengths uniform in [1000, 4000]; size-independent checks.
+    from parpy_b200 import synthetic
+    hmm = synthetic.hmm_model(7)
+    seqs = synthetic.hmm_sequences(500, 1000, 4000)
+    dh, ds = to_dev(hmm), to_dev(seqs)
+    rc, res, _, _ = cabi_forward(native, dh, ds)
+    assert rc == 0, native.error_message()
+    full = res.cpu().numpy()
+    assert np.isfinite(full).all() and (full < 0).all()
+    # determinism: a second run is bit-identical
+    rc, res2, _, _ = cabi_forward(native, dh, ds)
+    assert np.array_equal(full, res2.cpu().numpy())
+    # permutation / batch-composition invariance: every sequence is scored independently
+    perm = torch.randperm(500, generator=torch.Generator().manual_seed(5))[:97]
+    sub = {"data": seqs["data"][perm].contiguous(), "lens": seqs["lens"][perm].contiguous(),
+           "maxlen": seqs["maxlen"], "num_instances": torch.tensor(97)}
+    rc, res3, _, _ = cabi_forward(native, dh, to_dev(sub))
+    assert rc == 0
+    assert np.array_equal(res3.cpu().numpy(), full[perm.numpy()])
+    # a prefix is at least as likely as the whole sequence (all emissions are log-probabilities)
+    half = dict(sub)
+    half["lens"] = (sub["lens"] // 2).contiguous()
+    rc, res4, _, _ = cabi_forward(native, dh, to_dev(half))
+    assert (res4.cpu().numpy() >= res3.cpu().numpy()).all()
+    # the five-term form agrees with the factored form far inside the tolerance
+    rc, res5, _, _ = cabi_forward(native, dh, to_dev(sub), FLAGS["five_term"])
+    assert max_rel(res3.cpu().numpy(), res5.cpu().numpy()) <= REL_ORACLE
+
+
+def test_padding_is_never_used_and_uint8_is_accepted(native):
+    from parpy_b200 import synthetic
+    hmm = synthetic.hmm_model(5, seed=3)
+    seqs = synthetic.hmm_sequences(40, 3, 300, seed=8)          # padding = -7 (out of range)
+    dh = to_dev(hmm)
+    rc, a, _, _ = cabi_forward(native, dh, to_dev(seqs))
+    clean = dict(seqs)
+    d = seqs["data"].clone()
+    d[d < 0] = 0
+    clean["data"] = d.to(torch.uint8)
+    rc2, b, _, _ = cabi_forward(native, dh, to_dev(clean))
+    assert rc == 0 and rc2 == 0
+    assert np.array_equal(a.cpu().numpy(), b.cpu().numpy())
+    # extra slack columns (maxlen larger than any length) change nothing
+    wide = dict(clean)
+    wide["data"] = torch.cat([clean["data"], torch.full((40, 17), 100, dtype=torch.uint8)], dim=1).contiguous()
+    wide["maxlen"] = torch.tensor(wide["data"].shape[1])
+    rc3, c, _, _ = cabi_forward(native, dh, to_dev(wide))
+    assert rc3 == 0 and np.array_equal(a.cpu().numpy(), c.cpu().numpy())
+
+
+@pytest.mark.parametrize("k", [2, 3, 4, 6])
+def test_other_state_spaces_against_oracle(native, oracle_mod, k):
+    # k=2 (256 states) has no resident mapping and runs the streaming kernel
+    from parpy_b200 import synthetic
+    hmm = synthetic.hmm_model(k, seed=k)
+    seqs = synthetic.hmm_sequences(7, 1, 90 if k < 6 else 40, seed=k + 1)
+    exp = oracle_mod.forward(hmm, seqs)
+    rc, res, _, _ = cabi_forward(native, to_dev(hmm), to_dev(seqs), alpha=True)
+    assert rc == 0, native.error_message()
+    assert max_rel(res.cpu().numpy(), exp) <= REL_ORACLE
+
+
+def test_zero_probability_emissions_stay_minus_inf(native, oracle_mod):
+    hmm = load_model("3mer")
+    seqs = load_signals(shortest_reads(3))
+    last = int(seqs["data"][0, int(seqs["lens"][0]) - 1].item())
+    hmm["output_prob"] = hmm["output_prob"].clone()
+    hmm["output_prob"][last, 5] = -np.inf
+    exp, exp_alpha = oracle_mod.forward(hmm, seqs, want_alpha=True)
+    rc, res, a1, a2 = cabi_forward(native, to_dev(hmm), to_dev(seqs), 2, alpha=True)
+    assert rc == 0
+    a = (a1 if int(seqs["lens"][0]) & 1 else a2)[0].cpu().numpy().reshape(16, 64)
+    assert np.isneginf(a[:, 5]).all() and not np.isnan(a).any()
+    assert max_rel(res.cpu().numpy(), exp) <= REL_ORACLE
+
+
+def test_bad_arguments_are_rejected_with_a_message(native):
+    from parpy_b200 import synthetic
+    hmm, seqs = to_dev(synthetic.hmm_model(3)), to_dev(synthetic.hmm_sequences(4, 5, 9))
+    bad = dict(hmm)
+    bad["num_states"] = torch.tensor(1000)
+    rc, _, _, _ = cabi_forward(native, bad, seqs)
+    assert rc != 0 and "multiple of 64" in native.error_message()
+    rc, _, _, _ = cabi_forward(native, hmm, seqs, FLAGS["streaming"], alpha=False)
+    assert rc != 0 and "alpha1 and alpha2" in native.error_message()
+    # the context is still healthy afterwards
+    rc, res, _, _ = cabi_forward(native, hmm, seqs)
+    assert rc == 0 and np.isfinite(res.cpu().numpy()).all()
+
+
+def test_out_of_range_lengths_are_clamped_and_flagged(native):
+    from parpy_b200 import synthetic
+    hmm, seqs = synthetic.hmm_model(3), synthetic.hmm_sequences(4, 5, 9, pad_value=0)
+    st = ctypes.c_uint32(7)
+    assert native.lib().parpy_b200_forward_status(ctypes.byref(st)) == 0
+    seqs["lens"][2] = 10_000
+    rc, res, _, _ = cabi_forward(native, to_dev(hmm), to_dev(seqs))
+    assert rc == 0
+    assert native.lib().parpy_b200_forward_status(ctypes.byref(st)) == 0
+    assert st.value & 1
+    assert np.isfinite(res.cpu().numpy()).all()
+    assert native.lib().parpy_b200_forward_status(ctypes.byref(st)) == 0 and st.value == 0
+
+
+# ---- the Python call surface, written the way the reference's tests are ------------
+def _forward_like_reference(hmm, seqs, opts, device):
+    # test/test_forward.py:162-167
+    import parpy_b200 as parpy
+
+    @parpy.jit
+    def forward_kernel(hmm, seqs, alpha1, alpha2, result):
+        pass
+
+    n, b = int(hmm["num_states"]), int(seqs["num_instances"])
+    alpha1 = torch.zeros((b, n), dtype=torch.float32, device=device)
+    alpha2 = torch.zeros_like(alpha1)
+    result = torch.zeros(b, dtype=torch.float32, device=device)
+    forward_kernel(hmm, seqs, alpha1, alpha2, result, opts=opts)
+    return result, alpha1, alpha2
+
+
+@pytest.mark.parametrize("nthreads", [512, 2048])
+@pytest.mark.parametrize("device", ["cpu", "cuda"])
+def test_forward_python_surface(device, nthreads):
+    # test/test_forward.py:180-207 (single block / multi block), host arrays and device arrays
+    import parpy_b200 as parpy
+    hmm, seqs, exp = load_model("3mer"), load_signals(), torch.from_numpy(load_expected("3mer"))
+    if device == "cuda":
+        hmm = {k: v.cuda() for k, v in hmm.items()}      # 0-d entries on the device too, as in the benchmark
+        seqs = {k: v.cuda() for k, v in seqs.items()}
+    p = {"inst": parpy.threads(int(seqs["num_instances"])), "state": parpy.threads(nthreads)}
+    opts = parpy.par(p)
+    probs, a1, a2 = _forward_like_reference(hmm, seqs, opts, device)
+    if device == "cuda":
+        torch.cuda.synchronize()
+    assert torch.allclose(probs.cpu(), exp, atol=1e-5), f"{probs}\n{exp}"
+    assert not a1.any() and not a2.any()        # resident kernel: scratch untouched
+
+
+def test_forward_python_surface_numpy_and_write_alpha(oracle_mod):
+    import parpy_b200 as parpy
+    from parpy_b200.hmm import forward_kernel
+    idx = shortest_reads(3)
+    hmm_t, seqs_t = load_model("3mer"), load_signals(idx)
+    exp, exp_alpha = oracle_mod.forward(hmm_t, seqs_t, want_alpha=True)
+    hmm = {k: v.numpy() for k, v in hmm_t.items()}
+    seqs = {k: v.numpy() for k, v in seqs_t.items()}
+    result = np.zeros(3, dtype=np.float32)
+    a1 = np.zeros((3, 1024), dtype=np.float32)
+    a2 = np.zeros_like(a1)
+    opts = parpy.par({"inst": parpy.threads(3)})
+    opts.b200 = {"write_alpha": True}
+    forward_kernel(hmm, seqs, result, a1, a2, opts=opts)
+    assert max_rel(result, exp) <= REL_ORACLE
+    for i in range(3):
+        got = a1[i] if int(seqs["lens"][i]) & 1 else a2[i]
+        assert max_rel(got, exp_alpha[i]) <= REL_ORACLE
+    # non-contiguous and read-only arrays are rejected like the reference does
+    with pytest.raises(ValueError, match="contiguous"):
+        forward_kernel(hmm, seqs, np.zeros(6, dtype=np.float32)[::2], a1, a2, opts=opts)
+
+
+def test_forward_parpy_wrapper_and_sharded_gather_single_rank():
+    from parpy_b200 import dist, hmm as hmm_mod, synthetic
+    hmm, seqs = synthetic.hmm_model(5), synthetic.hmm_sequences(24, 20, 200, seed=4)
+    full = hmm_mod.forward_parpy(hmm_mod.to_device(hmm), hmm_mod.to_device(seqs), 1024).cpu().numpy()
+    parts = []
+    for rank in range(3):
+        local, idx = dist.shard_sequences(seqs, rank, 3)
+        r = hmm_mod.forward_parpy(hmm_mod.to_device(hmm), hmm_mod.to_device(local)).cpu().numpy()
+        parts.append((idx, r))
+    merged = np.empty(24, dtype=np.float32)
+    for idx, r in parts:
+        merged[idx] = r
+    assert np.array_equal(merged, full)
+
+
+def test_reference_cuda_agrees_on_5mer_fixture(native, oracle_mod):
+    # the reference's own CUDA implementation (benchmarks/5mer/hmm.cu built into oracle/_ref)
+    if not oracle_mod.trellis_available(5):
+        pytest.skip("oracle/_ref/trellis_5mer.so has not been built")
+    idx = shortest_reads(6)
+    hmm, seqs, exp = load_model("5mer"), load_signals(idx), load_expected("5mer")[idx]
+    ref = oracle_mod.trellis_forward(5, hmm, seqs)
+    assert np.allclose(ref, exp, atol=1e-5, rtol=1e-5), max_rel(ref, exp)
+    rc, res, _, _ = cabi_forward(native, to_dev(hmm), to_dev(seqs))
+    assert rc == 0 and max_rel(res.cpu().numpy(), ref) <= REL_ORACLE
