@@ -113,6 +113,53 @@ int32_t parpy_b200_forward_plan(int64_t num_states, int64_t num_instances, int32
  * clamped. */
 int32_t parpy_b200_forward_status(uint32_t *status);
 
+/* ---- row-wise softmax ---------------------------------------------------------
+ * out[i,:] = exp(x[i,:] - max_i) / sum(exp(x[i,:] - max_i)) for fp32 x[N,M]
+ * (row-major, contiguous). `softmax` is the entry the reference generates for
+ * test/test_softmax.py:11-26 `softmax(x, N, M, out)`. */
+int32_t softmax(float *x, int64_t N, int64_t M, float *out);
+int32_t parpy_b200_softmax(const float *x, int64_t N, int64_t M, float *out, void *stream);
+
+/* ---- reductions -------------------------------------------------------------------
+ * out[i] = reduce(x[i, 0:M]) for fp32 x[N,M]; op: 0 sum, 1 prod, 2 max, 3 min
+ * (neutral elements of src/utils/reduce.rs:75-88 for M = 0). Covers the
+ * reference's sum_rows / prod_rows / max_rows / min_rows and *_axis functions
+ * (test/test_reduce.py:12-54) and, with N = 1, the full reductions *_2d
+ * (:56-70). The reference's generated entries take (x, out, N) only, with M
+ * compiled in, so they have no fixed-signature twin here. */
+int32_t parpy_b200_reduce_rows(int32_t op, const float *x, float *out, int64_t N, int64_t M,
+                               void *stream);
+/* Sum and max of one fp32 vector of n >= 1 elements in a single pass. */
+int32_t parpy_b200_sum_max(const float *x, int64_t n, float *out_sum, float *out_max, void *stream);
+
+/* ---- CSR SpMV -------------------------------------------------------------------------
+ * y[row] += sum_i values[i] * x[cols[i]], i in [rows[row], rows[row+1]); int64
+ * row pointers and column indices; y is accumulated into (the caller zeroes it).
+ * `spmv_row` is the entry the reference generates for test/test_spmv.py:12-18
+ * `spmv_row(A, x, y)` with A = {cols, nrows, rows, values} (sorted keys); it
+ * reads the non-zero count back from rows[nrows], which synchronises stream 0. */
+int32_t spmv_row(int64_t *cols, int64_t nrows, int64_t *rows, float *values, float *x, float *y);
+int32_t parpy_b200_spmv(const float *values, const int64_t *rows, const int64_t *cols, int64_t nrows,
+                        int64_t nnz, const float *x, float *y, void *stream);
+
+/* ---- SDDMM -------------------------------------------------------------------------------
+ * D[i] = alpha * dot(A[rows[i], 0:K], B[0:K, cols[i]]) + beta * cvalues[i] for
+ * every non-zero i of the mask; A fp32 [N,K], B fp32 [K,ncols], int64 indices.
+ * parpy_sddmm_decompress_csr: the entry generated for benchmarks/sddmm.py:21-26
+ * (rows_out[i] = row of non-zero i). parpy_b200_sddmm_csr replaces
+ * parpy_sddmm_csr_kernel (benchmarks/sddmm.py:28-41; it also fills rows_out, as
+ * the reference's kernel does), parpy_b200_sddmm_coo replaces
+ * parpy_sddmm_coo_kernel (:63-70). K and ncols are compiled into the
+ * reference's generated entries, hence the explicit-shape signatures. */
+int32_t parpy_sddmm_decompress_csr(int64_t *C_crows, int64_t *C_rows, int64_t N);
+int32_t parpy_b200_sddmm_decompress_csr(const int64_t *crows, int64_t *rows_out, int64_t N, void *stream);
+int32_t parpy_b200_sddmm_csr(const float *A, const float *B, const int64_t *crows, int64_t *rows_out,
+                             const int64_t *cols, const float *cvalues, float *D, int64_t N, int64_t K,
+                             int64_t ncols, int64_t nnz, double alpha, double beta, void *stream);
+int32_t parpy_b200_sddmm_coo(const float *A, const float *B, const int64_t *rows, const int64_t *cols,
+                             const float *cvalues, float *D, int64_t K, int64_t ncols, int64_t nnz,
+                             double alpha, double beta, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -146,3 +146,65 @@ def trellis_forward(k, hmm, seqs):
     res = np.ctypeslib.as_array(res_ptr, shape=(batch,)).copy()
     ctypes.CDLL(None).free(res_ptr)
     return res
+
+
+# ---- surrounding kernels ------------------------------------------------------------
+def _f32(a):
+    return _np(a, np.float32)
+
+
+def softmax(x):
+    """test/test_softmax.py:11-26 on a host array [N, M]."""
+    x = _f32(x)
+    out = np.empty_like(x)
+    fn = lib().oracle_softmax
+    fn.restype = None
+    fn.argtypes = [_P, ctypes.c_int64, ctypes.c_int64, _P]
+    fn(x.ctypes.data, x.shape[0], x.shape[1], out.ctypes.data)
+    return out
+
+
+def reduce_rows(op, x):
+    """test/test_reduce.py:12-54; op in {'sum','prod','max','min'}."""
+    x = _f32(x)
+    out = np.empty(x.shape[0], dtype=np.float32)
+    fn = lib().oracle_reduce_rows
+    fn.restype = None
+    fn.argtypes = [ctypes.c_int32, _P, _P, ctypes.c_int64, ctypes.c_int64]
+    fn({"sum": 0, "prod": 1, "max": 2, "min": 3}[op], x.ctypes.data, out.ctypes.data, x.shape[0], x.shape[1])
+    return out
+
+
+def spmv(A, x, y):
+    """test/test_spmv.py:12-18; returns y + A @ x for the CSR dict A."""
+    values, rows, cols = _f32(A["values"]), _np(A["rows"], np.int64), _np(A["cols"], np.int64)
+    x, y = _f32(x), _f32(y).copy()
+    fn = lib().oracle_spmv
+    fn.restype = None
+    fn.argtypes = [_P, _P, _P, ctypes.c_int64, _P, _P]
+    fn(values.ctypes.data, rows.ctypes.data, cols.ctypes.data, len(rows) - 1, x.ctypes.data, y.ctypes.data)
+    return y
+
+
+def sddmm_decompress(crows):
+    crows = _np(crows, np.int64)
+    rows = np.empty(int(crows[-1]), dtype=np.int64)
+    fn = lib().oracle_sddmm_decompress
+    fn.restype = None
+    fn.argtypes = [_P, _P, ctypes.c_int64]
+    fn(crows.ctypes.data, rows.ctypes.data, len(crows) - 1)
+    return rows
+
+
+def sddmm(A, B, rows, cols, cvalues, alpha, beta):
+    """benchmarks/sddmm.py:33-41: D[i] = alpha * A[rows[i],:] . B[:,cols[i]] + beta * C[i]."""
+    A, B, cvalues = _f32(A), _f32(B), _f32(cvalues)
+    rows, cols = _np(rows, np.int64), _np(cols, np.int64)
+    D = np.empty(len(cols), dtype=np.float32)
+    fn = lib().oracle_sddmm
+    fn.restype = None
+    fn.argtypes = [_P, _P, _P, _P, _P, _P, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                   ctypes.c_double, ctypes.c_double]
+    fn(A.ctypes.data, B.ctypes.data, rows.ctypes.data, cols.ctypes.data, cvalues.ctypes.data,
+       D.ctypes.data, A.shape[1], B.shape[1], len(cols), float(alpha), float(beta))
+    return D

@@ -40,7 +40,21 @@ SIGNATURES = {
                                    c_i64, c_i64, c_ptr, c_ptr, c_ptr, c_u32, c_ptr]),
     "parpy_b200_forward_plan": (c_i32, [c_i64, c_i64, c_ptr, c_ptr, c_ptr, c_ptr]),
     "parpy_b200_forward_status": (c_i32, [c_ptr]),
+    "softmax": (c_i32, [c_ptr, c_i64, c_i64, c_ptr]),
+    "parpy_b200_softmax": (c_i32, [c_ptr, c_i64, c_i64, c_ptr, c_ptr]),
+    "parpy_b200_reduce_rows": (c_i32, [c_i32, c_ptr, c_ptr, c_i64, c_i64, c_ptr]),
+    "parpy_b200_sum_max": (c_i32, [c_ptr, c_i64, c_ptr, c_ptr, c_ptr]),
+    "spmv_row": (c_i32, [c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_ptr]),
+    "parpy_b200_spmv": (c_i32, [c_ptr, c_ptr, c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_ptr]),
+    "parpy_sddmm_decompress_csr": (c_i32, [c_ptr, c_ptr, c_i64]),
+    "parpy_b200_sddmm_decompress_csr": (c_i32, [c_ptr, c_ptr, c_i64, c_ptr]),
+    "parpy_b200_sddmm_csr": (c_i32, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_i64,
+                                     c_i64, c_i64, c_f64, c_f64, c_ptr]),
+    "parpy_b200_sddmm_coo": (c_i32, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_i64, c_i64,
+                                     c_f64, c_f64, c_ptr]),
 }
+
+REDUCE_SUM, REDUCE_PROD, REDUCE_MAX, REDUCE_MIN = 0, 1, 2, 3
 
 FWD_AUTO = 0
 FWD_STREAMING = 1

@@ -52,11 +52,22 @@ struct DeviceInfo {
 };
 int32_t device_info(DeviceInfo *out);
 
-// Grow-only device workspace owned by the library (one per device). Used for
-// small scheduling scratch; never for caller data.
-int32_t workspace(size_t bytes, void **ptr);
+// Grow-only device scratch owned by the library, one block per (device, stream,
+// kind). Used for scheduling scratch and reduction partials; never for caller
+// data. `zeroed_workspace` returns a block whose first `zero_bytes` are cleared
+// (stream-ordered) before the caller's kernel runs.
+int32_t workspace(size_t bytes, void **ptr, cudaStream_t stream = nullptr, int kind = 0);
+int32_t zeroed_workspace(size_t zero_bytes, size_t extra_bytes, void **ptr, cudaStream_t stream);
 
-inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+#ifdef __CUDACC__
+#define PB_HD __host__ __device__
+#else
+#define PB_HD
+#endif
+PB_HD inline long long ll_min(long long a, long long b) { return a < b ? a : b; }
+PB_HD inline long long ll_max(long long a, long long b) { return a > b ? a : b; }
+
+PB_HD inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // ---- device helpers -------------------------------------------------------
 #ifdef __CUDACC__

@@ -602,7 +602,7 @@ int32_t forward_impl(float gamma, const float *initial_prob, int64_t num_states,
         // scratch: order[B] + counter, from the library workspace
         void *ws = nullptr;
         const size_t order_bytes = (size_t(p.B) * sizeof(int) + 255) & ~size_t(255);
-        rc = pb::workspace(order_bytes + 512, &ws);
+        rc = pb::workspace(order_bytes + 512, &ws, stream, 0);
         if (rc) return rc;
         int *order = static_cast<int *>(ws);
         int *counter = reinterpret_cast<int *>(static_cast<char *>(ws) + order_bytes);

@@ -3,6 +3,7 @@
 // from its per-backend runtime library (python/parpy/runtime.py:11-26,
 // python/parpy/native/parpy_cuda.cpp:3-39), plus the library-wide error text.
 #include <cstdarg>
+#include <map>
 #include <mutex>
 
 #include "../../include/parpy_b200.h"
@@ -30,8 +31,6 @@ int32_t cuda_fail(cudaError_t err, const char *what) {
 static std::mutex g_mu;
 static constexpr int kMaxDevices = 64;
 static DeviceInfo g_info[kMaxDevices];
-static void *g_ws[kMaxDevices];
-static size_t g_ws_bytes[kMaxDevices];
 
 int32_t device_info(DeviceInfo *out) {
     int dev = 0;
@@ -55,27 +54,49 @@ int32_t device_info(DeviceInfo *out) {
     return PB_OK;
 }
 
-int32_t workspace(size_t bytes, void **ptr) {
+// Scratch blocks are keyed by (device, stream, kind) so that calls queued on
+// different streams never share one. Blocks only grow and live until exit.
+struct WsKey {
+    int dev;
+    cudaStream_t stream;
+    int kind;
+    bool operator<(const WsKey &o) const {
+        if (dev != o.dev) return dev < o.dev;
+        if (stream != o.stream) return stream < o.stream;
+        return kind < o.kind;
+    }
+};
+struct WsBlock {
+    void *ptr = nullptr;
+    size_t bytes = 0;
+};
+static std::map<WsKey, WsBlock> g_ws;
+
+int32_t workspace(size_t bytes, void **ptr, cudaStream_t stream, int kind) {
     int dev = 0;
     PB_CUDA(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= kMaxDevices) {
-        set_error("device ordinal %d out of range", dev);
-        return PB_ERR_ARGUMENT;
-    }
     std::lock_guard<std::mutex> lk(g_mu);
-    if (g_ws_bytes[dev] < bytes) {
-        // Work already queued against the old block must finish before it goes.
-        if (g_ws[dev]) {
-            PB_CUDA(cudaDeviceSynchronize());
-            PB_CUDA(cudaFree(g_ws[dev]));
-            g_ws[dev] = nullptr;
-            g_ws_bytes[dev] = 0;
+    WsBlock &b = g_ws[WsKey{dev, stream, kind}];
+    if (b.bytes < bytes) {
+        if (b.ptr) {
+            // work already queued on this stream may still use the old block
+            PB_CUDA(cudaStreamSynchronize(stream));
+            PB_CUDA(cudaFree(b.ptr));
+            b.ptr = nullptr;
+            b.bytes = 0;
         }
-        size_t want = bytes < (size_t(1) << 20) ? (size_t(1) << 20) : bytes;
-        PB_CUDA(cudaMalloc(&g_ws[dev], want));
-        g_ws_bytes[dev] = want;
+        const size_t want = bytes < (size_t(1) << 20) ? (size_t(1) << 20) : bytes;
+        PB_CUDA(cudaMalloc(&b.ptr, want));
+        b.bytes = want;
     }
-    *ptr = g_ws[dev];
+    *ptr = b.ptr;
+    return PB_OK;
+}
+
+int32_t zeroed_workspace(size_t zero_bytes, size_t extra_bytes, void **ptr, cudaStream_t stream) {
+    int32_t rc = workspace(zero_bytes + extra_bytes, ptr, stream, 1);
+    if (rc) return rc;
+    PB_CUDA(cudaMemsetAsync(*ptr, 0, zero_bytes, stream));
     return PB_OK;
 }
 

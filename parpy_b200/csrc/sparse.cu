@@ -1,0 +1,280 @@
+// CSR SpMV and SDDMM for sm_100a. Both are FFMA kernels bound by memory
+// traffic; neither is a dense contraction worth tensor cores.
+//
+// SpMV (test/test_spmv.py:12-18): y[row] += sum_i values[i] * x[cols[i]] over
+// the row's non-zeros, int64 row pointers and column indices as torch CSR
+// tensors carry them. The reference maps one 128-thread CTA to every row,
+// whatever its length. Here the non-zeros are cut into equal chunks, one CTA per
+// chunk: values and column indices stream in fully coalesced, the products go to
+// shared memory, and a segmented reduction hands them to their rows (one thread
+// per short row, one warp per long row). Work per CTA is the same whatever the
+// row-length distribution, which is what a power-law matrix needs.
+//
+// SDDMM (benchmarks/sddmm.py:21-41,63-70): D[i] = alpha * dot(A[row_i,:],
+// B[:,col_i]) + beta * Cvalues[i]. The reference reads B[:,col] with a stride of
+// ncols floats per element (one 32-byte sector per 4 useful bytes). Here B is
+// transposed once per call into library scratch so that both operands of every
+// dot product are contiguous; half a warp serves one non-zero with 128-bit loads.
+#include <algorithm>
+
+#include "../../include/parpy_b200.h"
+#include "common.cuh"
+
+namespace {
+
+// ------------------------------------------------------------------- SpMV ----
+constexpr int kSpmvThreads = 256;
+constexpr int kSpmvPerThread = 8;
+constexpr int kSpmvChunk = kSpmvThreads * kSpmvPerThread;  // non-zeros per CTA
+constexpr int kLongRow = 64;                                // segments above this get a warp
+constexpr int kMaxLong = kSpmvChunk / kLongRow;
+
+// Largest r in [0, nrows] with rows[r] <= target, found by one warp with a
+// 32-way search (rows is non-decreasing, rows[0] = 0 <= target).
+__device__ long long warp_find_row(const int64_t *__restrict__ rows, long long nrows, long long target) {
+    const int lane = threadIdx.x & 31;
+    long long a = 0, b = nrows + 1;  // answer in [a, b)
+    while (b - a > 1) {
+        const long long step = (b - a + 31) / 32;
+        const long long p = a + lane * step;
+        const bool ok = p < b && __ldg(rows + p) <= target;
+        const unsigned mask = __ballot_sync(0xffffffffu, ok);
+        const int cnt = __popc(mask);  // lanes 0..cnt-1 are true (monotone); cnt >= 1
+        const long long na = a + (long long)(cnt - 1) * step;
+        const long long nb = pb::ll_min(b, a + (long long)cnt * step);
+        a = na;
+        b = nb;
+    }
+    return a;
+}
+
+__global__ void __launch_bounds__(kSpmvThreads) spmv_chunks(const float *__restrict__ values,
+                                                            const int64_t *__restrict__ cols,
+                                                            const int64_t *__restrict__ rows,
+                                                            long long nrows, long long nnz,
+                                                            const float *__restrict__ x,
+                                                            float *__restrict__ y) {
+    __shared__ float s_prod[kSpmvChunk];
+    __shared__ long long s_first_row;
+    __shared__ int s_nlong;
+    __shared__ long long s_long_row[kMaxLong];
+    __shared__ int s_long_a[kMaxLong], s_long_b[kMaxLong];
+    const int tid = threadIdx.x;
+    const long long lo = (long long)blockIdx.x * kSpmvChunk;
+    const long long hi = pb::ll_min(nnz, lo + kSpmvChunk);
+    if (tid == 0) s_nlong = 0;
+
+    // stream this chunk's non-zeros: loads first, then the gathers, then smem
+    float v[kSpmvPerThread];
+    long long c[kSpmvPerThread];
+#pragma unroll
+    for (int i = 0; i < kSpmvPerThread; ++i) {
+        const long long idx = lo + i * kSpmvThreads + tid;
+        if (idx < hi) {
+            v[i] = __ldcs(values + idx);
+            c[i] = __ldcs(cols + idx);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < kSpmvPerThread; ++i) {
+        const long long idx = lo + i * kSpmvThreads + tid;
+        if (idx < hi) s_prod[i * kSpmvThreads + tid] = v[i] * __ldg(x + c[i]);
+    }
+    if (tid < 32) {
+        const long long r = warp_find_row(rows, nrows, lo);
+        if (tid == 0) s_first_row = r;
+    }
+    __syncthreads();
+
+    // rows that own a piece of this chunk: one thread per row
+    for (long long r = s_first_row + tid; r < nrows; r += kSpmvThreads) {
+        const long long start = __ldg(rows + r);
+        if (start >= hi) break;
+        const long long end = __ldg(rows + r + 1);
+        const long long a = pb::ll_max(start, lo), b = pb::ll_min(end, hi);
+        if (b <= a) continue;
+        const int ia = (int)(a - lo), ib = (int)(b - lo);
+        if (ib - ia > kLongRow) {
+            const int slot = atomicAdd(&s_nlong, 1);
+            s_long_row[slot] = r;
+            s_long_a[slot] = ia;
+            s_long_b[slot] = ib;
+            continue;
+        }
+        float sum = 0.0f;
+        for (int j = ia; j < ib; ++j) sum += s_prod[j];
+        if (start >= lo && end <= hi) y[r] = y[r] + sum;   // the row lies inside this chunk
+        else atomicAdd(y + r, sum);                        // shared with a neighbouring chunk
+    }
+    __syncthreads();
+    const int nlong = s_nlong;
+    const int lane = tid & 31, warp = tid >> 5;
+    for (int k = warp; k < nlong; k += kSpmvThreads / 32) {
+        const int ia = s_long_a[k], ib = s_long_b[k];
+        float sum = 0.0f;
+        for (int j = ia + lane; j < ib; j += 32) sum += s_prod[j];
+        sum = pb::warp_sum(sum);
+        if (lane == 0) {
+            const long long r = s_long_row[k];
+            const long long start = __ldg(rows + r), end = __ldg(rows + r + 1);
+            if (start >= lo && end <= hi) y[r] = y[r] + sum;
+            else atomicAdd(y + r, sum);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ SDDMM ----
+// rows[i] = row for every non-zero of a CSR matrix (benchmarks/sddmm.py:21-26).
+__global__ void sddmm_decompress(const int64_t *__restrict__ crows, int64_t *__restrict__ rows, long long N) {
+    const int lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= N) return;
+    const long long a = __ldg(crows + row), b = __ldg(crows + row + 1);
+    for (long long i = a + lane; i < b; i += 32) rows[i] = row;
+}
+
+// Bt[c, k] = B[k, c]
+__global__ void transpose_b(const float *__restrict__ B, float *__restrict__ Bt, long long K, long long ncols) {
+    __shared__ float tile[32][33];
+    const long long c0 = (long long)blockIdx.x * 32, k0 = (long long)blockIdx.y * 32;
+    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+        const long long k = k0 + j, c = c0 + threadIdx.x;
+        if (k < K && c < ncols) tile[j][threadIdx.x] = B[k * ncols + c];
+    }
+    __syncthreads();
+    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+        const long long c = c0 + j, k = k0 + threadIdx.x;
+        if (k < K && c < ncols) Bt[c * K + k] = tile[threadIdx.x][j];
+    }
+}
+
+// Half a warp per non-zero; VEC: 128-bit loads (K % 4 == 0, 16-byte aligned rows).
+template <bool VEC>
+__global__ void __launch_bounds__(256) sddmm_nnz(const float *__restrict__ A, const float *__restrict__ Bt,
+                                                 const int64_t *__restrict__ rows,
+                                                 const int64_t *__restrict__ cols,
+                                                 const float *__restrict__ cvalues, float *__restrict__ D,
+                                                 long long nnz, int K, float alpha, float beta) {
+    // Both halves of a warp run the same number of iterations (the shuffles
+    // below name all 32 lanes); a half without a non-zero idles through them.
+    const int sub = threadIdx.x & 15;
+    const int half = (threadIdx.x >> 4) & 1;
+    const long long warp_first = (((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5) * 2;
+    const long long ngroups = ((long long)gridDim.x * blockDim.x) >> 4;
+    for (long long base = warp_first; base < nnz; base += ngroups) {
+        const long long i = base + half;
+        const bool valid = i < nnz;
+        float acc = 0.0f;
+        if (valid) {
+            const long long row = __ldg(rows + i), col = __ldg(cols + i);
+            const float *a = A + row * K, *b = Bt + col * K;
+            if (VEC) {
+                for (int k = 4 * sub; k < K; k += 64) {
+                    const float4 p = __ldg(reinterpret_cast<const float4 *>(a + k));
+                    const float4 q = __ldg(reinterpret_cast<const float4 *>(b + k));
+                    acc = fmaf(p.x, q.x, acc);
+                    acc = fmaf(p.y, q.y, acc);
+                    acc = fmaf(p.z, q.z, acc);
+                    acc = fmaf(p.w, q.w, acc);
+                }
+            } else {
+                for (int k = sub; k < K; k += 16) acc = fmaf(__ldg(a + k), __ldg(b + k), acc);
+            }
+        }
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o, 16);
+        if (valid && sub == 0) D[i] = alpha * acc + beta * __ldg(cvalues + i);
+    }
+}
+
+int32_t sddmm_common(const float *A, const float *B, const int64_t *rows, const int64_t *cols,
+                     const float *cvalues, float *D, int64_t K, int64_t ncols, int64_t nnz,
+                     double alpha, double beta, cudaStream_t stream) {
+    PB_REQUIRE(K >= 1 && K <= 0x7fffffffLL && ncols >= 1, "sddmm: bad inner size K=%lld or ncols=%lld",
+               (long long)K, (long long)ncols);
+    if (nnz == 0) return PB_OK;
+    PB_REQUIRE(A && B && rows && cols && cvalues && D, "sddmm: null pointer");
+    pb::DeviceInfo dev;
+    int32_t rc = pb::device_info(&dev);
+    if (rc) return rc;
+    void *ws = nullptr;
+    rc = pb::workspace((size_t)K * (size_t)ncols * sizeof(float), &ws, stream, 2);
+    if (rc) return rc;
+    float *Bt = static_cast<float *>(ws);
+    dim3 tgrid((unsigned)((ncols + 31) / 32), (unsigned)((K + 31) / 32), 1);
+    PB_REQUIRE(tgrid.y <= 65535, "sddmm: K=%lld too large", (long long)K);
+    transpose_b<<<tgrid, dim3(32, 8, 1), 0, stream>>>(B, Bt, K, ncols);
+    PB_CUDA(cudaGetLastError());
+    const long long groups_per_block = 256 / 16;
+    long long blocks = std::min<long long>((nnz + groups_per_block - 1) / groups_per_block, 16LL * dev.sm_count);
+    blocks = std::max<long long>(blocks, 1);
+    const bool vec = (K % 4 == 0) && pb::aligned16(A) && pb::aligned16(Bt);
+    if (vec) sddmm_nnz<true><<<(unsigned)blocks, 256, 0, stream>>>(A, Bt, rows, cols, cvalues, D, nnz, (int)K, (float)alpha, (float)beta);
+    else sddmm_nnz<false><<<(unsigned)blocks, 256, 0, stream>>>(A, Bt, rows, cols, cvalues, D, nnz, (int)K, (float)alpha, (float)beta);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t parpy_b200_spmv(const float *values, const int64_t *rows, const int64_t *cols, int64_t nrows,
+                        int64_t nnz, const float *x, float *y, void *stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    PB_REQUIRE(nrows >= 0 && nnz >= 0, "spmv: negative size (nrows=%lld, nnz=%lld)", (long long)nrows, (long long)nnz);
+    if (nrows == 0 || nnz == 0) return PB_OK;
+    PB_REQUIRE(values && rows && cols && x && y, "spmv: null pointer");
+    const long long blocks = (nnz + kSpmvChunk - 1) / kSpmvChunk;
+    PB_REQUIRE(blocks <= 0x7fffffffLL, "spmv: too many non-zeros");
+    spmv_chunks<<<(unsigned)blocks, kSpmvThreads, 0, stream>>>(values, cols, rows, nrows, nnz, x, y);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+int32_t spmv_row(int64_t *cols, int64_t nrows, int64_t *rows, float *values, float *x, float *y) {
+    PB_REQUIRE(nrows >= 0, "spmv_row: negative nrows");
+    if (nrows == 0) return PB_OK;
+    PB_REQUIRE(rows != nullptr, "spmv_row: null row pointer array");
+    // The reference bakes the number of non-zeros into the generated code; here
+    // it is read back from rows[nrows] (one 8-byte copy, synchronises stream 0).
+    int64_t nnz = 0;
+    PB_CUDA(cudaMemcpyAsync(&nnz, rows + nrows, sizeof(nnz), cudaMemcpyDeviceToHost, 0));
+    PB_CUDA(cudaStreamSynchronize(0));
+    return parpy_b200_spmv(values, rows, cols, nrows, nnz, x, y, nullptr);
+}
+
+int32_t parpy_b200_sddmm_decompress_csr(const int64_t *crows, int64_t *rows_out, int64_t N, void *stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    PB_REQUIRE(N >= 0, "sddmm_decompress_csr: negative N");
+    if (N == 0) return PB_OK;
+    PB_REQUIRE(crows && rows_out, "sddmm_decompress_csr: null pointer");
+    const long long blocks = (N + 7) / 8;
+    sddmm_decompress<<<(unsigned)blocks, 256, 0, stream>>>(crows, rows_out, N);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+int32_t parpy_sddmm_decompress_csr(int64_t *C_crows, int64_t *C_rows, int64_t N) {
+    return parpy_b200_sddmm_decompress_csr(C_crows, C_rows, N, nullptr);
+}
+
+int32_t parpy_b200_sddmm_coo(const float *A, const float *B, const int64_t *rows, const int64_t *cols,
+                             const float *cvalues, float *D, int64_t K, int64_t ncols, int64_t nnz,
+                             double alpha, double beta, void *stream_) {
+    PB_REQUIRE(nnz >= 0, "sddmm: negative nnz");
+    return sddmm_common(A, B, rows, cols, cvalues, D, K, ncols, nnz, alpha, beta,
+                        static_cast<cudaStream_t>(stream_));
+}
+
+int32_t parpy_b200_sddmm_csr(const float *A, const float *B, const int64_t *crows, int64_t *rows_out,
+                             const int64_t *cols, const float *cvalues, float *D, int64_t N, int64_t K,
+                             int64_t ncols, int64_t nnz, double alpha, double beta, void *stream_) {
+    PB_REQUIRE(nnz >= 0 && N >= 0, "sddmm: negative size");
+    int32_t rc = parpy_b200_sddmm_decompress_csr(crows, rows_out, N, stream_);
+    if (rc) return rc;
+    return sddmm_common(A, B, rows_out, cols, cvalues, D, K, ncols, nnz, alpha, beta,
+                        static_cast<cudaStream_t>(stream_));
+}
+
+}  // extern "C"

@@ -24,11 +24,8 @@ def forward_parpy(hmm, seqs, nthreads=None, opts=None, alpha=None):
     [B, num_states] float32 device tensors when the final alpha vectors are
     wanted (``opts.b200['write_alpha']``) or the streaming kernel is forced."""
     import torch
-    from .ops import scalar
-    from .buffer import from_array
     batch = seqs["num_instances"]
-    if not isinstance(batch, int):
-        batch = int(scalar(from_array(batch), "seqs['num_instances']")) if hasattr(batch, "shape") else int(batch)
+    batch = int(batch.item()) if hasattr(batch, "item") else int(batch)
     result = torch.zeros(batch, dtype=torch.float32, device="cuda")
     if opts is None:
         p = {"inst": threads(batch)}

@@ -52,26 +52,32 @@ def resolve(name, params):
 
 
 # ---- argument helpers -------------------------------------------------------
-_scalar_cache = {}
+_scalar_cache = {}   # id(tensor) -> (weakref, version, value)
 
 
 def scalar(v, what):
-    """Python value of an int/float argument or of a 0-d buffer. Device-resident
-    0-d tensors cost one D2H read, cached per (pointer, version)."""
+    """Python value of an int/float argument or of a 0-d buffer. A device-resident
+    0-d tensor costs one D2H read, remembered for as long as that tensor object
+    lives and is not written to (its version counter is unchanged)."""
+    import weakref
     if isinstance(v, (bool, int, float)):
         return v
     if isinstance(v, Buffer):
         if len(v.shape) != 0:
             raise TypeError(f"{what}: expected a scalar, got a buffer of shape {v.shape}")
         t = v.buf
-        key = (t.data_ptr(), getattr(t, "_version", None), t.dtype)
-        if key[1] is not None and key in _scalar_cache:
-            return _scalar_cache[key]
+        version = getattr(t, "_version", None)
+        hit = _scalar_cache.get(id(t))
+        if hit is not None and hit[0]() is t and hit[1] == version and version is not None:
+            return hit[2]
         val = t.item()
-        if key[1] is not None:
+        if version is not None:
             if len(_scalar_cache) > 4096:
                 _scalar_cache.clear()
-            _scalar_cache[key] = val
+            try:
+                _scalar_cache[id(t)] = (weakref.ref(t), version, val)
+            except TypeError:
+                pass
         return val
     raise TypeError(f"{what}: expected an int, float or 0-d array, got {type(v)}")
 
@@ -186,3 +192,131 @@ register(OpSpec(
 
 # Callees of forward_kernel in the benchmark; the native kernel contains them.
 HELPERS.update({"forward_init_inst", "forward_step_inst", "forward_lse_inst"})
+
+
+# ---- softmax (test/test_softmax.py:11-26) ---------------------------------------------
+def _softmax_call(opts, x, N, M, out):
+    import torch
+    xt = tensor(x, "x", torch.float32, 2)
+    ot = tensor(out, "out", torch.float32, 2)
+    n, m = int(scalar(N, "N")), int(scalar(M, "M"))
+    if tuple(xt.shape) != (n, m) or tuple(ot.shape) != (n, m):
+        raise RuntimeError(f"softmax: x {tuple(xt.shape)} / out {tuple(ot.shape)} do not match N={n}, M={m}")
+    _native.check(_native.lib().parpy_b200_softmax(ptr(xt), n, m, ptr(ot), current_stream()), "softmax")
+
+
+register(OpSpec("softmax", ("x", "N", "M", "out"), {"x": "in", "out": "out"}, _softmax_call,
+                doc="test/test_softmax.py:11-26"))
+
+
+# ---- reductions (test/test_reduce.py:12-70) --------------------------------------------
+def _reduce_call(op, full):
+    def call(opts, x, out, N):
+        import torch
+        xt = tensor(x, "x", torch.float32, 2)
+        ot = tensor(out, "out", torch.float32, 1)
+        n = int(scalar(N, "N"))
+        if xt.shape[0] != n or ot.shape[0] < (1 if full else n):
+            raise RuntimeError(f"reduce: x {tuple(xt.shape)} / out {tuple(ot.shape)} do not match N={n}")
+        rows, width = (1, xt.numel()) if full else (n, xt.shape[1])
+        _native.check(_native.lib().parpy_b200_reduce_rows(op, ptr(xt), ptr(ot), rows, width,
+                                                           current_stream()), "reduce")
+    return call
+
+
+for _i, _op in enumerate(("sum", "prod", "max", "min")):
+    for _suffix in ("rows", "axis"):
+        register(OpSpec(f"{_op}_{_suffix}", ("x", "out", "N"), {"x": "in", "out": "out"},
+                        _reduce_call(_i, False), doc="test/test_reduce.py:12-54"))
+    # the full reductions write out[0] only; the rest of `out` keeps the caller's values
+    register(OpSpec(f"{_op}_2d", ("x", "out", "N"), {"x": "in", "out": "inout"},
+                    _reduce_call(_i, True), doc="test/test_reduce.py:56-70"))
+
+
+# ---- CSR SpMV (test/test_spmv.py:12-18) ---------------------------------------------------
+def _spmv_call(opts, A, x, y):
+    import torch
+    i64 = torch.int64
+    values = tensor(A["values"], "A['values']", torch.float32, 1)
+    rows = tensor(A["rows"], "A['rows']", i64, 1)
+    cols = tensor(A["cols"], "A['cols']", i64, 1)
+    nrows = int(scalar(A["nrows"], "A['nrows']"))
+    xt = tensor(x, "x", torch.float32, 1)
+    yt = tensor(y, "y", torch.float32, 1)
+    if rows.shape[0] != nrows + 1 or yt.shape[0] != nrows or cols.shape[0] != values.shape[0]:
+        raise RuntimeError(f"spmv_row: rows {tuple(rows.shape)}, cols {tuple(cols.shape)}, values "
+                           f"{tuple(values.shape)}, y {tuple(yt.shape)} do not match nrows={nrows}")
+    _native.check(_native.lib().parpy_b200_spmv(ptr(values), ptr(rows), ptr(cols), nrows,
+                                                values.shape[0], ptr(xt), ptr(yt), current_stream()),
+                  "spmv_row")
+
+
+register(OpSpec("spmv_row", ("A", "x", "y"),
+                {"A": {"values": "in", "rows": "in", "cols": "in", "nrows": "in"}, "x": "in", "y": "inout"},
+                _spmv_call, doc="test/test_spmv.py:12-18"))
+
+
+# ---- SDDMM (benchmarks/sddmm.py:21-41,63-70) -------------------------------------------------
+def _sddmm_decompress_call(opts, C_crows, C_rows, N):
+    import torch
+    crows = tensor(C_crows, "C_crows", torch.int64, 1)
+    rows = tensor(C_rows, "C_rows", torch.int64, 1)
+    n = int(scalar(N, "N"))
+    if crows.shape[0] != n + 1:
+        raise RuntimeError(f"parpy_sddmm_decompress_csr: crows {tuple(crows.shape)} does not match N={n}")
+    _native.check(_native.lib().parpy_b200_sddmm_decompress_csr(ptr(crows), ptr(rows), n, current_stream()),
+                  "parpy_sddmm_decompress_csr")
+
+
+def _sddmm_operands(A, B, C, D):
+    import torch
+    At = tensor(A, "A", torch.float32, 2)
+    Bt = tensor(B, "B", torch.float32, 2)
+    cols = tensor(C["cols"], "C['cols']", torch.int64, 1)
+    vals = tensor(C["values"], "C['values']", torch.float32, 1)
+    Dt = tensor(D, "D", torch.float32, 1)
+    nnz = int(scalar(C["nnz"], "C['nnz']"))
+    if At.shape[1] != Bt.shape[0] or cols.shape[0] != nnz or vals.shape[0] != nnz or Dt.shape[0] != nnz:
+        raise RuntimeError(f"sddmm: A {tuple(At.shape)}, B {tuple(Bt.shape)}, cols {tuple(cols.shape)}, "
+                           f"values {tuple(vals.shape)}, D {tuple(Dt.shape)} do not match nnz={nnz}")
+    return At, Bt, cols, vals, Dt, nnz
+
+
+def _sddmm_csr_call(opts, A, B, C, D, N, alpha, beta):
+    import torch
+    At, Bt, cols, vals, Dt, nnz = _sddmm_operands(A, B, C, D)
+    crows = tensor(C["crows"], "C['crows']", torch.int64, 1)
+    rows = tensor(C["rows"], "C['rows']", torch.int64, 1)
+    n = int(scalar(N, "N"))
+    if crows.shape[0] != n + 1 or rows.shape[0] != nnz or At.shape[0] != n:
+        raise RuntimeError(f"parpy_sddmm_csr_kernel: crows {tuple(crows.shape)} / rows {tuple(rows.shape)} "
+                           f"do not match N={n}, nnz={nnz}")
+    _native.check(_native.lib().parpy_b200_sddmm_csr(
+        ptr(At), ptr(Bt), ptr(crows), ptr(rows), ptr(cols), ptr(vals), ptr(Dt), n, At.shape[1],
+        Bt.shape[1], nnz, float(scalar(alpha, "alpha")), float(scalar(beta, "beta")), current_stream()),
+        "parpy_sddmm_csr_kernel")
+
+
+def _sddmm_coo_call(opts, A, B, C, D, alpha, beta):
+    import torch
+    At, Bt, cols, vals, Dt, nnz = _sddmm_operands(A, B, C, D)
+    rows = tensor(C["rows"], "C['rows']", torch.int64, 1)
+    if rows.shape[0] != nnz:
+        raise RuntimeError(f"parpy_sddmm_coo_kernel: rows {tuple(rows.shape)} does not match nnz={nnz}")
+    _native.check(_native.lib().parpy_b200_sddmm_coo(
+        ptr(At), ptr(Bt), ptr(rows), ptr(cols), ptr(vals), ptr(Dt), At.shape[1], Bt.shape[1], nnz,
+        float(scalar(alpha, "alpha")), float(scalar(beta, "beta")), current_stream()),
+        "parpy_sddmm_coo_kernel")
+
+
+register(OpSpec("parpy_sddmm_decompress_csr", ("C_crows", "C_rows", "N"),
+                {"C_crows": "in", "C_rows": "out"}, _sddmm_decompress_call,
+                doc="benchmarks/sddmm.py:21-26"))
+register(OpSpec("parpy_sddmm_csr_kernel", ("A", "B", "C", "D", "N", "alpha", "beta"),
+                {"A": "in", "B": "in", "D": "out",
+                 "C": {"crows": "in", "rows": "out", "cols": "in", "values": "in", "nnz": "in"}},
+                _sddmm_csr_call, doc="benchmarks/sddmm.py:28-41"))
+register(OpSpec("parpy_sddmm_coo_kernel", ("A", "B", "C", "D", "alpha", "beta"),
+                {"A": "in", "B": "in", "D": "out",
+                 "C": {"rows": "in", "cols": "in", "values": "in", "nnz": "in"}},
+                _sddmm_coo_call, doc="benchmarks/sddmm.py:63-70"))

@@ -47,9 +47,16 @@ def shortest_reads(n):
 
 
 def max_rel(a, b):
+    """Largest relative error; entries where both sides hold the same infinity
+    count as exact, a one-sided infinity or any NaN as infinite error."""
     a = np.asarray(a, dtype=np.float64)
     b = np.asarray(b, dtype=np.float64)
-    return float(np.max(np.abs(a - b) / np.maximum(np.abs(b), 1e-30)))
+    same_inf = np.isinf(a) & np.isinf(b) & (np.sign(a) == np.sign(b))
+    with np.errstate(invalid="ignore"):
+        err = np.abs(a - b) / np.maximum(np.abs(b), 1e-30)
+    err = np.where(same_inf, 0.0, err)
+    err = np.where(np.isnan(err), np.inf, err)
+    return float(np.max(err)) if err.size else 0.0
 
 
 @pytest.fixture(scope="session")

@@ -1,0 +1,237 @@
+"""Parity of the softmax / reduction / SpMV / SDDMM kernels with the CPU oracle
+and with the references the reference's own tests use, through the Python call
+surface (host and device arrays) and through the C ABI. Tolerance: max relative
+error <= 1e-4 for fp32 values (plus the reference tests' own atol where they
+state one); integer outputs are compared bit for bit."""
+import ctypes
+import warnings
+
+import numpy as np
+import pytest
+import torch
+
+import parpy_b200 as parpy
+from conftest import max_rel
+from parpy_b200 import kernels, synthetic
+
+pytestmark = pytest.mark.gpu
+P = ctypes.c_void_p
+
+
+@pytest.fixture(scope="module")
+def oracle_mod():
+    from oracle import oracle
+    return oracle
+
+
+def opts(**labels):
+    return parpy.par({k: v for k, v in labels.items()})
+
+
+# ---- softmax ---------------------------------------------------------------------------------
+def test_softmax_like_reference_test():
+    # test/test_softmax.py:28-40,48-54: host tensors, N:256 M:128 threads
+    torch.manual_seed(1234)
+    N, M = 256, 512
+    x = torch.randn((N, M), dtype=torch.float32)
+    out = torch.zeros_like(x)
+    kernels.softmax(x, N, M, out, opts=opts(N=parpy.threads(256), M=parpy.threads(128)))
+    assert torch.allclose(torch.softmax(x, 1), out, atol=1e-5)
+
+
+@pytest.mark.parametrize("shape", [(256, 1024), (3, 4), (5, 1), (7, 1023), (33, 2048), (9, 2052),
+                                   (4, 5000), (3, 49152), (2, 70001), (1, 8), (1000, 36)])
+def test_softmax_shapes_against_oracle(native, oracle_mod, shape):
+    g = torch.Generator().manual_seed(1234)
+    x = torch.randn(shape, generator=g, dtype=torch.float32)
+    xd = x.cuda()
+    out = torch.empty_like(xd)
+    rc = native.lib().parpy_b200_softmax(P(xd.data_ptr()), shape[0], shape[1], P(out.data_ptr()),
+                                         P(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0, native.error_message()
+    exp = oracle_mod.softmax(x)
+    got = out.cpu().numpy()
+    assert max_rel(got, exp) <= 1e-4
+    assert np.allclose(got.sum(axis=1), 1.0, atol=1e-5)
+
+
+def test_softmax_reference_shaped_entry_and_extremes(native):
+    x = torch.tensor([[1e4, 1e4 - 1, -1e4, 0.0], [-3e38, -3e38, -3e38, -3e38]], device="cuda")
+    out = torch.empty_like(x)
+    rc = native.lib().softmax(P(x.data_ptr()), 2, 4, P(out.data_ptr()))
+    torch.cuda.synchronize()
+    assert rc == 0
+    assert torch.allclose(out.cpu(), torch.softmax(x.cpu(), 1), atol=1e-6)
+    rc = native.lib().softmax(None, 2, 4, P(out.data_ptr()))
+    assert rc != 0 and "null" in native.error_message()
+
+
+# ---- reductions ------------------------------------------------------------------------------------
+NP_OPS = {"sum": np.sum, "prod": np.prod, "max": np.max, "min": np.min}
+
+
+@pytest.mark.parametrize("op", ["sum", "prod", "max", "min"])
+@pytest.mark.parametrize("kind", ["rows", "axis", "2d"])
+def test_reduce_like_reference_test(op, kind):
+    # test/test_reduce.py:72-85,103-126: NumPy host arrays, N=100, M=50, atol 1e-4
+    np.random.seed(1234)
+    N, M = 100, 50
+    x = np.random.randn(N, M).astype(np.float32)
+    out = np.zeros(N, dtype=np.float32)
+    fn = getattr(kernels, f"{op}_{kind}")
+    fn(x, out, N, opts=opts(outer=parpy.threads(N), inner=parpy.threads(128)))
+    if kind == "2d":
+        expected = np.zeros(N, dtype=np.float32)
+        expected[0] = NP_OPS[op](x)
+    else:
+        expected = NP_OPS[op](x, axis=1)
+    assert np.allclose(expected, out, atol=1e-4), f"{expected}\n{out}"
+
+
+@pytest.mark.parametrize("shape", [(1, 1), (3, 5), (64, 1024), (2000, 300), (8, 100003), (3, 1 << 20),
+                                   (1, (1 << 22) + 3), (5, 0)])
+@pytest.mark.parametrize("op", [0, 2, 3])
+def test_reduce_shapes_against_oracle(native, oracle_mod, shape, op):
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(shape, generator=g, dtype=torch.float32)
+    xd = x.cuda()
+    out = torch.full((shape[0],), 123.0, device="cuda")
+    for _ in range(2):          # twice: the scratch tickets must be left reusable
+        rc = native.lib().parpy_b200_reduce_rows(op, P(xd.data_ptr()), P(out.data_ptr()), shape[0], shape[1],
+                                                 P(torch.cuda.current_stream().cuda_stream))
+        assert rc == 0, native.error_message()
+    exp = oracle_mod.reduce_rows(["sum", "prod", "max", "min"][op], x.numpy())
+    got = out.cpu().numpy()
+    if op == 0:
+        # sums of N(0,1) values: compare against the double-precision oracle relative to sqrt(M)
+        assert np.all(np.abs(got - exp) <= 1e-4 * max(1.0, np.sqrt(shape[1])))
+    else:
+        assert np.array_equal(got, exp)
+
+
+def test_prod_rows_against_oracle(native, oracle_mod):
+    g = torch.Generator().manual_seed(3)
+    x = (1.0 + 0.01 * torch.randn((37, 4099), generator=g)).float()
+    out = torch.empty(37, device="cuda")
+    xd = x.cuda()
+    rc = native.lib().parpy_b200_reduce_rows(1, P(xd.data_ptr()), P(out.data_ptr()), 37, 4099, None)
+    torch.cuda.synchronize()
+    assert rc == 0 and max_rel(out.cpu().numpy(), oracle_mod.reduce_rows("prod", x.numpy())) <= 1e-4
+
+
+def test_fused_sum_max():
+    g = torch.Generator().manual_seed(11)
+    for n in (1, 5, 1 << 20, (1 << 24) + 5):
+        x = torch.randn(n, generator=g, dtype=torch.float32).cuda()
+        r1 = kernels.sum_max(x).cpu().numpy()
+        r2 = kernels.sum_max(x).cpu().numpy()
+        assert np.array_equal(r1, r2)                      # deterministic
+        assert r1[1] == float(x.max())
+        assert abs(r1[0] - float(x.double().sum())) <= 1e-4 * max(1.0, np.sqrt(n))
+
+
+# ---- SpMV -----------------------------------------------------------------------------------------------
+def uniform_random_csr_f32_i64(N, M, d):
+    # test/test_spmv.py:31-44
+    nnz = int(N * M * d)
+    s = set()
+    while len(s) < nnz:
+        s.update(np.random.randint(0, N * M, nnz - len(s)))
+    flat = np.array(list(s), dtype=np.int64)
+    rows, cols = np.divmod(flat, M)
+    values = torch.randn(nnz, dtype=torch.float32)
+    A = torch.sparse_coo_tensor(np.array((rows, cols)), values)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        return A.to_sparse_csr()
+
+
+def test_spmv_like_reference_test():
+    # test/test_spmv.py:20-29,46-53,62-71: host tensors, compare with torch CSR matmul, atol 1e-5
+    torch.manual_seed(1234)
+    np.random.seed(1234)
+    N, M = 256, 4096
+    A = uniform_random_csr_f32_i64(N, M, 0.01)
+    x = torch.randn(M, dtype=torch.float32)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        y1 = A.matmul(x)
+        Ad = {"values": A.values(), "rows": A.crow_indices(), "cols": A.col_indices(), "nrows": N}
+    y2 = torch.zeros((N,), dtype=x.dtype)
+    kernels.spmv_row(Ad, x, y2, opts=opts(row=parpy.threads(N), i=parpy.threads(128).reduce()))
+    assert torch.allclose(y1, y2, atol=1e-5)
+
+
+@pytest.mark.parametrize("nrows,ncols,mean,cap", [(1, 10, 3, 8), (5000, 5000, 2, 16), (20000, 30000, 32, 4096),
+                                                   (300, 1000, 900, 4096), (100000, 100000, 8, 64)])
+def test_spmv_power_law_against_oracle(native, oracle_mod, nrows, ncols, mean, cap):
+    A = synthetic.zipf_csr(nrows, ncols, mean_nnz=mean, cap=min(cap, ncols), seed=nrows)
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(ncols, generator=g)
+    y0 = torch.randn(nrows, generator=g)          # y is accumulated into
+    exp = oracle_mod.spmv(A, x, y0.numpy())
+    d = {k: v.cuda() for k, v in A.items() if isinstance(v, torch.Tensor)}
+    xd, yd = x.cuda(), y0.cuda()
+    rc = native.lib().parpy_b200_spmv(P(d["values"].data_ptr()), P(d["rows"].data_ptr()), P(d["cols"].data_ptr()),
+                                      nrows, d["values"].numel(), P(xd.data_ptr()), P(yd.data_ptr()),
+                                      P(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0, native.error_message()
+    got = yd.cpu().numpy()
+    scale = np.maximum(np.abs(exp), np.sqrt(np.maximum(np.diff(A["rows"].numpy()), 1)))
+    assert np.all(np.abs(got - exp) <= 1e-4 * scale)
+    empty = np.diff(A["rows"].numpy()) == 0
+    assert np.array_equal(got[empty], y0.numpy()[empty])       # empty rows untouched, bit for bit
+
+
+def test_spmv_reference_shaped_entry(native, oracle_mod):
+    A = synthetic.zipf_csr(4000, 4000, mean_nnz=20, cap=500, seed=12)
+    x = torch.randn(4000, generator=torch.Generator().manual_seed(5))
+    d = {k: v.cuda() for k, v in A.items() if isinstance(v, torch.Tensor)}
+    xd, yd = x.cuda(), torch.zeros(4000, device="cuda")
+    torch.cuda.synchronize()
+    rc = native.lib().spmv_row(P(d["cols"].data_ptr()), 4000, P(d["rows"].data_ptr()), P(d["values"].data_ptr()),
+                               P(xd.data_ptr()), P(yd.data_ptr()))
+    torch.cuda.synchronize()
+    assert rc == 0, native.error_message()
+    exp = oracle_mod.spmv(A, x, np.zeros(4000, dtype=np.float32))
+    assert np.allclose(yd.cpu().numpy(), exp, atol=1e-4, rtol=1e-4)
+
+
+# ---- SDDMM ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("alpha,beta", [(1.0, 0.0), (1.5, 2.0)])
+@pytest.mark.parametrize("N,ncols,K,density", [(512, 768, 64, 0.02), (100, 333, 30, 0.05), (64, 64, 1024, 0.1)])
+def test_sddmm_csr_and_coo_against_oracle(oracle_mod, alpha, beta, N, ncols, K, density):
+    # benchmarks/sddmm.py:43-61,72-84 call shapes; validation rule of :86-103 is atol=rtol=1e-5
+    C = synthetic.uniform_csr(N, ncols, density, seed=N + K)
+    g = torch.Generator().manual_seed(42)
+    A, B = torch.randn(N, K, generator=g), torch.randn(K, ncols, generator=g)
+    exp_rows = oracle_mod.sddmm_decompress(C["crows"])
+    exp = oracle_mod.sddmm(A, B, exp_rows, C["cols"], C["values"], alpha, beta)
+    nnz = C["nnz"]
+    # CSR entry, device tensors
+    Cd = {"crows": C["crows"].cuda(), "rows": torch.empty(nnz, dtype=torch.int64, device="cuda"),
+          "cols": C["cols"].cuda(), "values": C["values"].cuda(), "nnz": nnz}
+    D = torch.empty(nnz, device="cuda")
+    p = {"N": parpy.threads(N), "M": parpy.threads(32), "nnz": parpy.threads(nnz)}
+    kernels.parpy_sddmm_csr_kernel(A.cuda(), B.cuda(), Cd, D, N, alpha, beta, opts=parpy.par(p))
+    assert np.array_equal(Cd["rows"].cpu().numpy(), exp_rows)                  # index output: bit exact
+    got = D.cpu().numpy()
+    assert np.all(np.abs(got - exp) <= 1e-5 + 1e-4 * np.abs(exp)), max_rel(got, exp)
+    # COO entry, host arrays
+    Ch = {"rows": exp_rows, "cols": C["cols"].numpy(), "values": C["values"].numpy(), "nnz": nnz}
+    Dh = np.zeros(nnz, dtype=np.float32)
+    kernels.parpy_sddmm_coo_kernel(A.numpy(), B.numpy(), Ch, Dh, alpha, beta, opts=parpy.par({"nnz": parpy.threads(nnz)}))
+    assert np.array_equal(Dh, got)
+
+
+def test_sddmm_decompress_entry(native, oracle_mod):
+    C = synthetic.uniform_csr(1000, 2000, 0.01, seed=4)
+    crows = C["crows"].cuda()
+    rows = torch.full((C["nnz"],), -1, dtype=torch.int64, device="cuda")
+    rc = native.lib().parpy_sddmm_decompress_csr(P(crows.data_ptr()), P(rows.data_ptr()), 1000)
+    torch.cuda.synchronize()
+    assert rc == 0
+    assert np.array_equal(rows.cpu().numpy(), oracle_mod.sddmm_decompress(C["crows"]))
+    rows_h = np.zeros(C["nnz"], dtype=np.int64)
+    kernels.parpy_sddmm_decompress_csr(C["crows"].numpy(), rows_h, 1000, opts=parpy.par({}))
+    assert np.array_equal(rows_h, oracle_mod.sddmm_decompress(C["crows"]))
