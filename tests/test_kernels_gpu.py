@@ -216,7 +216,8 @@ def test_sddmm_csr_and_coo_against_oracle(oracle_mod, alpha, beta, N, ncols, K, 
     kernels.parpy_sddmm_csr_kernel(A.cuda(), B.cuda(), Cd, D, N, alpha, beta, opts=parpy.par(p))
     assert np.array_equal(Cd["rows"].cpu().numpy(), exp_rows)                  # index output: bit exact
     got = D.cpu().numpy()
-    assert np.all(np.abs(got - exp) <= 1e-5 + 1e-4 * np.abs(exp)), max_rel(got, exp)
+    # fp32 dot products of K terms in different summation orders: absolute slack grows with K
+    assert np.all(np.abs(got - exp) <= 1e-5 + 2e-7 * K + 1e-4 * np.abs(exp)), max_rel(got, exp)
     # COO entry, host arrays
     Ch = {"rows": exp_rows, "cols": C["cols"].numpy(), "values": C["values"].numpy(), "nnz": nnz}
     Dh = np.zeros(nnz, dtype=np.float32)
