@@ -113,6 +113,44 @@ int32_t parpy_b200_forward_plan(int64_t num_states, int64_t num_instances, int32
  * clamped. */
 int32_t parpy_b200_forward_status(uint32_t *status);
 
+/* Forward pass for callers that must not trigger a device allocation.
+ * No counterpart in the reference: its generated host stub allocates and frees
+ * its temporaries with cudaMallocAsync on every call.
+ *
+ * Who needs this: code that calls the library from a context where cudaMalloc
+ * is off limits — a stream-ordered pipeline that must not hit the implicit
+ * device synchronisation an allocation can cause, a service whose device memory
+ * is fully budgeted up front and which treats any late allocation as a fault, or
+ * a plugin host that forbids allocation inside its execute callback.
+ * parpy_b200_forward may grow the library's scheduling scratch with cudaMalloc
+ * on its first call or when the batch grows; this entry never does. It computes
+ * the same result[] (resident kernel, factored log-sum-exp, alpha kept on chip)
+ * with its scheduling scratch — the length-sorted sequence order and the work-
+ * queue head — in a fixed device array compiled into the library, of
+ * 4 * PARPY_B200_NOALLOC_MAX_SEQUENCES + 256 bytes on every GPU that loads the
+ * library, held until the process exits.
+ *
+ * Limits and rules:
+ *  - num_instances above PARPY_B200_NOALLOC_MAX_SEQUENCES is rejected with an
+ *    error text that names the limit; so are state spaces that only the
+ *    streaming kernel covers (that kernel needs caller scratch).
+ *  - It calls no cudaMalloc / cudaFree and no allocating library routine; the
+ *    caller passes every input and output, as for parpy_b200_forward.
+ *  - The first call on each device looks up the array's device address (one
+ *    cudaGetSymbolAddress, with that device current). Make that first call
+ *    before any stream capture is begun on the device.
+ *  - All calls on a device share the one array, and it keeps the previous
+ *    call's contents; each call rewrites the part it uses before reading it.
+ *    Two calls whose kernels overlap on the GPU (different streams) race on it:
+ *    serialise them on one stream or with events.
+ */
+#define PARPY_B200_NOALLOC_MAX_SEQUENCES 16384
+int32_t parpy_b200_forward_noalloc(float gamma, const float *initial_prob, int64_t num_states,
+                                   const float *output_prob, float synthetic_248,
+                                   const float *trans1, const float *trans2, const void *data,
+                                   const int64_t *lens, int64_t maxlen, int64_t num_instances,
+                                   float *result, void *stream);
+
 /* ---- row-wise softmax ---------------------------------------------------------
  * out[i,:] = exp(x[i,:] - max_i) / sum(exp(x[i,:] - max_i)) for fp32 x[N,M]
  * (row-major, contiguous). `softmax` is the entry the reference generates for

@@ -38,6 +38,8 @@ SIGNATURES = {
                                              c_ptr, c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_ptr]),
     "parpy_b200_forward": (c_i32, [c_f32, c_ptr, c_i64, c_ptr, c_f32, c_ptr, c_ptr, c_ptr, c_ptr,
                                    c_i64, c_i64, c_ptr, c_ptr, c_ptr, c_u32, c_ptr]),
+    "parpy_b200_forward_noalloc": (c_i32, [c_f32, c_ptr, c_i64, c_ptr, c_f32, c_ptr, c_ptr, c_ptr, c_ptr,
+                                           c_i64, c_i64, c_ptr, c_ptr]),
     "parpy_b200_forward_plan": (c_i32, [c_i64, c_i64, c_ptr, c_ptr, c_ptr, c_ptr]),
     "parpy_b200_forward_status": (c_i32, [c_ptr]),
     "softmax": (c_i32, [c_ptr, c_i64, c_i64, c_ptr]),
@@ -55,6 +57,8 @@ SIGNATURES = {
 }
 
 REDUCE_SUM, REDUCE_PROD, REDUCE_MAX, REDUCE_MIN = 0, 1, 2, 3
+
+NOALLOC_MAX_SEQUENCES = 16384
 
 FWD_AUTO = 0
 FWD_STREAMING = 1

@@ -22,6 +22,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <mutex>
 
 #include "../../include/parpy_b200.h"
 #include "common.cuh"
@@ -43,6 +44,15 @@ __constant__ ModelConsts c_model[kModelSlots];
 
 // Device status word. Bit 0: a sequence length outside [1, maxlen] was clamped.
 __device__ unsigned g_status;
+
+// Fixed scheduling scratch of parpy_b200_forward_noalloc: the sequence order
+// (one int per sequence) followed by the work-queue head. It is part of the
+// loaded module, so every GPU that loads the library holds these bytes until the
+// process exits. In host code this name is only a handle for the symbol, not a
+// device address; host code obtains the address with cudaGetSymbolAddress.
+constexpr int kNoAllocMaxSequences = PARPY_B200_NOALLOC_MAX_SEQUENCES;
+constexpr size_t kNoAllocOrderBytes = size_t(kNoAllocMaxSequences) * sizeof(int);
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocOrderBytes + 256];
 
 struct FwdParams {
     const float *initial_prob;  // [16*K]
@@ -704,3 +714,97 @@ int32_t parpy_b200_forward_status(uint32_t *status) {
 }
 
 }  // extern "C"
+
+// ---- entry point that allocates nothing --------------------------------------------
+namespace {
+
+std::mutex g_noalloc_mu;
+void *g_noalloc_addr[64];  // device address of g_noalloc_scratch, per device ordinal
+
+// Looks up (once per device, with that device current) where the module's copy
+// of g_noalloc_scratch lives on the current device.
+int32_t noalloc_scratch_address(void **out) {
+    int dev = 0;
+    PB_CUDA(cudaGetDevice(&dev));
+    PB_REQUIRE(dev >= 0 && dev < 64, "forward_noalloc: device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    if (g_noalloc_addr[dev] == nullptr) {
+        void *p = nullptr;
+        PB_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+        g_noalloc_addr[dev] = p;
+    }
+    *out = g_noalloc_addr[dev];
+    return PB_OK;
+}
+
+}  // namespace
+
+extern "C" int32_t parpy_b200_forward_noalloc(float gamma, const float *initial_prob,
+                                              int64_t num_states, const float *output_prob,
+                                              float synthetic_248, const float *trans1,
+                                              const float *trans2, const void *data,
+                                              const int64_t *lens, int64_t maxlen,
+                                              int64_t num_instances, float *result, void *stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    PB_REQUIRE(num_states >= 64 && num_states % 64 == 0,
+               "forward_noalloc: num_states=%lld must be a positive multiple of 64", (long long)num_states);
+    PB_REQUIRE(num_instances >= 0, "forward_noalloc: negative num_instances");
+    PB_REQUIRE(num_instances <= kNoAllocMaxSequences,
+               "forward_noalloc: num_instances=%lld exceeds the fixed scratch capacity of %d sequences; "
+               "split the batch or call parpy_b200_forward",
+               (long long)num_instances, kNoAllocMaxSequences);
+    PB_REQUIRE(maxlen >= 1 && maxlen <= 0x7fffffffLL, "forward_noalloc: maxlen=%lld out of range", (long long)maxlen);
+    if (num_instances == 0) return PB_OK;
+    PB_REQUIRE(initial_prob && output_prob && trans1 && trans2 && data && lens && result,
+               "forward_noalloc: null table, observation or result pointer");
+    const long long K = num_states / kLayers;
+    Plan pl;
+    PB_REQUIRE(make_plan(K, &pl),
+               "forward_noalloc: num_states=%lld has no resident mapping (the streaming kernel needs "
+               "caller scratch: use parpy_b200_forward)", (long long)num_states);
+    PB_REQUIRE(pl.kpt == 1 || (pb::aligned16(initial_prob) && pb::aligned16(output_prob) && pb::aligned16(trans1)),
+               "forward_noalloc: tables must be 16-byte aligned");
+    pb::DeviceInfo dev;
+    int32_t rc = pb::device_info(&dev);
+    if (rc) return rc;
+    PB_REQUIRE(dev.cc_major >= 10, "forward_noalloc: needs compute capability 10.x, found %d.%d",
+               dev.cc_major, dev.cc_minor);
+    void *scratch = nullptr;
+    rc = noalloc_scratch_address(&scratch);
+    if (rc) return rc;
+
+    FwdParams p{};
+    p.initial_prob = initial_prob;
+    p.output_prob = output_prob;
+    p.trans1 = trans1;
+    p.data = static_cast<const uint8_t *>(data);
+    p.lens = lens;
+    p.result = result;
+    p.maxlen = maxlen;
+    p.B = static_cast<int>(num_instances);
+    p.K = static_cast<int>(K);
+    p.gamma = gamma;
+    p.synthetic = synthetic_248;
+    p.write_alpha = 0;
+    p.slot = static_cast<int>(g_slot.fetch_add(1) % kModelSlots);
+    p.order = static_cast<int *>(scratch);
+    p.counter = reinterpret_cast<int *>(static_cast<char *>(scratch) + kNoAllocOrderBytes);
+    PB_CUDA(cudaMemcpyToSymbolAsync(c_model, trans2, sizeof(ModelConsts),
+                                    size_t(p.slot) * sizeof(ModelConsts), cudaMemcpyDeviceToDevice, stream));
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[1];
+    int max_clusters = 0;
+    ResidentKernel kern = nullptr;
+    rc = resident_config(pl, false, &cfg, attr, &max_clusters, &kern);
+    if (rc) return rc;
+    // The array keeps whatever the previous call left in it. hmm_schedule rewrites
+    // all num_instances order entries and sets the queue head to zero before the
+    // forward kernel (same stream) reads either, so nothing stale is ever used.
+    const size_t sched_smem = p.B <= kSortLimit ? size_t(p.B) * sizeof(int) : 0;
+    hmm_schedule<<<1, 1024, sched_smem, stream>>>(lens, p.B, const_cast<int *>(p.order), p.counter);
+    PB_CUDA(cudaGetLastError());
+    cfg.gridDim = dim3(pl.cs * std::min(max_clusters, p.B), 1, 1);
+    cfg.stream = stream;
+    PB_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
+    return PB_OK;
+}
