@@ -64,7 +64,13 @@ def report(name, ms, nbytes, extra=None):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--quick", action="store_true", help="smaller SpMV / reduction sizes")
+    ap.add_argument("--profile", action="store_true",
+                    help="one warm-up and one timed launch per kernel (for captures under a profiler)")
     args = ap.parse_args()
+    if args.profile:
+        global timed
+        plain = timed
+        timed = lambda fn, reps=1, warmup=1, flush=None: plain(fn, 1, 1, flush)
     lib = _native.lib()
     stream = lambda: P(torch.cuda.current_stream().cuda_stream)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")

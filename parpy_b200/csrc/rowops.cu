@@ -60,14 +60,15 @@ __global__ void __launch_bounds__(256) softmax_warp_rows(const float *__restrict
         }
     }
     s = pb::warp_sum(s);
+    const float inv = 1.0f / s;
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
         const int idx = lane + 32 * i;
         if (idx < nvec) {
-            v[i].x = v[i].x / s;
-            v[i].y = v[i].y / s;
-            v[i].z = v[i].z / s;
-            v[i].w = v[i].w / s;
+            v[i].x *= inv;
+            v[i].y *= inv;
+            v[i].z *= inv;
+            v[i].w *= inv;
             __stcs(dst + idx, v[i]);
         }
     }
@@ -95,6 +96,55 @@ __device__ __forceinline__ float block_sum(float v, float *s_red) {
     return r;
 }
 
+// One CTA per row, the row held in registers (VEC float4 per thread): a single
+// global read and a single write for rows of up to blockDim * 4 * VEC floats.
+template <int VEC>
+__global__ void __launch_bounds__(1024) softmax_block_regs(const float *__restrict__ x,
+                                                           float *__restrict__ out, long long N, int M) {
+    __shared__ float s_red[32];
+    const int nvec = M >> 2;
+    for (long long row = blockIdx.x; row < N; row += gridDim.x) {
+        const float4 *src = reinterpret_cast<const float4 *>(x + row * M);
+        float4 *dst = reinterpret_cast<float4 *>(out + row * M);
+        float4 v[VEC];
+        float m = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            const int idx = threadIdx.x + blockDim.x * i;
+            if (idx < nvec) {
+                v[i] = __ldcs(src + idx);
+                m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+            }
+        }
+        m = block_max(m, s_red);
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            const int idx = threadIdx.x + blockDim.x * i;
+            if (idx < nvec) {
+                v[i].x = fast_exp(v[i].x - m);
+                v[i].y = fast_exp(v[i].y - m);
+                v[i].z = fast_exp(v[i].z - m);
+                v[i].w = fast_exp(v[i].w - m);
+                s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+            }
+        }
+        s = block_sum(s, s_red);
+        const float inv = 1.0f / s;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            const int idx = threadIdx.x + blockDim.x * i;
+            if (idx < nvec) {
+                v[i].x *= inv;
+                v[i].y *= inv;
+                v[i].z *= inv;
+                v[i].w *= inv;
+                __stcs(dst + idx, v[i]);
+            }
+        }
+    }
+}
+
 // One CTA per row (grid-stride over rows). STAGE: keep the row in dynamic shared
 // memory between the passes; otherwise re-read it from global memory.
 template <bool STAGE>
@@ -120,9 +170,10 @@ __global__ void __launch_bounds__(1024) softmax_block_rows(const float *__restri
             s += e;
         }
         s = block_sum(s, s_red);
+        const float inv = 1.0f / s;
         for (long long i = threadIdx.x; i < M; i += blockDim.x) {
             const float e = STAGE ? s_row[i] : fast_exp(src[i] - m);
-            dst[i] = e / s;
+            dst[i] = e * inv;
         }
         __syncthreads();
     }
@@ -414,6 +465,18 @@ int32_t parpy_b200_softmax(const float *x, int64_t N, int64_t M, float *out, voi
         else if (nvec <= 32 * 4) softmax_warp_rows<4><<<(unsigned)blocks, wpb * 32, 0, stream>>>(x, out, N, (int)M);
         else if (nvec <= 32 * 8) softmax_warp_rows<8><<<(unsigned)blocks, wpb * 32, 0, stream>>>(x, out, N, (int)M);
         else softmax_warp_rows<16><<<(unsigned)blocks, wpb * 32, 0, stream>>>(x, out, N, (int)M);
+        PB_CUDA(cudaGetLastError());
+        return PB_OK;
+    }
+    if (vec_ok && M <= 32768) {
+        // row in registers of one CTA: threads x VEC float4
+        const int nvec = (int)(M / 4);
+        const int threads = nvec <= 2048 ? 256 : nvec <= 4096 ? 512 : 1024;
+        const int per = (nvec + threads - 1) / threads;
+        const long long g = std::min<long long>(N, (long long)dev.sm_count * (2048 / threads) * 2);
+        if (per <= 2) softmax_block_regs<2><<<(unsigned)g, threads, 0, stream>>>(x, out, N, (int)M);
+        else if (per <= 4) softmax_block_regs<4><<<(unsigned)g, threads, 0, stream>>>(x, out, N, (int)M);
+        else softmax_block_regs<8><<<(unsigned)g, threads, 0, stream>>>(x, out, N, (int)M);
         PB_CUDA(cudaGetLastError());
         return PB_OK;
     }

@@ -29,23 +29,19 @@ constexpr int kSpmvChunk = kSpmvThreads * kSpmvPerThread;  // non-zeros per CTA
 constexpr int kLongRow = 64;                                // segments above this get a warp
 constexpr int kMaxLong = kSpmvChunk / kLongRow;
 
-// Largest r in [0, nrows] with rows[r] <= target, found by one warp with a
-// 32-way search (rows is non-decreasing, rows[0] = 0 <= target).
-__device__ long long warp_find_row(const int64_t *__restrict__ rows, long long nrows, long long target) {
-    const int lane = threadIdx.x & 31;
-    long long a = 0, b = nrows + 1;  // answer in [a, b)
-    while (b - a > 1) {
-        const long long step = (b - a + 31) / 32;
-        const long long p = a + lane * step;
-        const bool ok = p < b && __ldg(rows + p) <= target;
-        const unsigned mask = __ballot_sync(0xffffffffu, ok);
-        const int cnt = __popc(mask);  // lanes 0..cnt-1 are true (monotone); cnt >= 1
-        const long long na = a + (long long)(cnt - 1) * step;
-        const long long nb = pb::ll_min(b, a + (long long)cnt * step);
-        a = na;
-        b = nb;
-    }
-    return a;
+// first_row[c] = the row that contains non-zero c * kSpmvChunk, i.e. the largest
+// r with rows[r] <= c * kSpmvChunk. One thread per row writes the entries of the
+// chunk starts that fall inside its row (none for an empty row), so the table is
+// built with one coalesced pass over the row pointers and no search; the pass
+// also leaves the row pointers in L2 for the main kernel.
+__global__ void spmv_first_rows(const int64_t *__restrict__ rows, long long nrows,
+                                int *__restrict__ first_row) {
+    const long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= nrows) return;
+    const long long start = __ldg(rows + r), end = __ldg(rows + r + 1);
+    if (end <= start) return;
+    for (long long c = (start + kSpmvChunk - 1) / kSpmvChunk; c * kSpmvChunk < end; ++c)
+        first_row[c] = (int)r;
 }
 
 __global__ void __launch_bounds__(kSpmvThreads) spmv_chunks(const float *__restrict__ values,
@@ -53,9 +49,9 @@ __global__ void __launch_bounds__(kSpmvThreads) spmv_chunks(const float *__restr
                                                             const int64_t *__restrict__ rows,
                                                             long long nrows, long long nnz,
                                                             const float *__restrict__ x,
-                                                            float *__restrict__ y) {
+                                                            float *__restrict__ y,
+                                                            const int *__restrict__ first_row) {
     __shared__ float s_prod[kSpmvChunk];
-    __shared__ long long s_first_row;
     __shared__ int s_nlong;
     __shared__ long long s_long_row[kMaxLong];
     __shared__ int s_long_a[kMaxLong], s_long_b[kMaxLong];
@@ -75,22 +71,25 @@ __global__ void __launch_bounds__(kSpmvThreads) spmv_chunks(const float *__restr
             c[i] = __ldcs(cols + idx);
         }
     }
+    // the rows this thread will own, fetched while the non-zeros are in flight
+    const long long r0 = (long long)__ldg(first_row + blockIdx.x) + tid;
+    long long start0 = 0, end0 = 0;
+    if (r0 < nrows) {
+        start0 = __ldg(rows + r0);
+        end0 = __ldg(rows + r0 + 1);
+    }
 #pragma unroll
     for (int i = 0; i < kSpmvPerThread; ++i) {
         const long long idx = lo + i * kSpmvThreads + tid;
         if (idx < hi) s_prod[i * kSpmvThreads + tid] = v[i] * __ldg(x + c[i]);
     }
-    if (tid < 32) {
-        const long long r = warp_find_row(rows, nrows, lo);
-        if (tid == 0) s_first_row = r;
-    }
     __syncthreads();
 
     // rows that own a piece of this chunk: one thread per row
-    for (long long r = s_first_row + tid; r < nrows; r += kSpmvThreads) {
-        const long long start = __ldg(rows + r);
+    for (long long r = r0; r < nrows; r += kSpmvThreads) {
+        const long long start = r == r0 ? start0 : __ldg(rows + r);
         if (start >= hi) break;
-        const long long end = __ldg(rows + r + 1);
+        const long long end = r == r0 ? end0 : __ldg(rows + r + 1);
         const long long a = pb::ll_max(start, lo), b = pb::ll_min(end, hi);
         if (b <= a) continue;
         const int ia = (int)(a - lo), ib = (int)(b - lo);
@@ -148,7 +147,11 @@ __global__ void transpose_b(const float *__restrict__ B, float *__restrict__ Bt,
     }
 }
 
-// Half a warp per non-zero; VEC: 128-bit loads (K % 4 == 0, 16-byte aligned rows).
+// Half a warp per group of kSddmmUnroll consecutive non-zeros: all index loads,
+// then all operand loads, then the math, so that several L2 round trips overlap.
+// VEC: 128-bit loads (K % 4 == 0, 16-byte aligned rows).
+constexpr int kSddmmUnroll = 4;
+
 template <bool VEC>
 __global__ void __launch_bounds__(256) sddmm_nnz(const float *__restrict__ A, const float *__restrict__ Bt,
                                                  const int64_t *__restrict__ rows,
@@ -156,34 +159,54 @@ __global__ void __launch_bounds__(256) sddmm_nnz(const float *__restrict__ A, co
                                                  const float *__restrict__ cvalues, float *__restrict__ D,
                                                  long long nnz, int K, float alpha, float beta) {
     // Both halves of a warp run the same number of iterations (the shuffles
-    // below name all 32 lanes); a half without a non-zero idles through them.
+    // below name all 32 lanes); a half without work idles through them.
     const int sub = threadIdx.x & 15;
     const int half = (threadIdx.x >> 4) & 1;
     const long long warp_first = (((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5) * 2;
     const long long ngroups = ((long long)gridDim.x * blockDim.x) >> 4;
-    for (long long base = warp_first; base < nnz; base += ngroups) {
-        const long long i = base + half;
-        const bool valid = i < nnz;
-        float acc = 0.0f;
-        if (valid) {
-            const long long row = __ldg(rows + i), col = __ldg(cols + i);
-            const float *a = A + row * K, *b = Bt + col * K;
-            if (VEC) {
-                for (int k = 4 * sub; k < K; k += 64) {
-                    const float4 p = __ldg(reinterpret_cast<const float4 *>(a + k));
-                    const float4 q = __ldg(reinterpret_cast<const float4 *>(b + k));
-                    acc = fmaf(p.x, q.x, acc);
-                    acc = fmaf(p.y, q.y, acc);
-                    acc = fmaf(p.z, q.z, acc);
-                    acc = fmaf(p.w, q.w, acc);
+    for (long long base = warp_first * kSddmmUnroll; base < nnz; base += ngroups * kSddmmUnroll) {
+        const long long i0 = base + (long long)half * kSddmmUnroll;
+        const float *a[kSddmmUnroll], *b[kSddmmUnroll];
+        float acc[kSddmmUnroll];
+#pragma unroll
+        for (int u = 0; u < kSddmmUnroll; ++u) {
+            const long long i = i0 + u < nnz ? i0 + u : nnz - 1;   // clamp: harmless duplicate work
+            a[u] = A + __ldg(rows + i) * K;
+            b[u] = Bt + __ldg(cols + i) * K;
+            acc[u] = 0.0f;
+        }
+        if (VEC) {
+            for (int k = 4 * sub; k < K; k += 64) {
+                float4 p[kSddmmUnroll], q[kSddmmUnroll];
+#pragma unroll
+                for (int u = 0; u < kSddmmUnroll; ++u) {
+                    p[u] = __ldg(reinterpret_cast<const float4 *>(a[u] + k));
+                    q[u] = __ldg(reinterpret_cast<const float4 *>(b[u] + k));
                 }
-            } else {
-                for (int k = sub; k < K; k += 16) acc = fmaf(__ldg(a + k), __ldg(b + k), acc);
+#pragma unroll
+                for (int u = 0; u < kSddmmUnroll; ++u) {
+                    acc[u] = fmaf(p[u].x, q[u].x, acc[u]);
+                    acc[u] = fmaf(p[u].y, q[u].y, acc[u]);
+                    acc[u] = fmaf(p[u].z, q[u].z, acc[u]);
+                    acc[u] = fmaf(p[u].w, q[u].w, acc[u]);
+                }
+            }
+        } else {
+            for (int k = sub; k < K; k += 16) {
+#pragma unroll
+                for (int u = 0; u < kSddmmUnroll; ++u) acc[u] = fmaf(__ldg(a[u] + k), __ldg(b[u] + k), acc[u]);
             }
         }
 #pragma unroll
-        for (int o = 8; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o, 16);
-        if (valid && sub == 0) D[i] = alpha * acc + beta * __ldg(cvalues + i);
+        for (int u = 0; u < kSddmmUnroll; ++u) {
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], o, 16);
+        }
+        // lane u of the half stores non-zero i0 + u
+#pragma unroll
+        for (int u = 0; u < kSddmmUnroll; ++u) {
+            if (sub == u && i0 + u < nnz) D[i0 + u] = alpha * acc[u] + beta * __ldg(cvalues + i0 + u);
+        }
     }
 }
 
@@ -205,8 +228,8 @@ int32_t sddmm_common(const float *A, const float *B, const int64_t *rows, const 
     PB_REQUIRE(tgrid.y <= 65535, "sddmm: K=%lld too large", (long long)K);
     transpose_b<<<tgrid, dim3(32, 8, 1), 0, stream>>>(B, Bt, K, ncols);
     PB_CUDA(cudaGetLastError());
-    const long long groups_per_block = 256 / 16;
-    long long blocks = std::min<long long>((nnz + groups_per_block - 1) / groups_per_block, 16LL * dev.sm_count);
+    const long long nnz_per_block = (256 / 16) * kSddmmUnroll;
+    long long blocks = std::min<long long>((nnz + nnz_per_block - 1) / nnz_per_block, 16LL * dev.sm_count);
     blocks = std::max<long long>(blocks, 1);
     const bool vec = (K % 4 == 0) && pb::aligned16(A) && pb::aligned16(Bt);
     if (vec) sddmm_nnz<true><<<(unsigned)blocks, 256, 0, stream>>>(A, Bt, rows, cols, cvalues, D, nnz, (int)K, (float)alpha, (float)beta);
@@ -226,8 +249,14 @@ int32_t parpy_b200_spmv(const float *values, const int64_t *rows, const int64_t 
     if (nrows == 0 || nnz == 0) return PB_OK;
     PB_REQUIRE(values && rows && cols && x && y, "spmv: null pointer");
     const long long blocks = (nnz + kSpmvChunk - 1) / kSpmvChunk;
-    PB_REQUIRE(blocks <= 0x7fffffffLL, "spmv: too many non-zeros");
-    spmv_chunks<<<(unsigned)blocks, kSpmvThreads, 0, stream>>>(values, cols, rows, nrows, nnz, x, y);
+    PB_REQUIRE(blocks <= 0x7fffffffLL && nrows <= 0x7fffffffLL, "spmv: matrix too large");
+    void *ws = nullptr;
+    int32_t rc = pb::workspace((size_t)blocks * sizeof(int), &ws, stream, 3);
+    if (rc) return rc;
+    int *first_row = static_cast<int *>(ws);
+    spmv_first_rows<<<(unsigned)((nrows + 255) / 256), 256, 0, stream>>>(rows, nrows, first_row);
+    PB_CUDA(cudaGetLastError());
+    spmv_chunks<<<(unsigned)blocks, kSpmvThreads, 0, stream>>>(values, cols, rows, nrows, nnz, x, y, first_row);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }
