@@ -136,8 +136,13 @@ int oracle_forward(float gamma, const float *initial_prob, int64_t num_states,
         const float *alpha = (len & 1) ? a1 : a2;
         float maxp = -INFINITY;
         for (int64_t s = 0; s < N; ++s) maxp = f32_max(maxp, alpha[s]);
-        float psum = 0.0f;
-        for (int64_t s = 0; s < N; ++s) psum += expf(alpha[s] - maxp);
+        /* parpy.operators.sum is a parallel (tree) reduction on the GPU and a
+         * pairwise sum in NumPy; a sequential float accumulator would instead drop
+         * small terms once it has grown (N reaches 2^20). The float terms are
+         * therefore accumulated in double and rounded once. */
+        double acc = 0.0;
+        for (int64_t s = 0; s < N; ++s) acc += (double)expf(alpha[s] - maxp);
+        const float psum = (float)acc;
         result[inst] = maxp + logf(psum);
         if (alpha_final)
             memcpy(alpha_final + inst * N, alpha, sizeof(float) * (size_t)N);

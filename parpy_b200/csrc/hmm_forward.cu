@@ -128,6 +128,37 @@ __device__ __forceinline__ float lse2(float u, float v) {
     return fmaxf(fmaf(l, kLn2, mx), -INFINITY);
 }
 
+// 2^t for t <= 0 without the MUFU unit: round-to-nearest split t = n + f with
+// the magic-number trick (n integer, f in [-0.5, 0.5]), a degree-5 minimax
+// polynomial for 2^f (max relative error 2.2e-7, on par with ex2.approx), and n
+// added straight into the exponent field. The forward kernels are bound by the
+// MUFU pipe; evaluating a fixed subset of the exponentials on the FMA pipe
+// instead balances the two.
+__device__ __forceinline__ float ex2_poly(float t) {
+    t = fmaxf(t, -126.0f);              // also maps NaN to -126 (result ~0)
+    const float magic = 12582912.0f;    // 1.5 * 2^23
+    const float r = t + magic;
+    const float n = r - magic;
+    const float f = t - n;
+    float p = 0.001327647129073739f;
+    p = fmaf(p, f, 0.009675540961325169f);
+    p = fmaf(p, f, 0.05550713092088699f);
+    p = fmaf(p, f, 0.24022120237350464f);
+    p = fmaf(p, f, 0.6931469440460205f);
+    p = fmaf(p, f, 1.0000001192092896f);
+    return __int_as_float(__float_as_int(p) + (__float_as_int(r) << 23));
+}
+
+// `poly` is a compile-time constant at every call site once the layer loops are
+// unrolled, so the unused branch disappears.
+__device__ __forceinline__ float lse2_sel(bool poly, float u, float v) {
+    const float mx = fmaxf(u, v);
+    const float t = -fabsf(u - v) * kLog2e;
+    const float ex = poly ? ex2_poly(t) : pb::ex2_approx(t);
+    const float l = pb::lg2_approx(1.0f + ex);
+    return fmaxf(fmaf(l, kLn2, mx), -INFINITY);
+}
+
 __device__ __forceinline__ float lse4(float p0, float p1, float p2, float p3) {
     const float m = fmaxf(fmaxf(p0, p1), fmaxf(p2, p3));
     const float s = fast_exp(p0 - m) + fast_exp(p1 - m) + fast_exp(p2 - m) + fast_exp(p3 - m);
@@ -409,6 +440,209 @@ hmm_forward_resident(const FwdParams p) {
     }
 }
 
+
+// ---- resident kernel, register/shared split ----------------------------------------
+// Same algorithm and arithmetic as hmm_forward_resident<4,false>, laid out for
+// twice the k-mers per SM: 1024 threads x 4 k-mers per CTA, duration layers 0..7
+// in registers, layers 8..15 and the transition columns in shared memory (each
+// thread only ever touches its own float4 slots, so no extra synchronisation).
+// A 7-mer sequence then needs a cluster of 4 CTAs instead of 8, and clusters of 4
+// pack the GPCs without leaving SMs idle.
+constexpr int kRegLayers = 8;
+
+template <unsigned POLY_MASK>   // bit d set: layer d evaluates its exponential on the FMA pipe
+__global__ void __launch_bounds__(1024, 1) hmm_forward_split(const FwdParams p) {
+    extern __shared__ __align__(16) float smem_dyn[];
+    __shared__ int s_seq;
+    __shared__ float s_warp[32];
+    __shared__ float s_cl[16];
+
+    const int tid = threadIdx.x;
+    const int NT = blockDim.x;
+    const unsigned rank = cluster_ctarank();
+    const unsigned CS = cluster_nctarank();
+    const int K = p.K;
+    const int Kq = K >> 2;
+    const int M = NT;                         // predecessor groups per CTA (4 k-mers per thread)
+    const int g = (rank * NT + tid) * 4;      // first global k-mer
+    const int lane = tid & 31, warp = tid >> 5, nwarps = (NT + 31) >> 5;
+    const ModelConsts &mc = c_model[p.slot];
+
+    float *a0s = smem_dyn;                                             // [2][4][M]
+    float4 *Ts = reinterpret_cast<float4 *>(smem_dyn + 8 * M);         // [4][NT] transition columns
+    float4 *As = Ts + 4 * NT;                                          // [8][NT] layers 8..15
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        Ts[j * NT + tid] = __ldg(reinterpret_cast<const float4 *>(p.trans1) + (j * Kq + (g >> 2)));
+
+    const unsigned a0_base = smem_u32(a0s);
+    unsigned dst0;
+    {
+        const int dj = g / Kq, rem = g % Kq;
+        const int dr = rem / M, di = rem % M;
+        dst0 = map_to_rank(a0_base + 4u * (dj * M + di), dr);
+    }
+    const unsigned buf_bytes = 16u * M;
+    const unsigned seq_addr = smem_u32(&s_seq);
+    const unsigned cl_addr = smem_u32(s_cl);
+
+    for (;;) {
+        if (rank == 0 && tid == 0) {
+            const int i = atomicAdd(p.counter, 1);
+            const int seq = i < p.B ? p.order[i] : -1;
+            for (unsigned r = 0; r < CS; ++r) st_cluster_s32(map_to_rank(seq_addr, r), seq);
+        }
+        cluster_arrive();
+        cluster_wait();
+        const int seq = s_seq;
+        if (seq < 0) break;
+
+        long long len = p.lens[seq];
+        if (len < 1 || len > p.maxlen) {
+            if (tid == 0 && rank == 0) atomicOr(&g_status, 1u);
+            len = len < 1 ? 1 : p.maxlen;
+        }
+        const uint8_t *obs = p.data + static_cast<long long>(seq) * p.maxlen;
+        const int T_len = static_cast<int>(len);
+
+        // t = 0
+        float a[kRegLayers][4];
+        float4 e;
+        int o_next;
+        {
+            const int o0 = obs[0];
+            o_next = obs[T_len > 1 ? 1 : 0];
+            e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o0 * K + g));
+#pragma unroll
+            for (int d = 0; d < kLayers; ++d) {
+                float4 v = __ldg(reinterpret_cast<const float4 *>(p.initial_prob + d * K + g));
+                v.x += e.x; v.y += e.y; v.z += e.z; v.w += e.w;
+                if (d < kRegLayers) { a[d][0] = v.x; a[d][1] = v.y; a[d][2] = v.z; a[d][3] = v.w; }
+                else As[(d - kRegLayers) * NT + tid] = v;
+            }
+        }
+        unsigned buf = 0;
+        st_cluster_v4(dst0, a[0][0], a[0][1], a[0][2], a[0][3]);
+        cluster_arrive();
+
+        for (int t = 1; t < T_len; ++t) {
+            // this step's emission slice; the observation after it
+            e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o_next * K + g));
+            o_next = obs[t + 1 < T_len ? t + 1 : T_len - 1];
+            const float ev[4] = {e.x, e.y, e.z, e.w};
+
+            cluster_wait();
+            const float *seg = a0s + (buf ? 4 * M : 0) + tid;
+            const float a0 = seg[0], a1 = seg[M], a2 = seg[2 * M], a3 = seg[3 * M];
+            const unsigned dst = dst0 + (buf ? 0u : buf_bytes);
+
+            float q[4];
+            {
+                const float4 t0 = Ts[tid], t1 = Ts[NT + tid], t2 = Ts[2 * NT + tid], t3 = Ts[3 * NT + tid];
+                q[0] = lse4(t0.x + a0, t1.x + a1, t2.x + a2, t3.x + a3);
+                q[1] = lse4(t0.y + a0, t1.y + a1, t2.y + a2, t3.y + a3);
+                q[2] = lse4(t0.z + a0, t1.z + a1, t2.z + a2, t3.z + a3);
+                q[3] = lse4(t0.w + a0, t1.w + a1, t2.w + a2, t3.w + a3);
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                a[0][c] = lse2_sel((POLY_MASK & 1u) != 0, mc.trans2[0] + q[c], a[1][c]) + ev[c];
+            st_cluster_v4(dst, a[0][0], a[0][1], a[0][2], a[0][3]);
+            cluster_arrive();
+#pragma unroll
+            for (int d = 1; d < kRegLayers - 1; ++d)
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    a[d][c] = lse2_sel(((POLY_MASK >> d) & 1u) != 0, mc.trans2[d] + q[c], a[d + 1][c]) + ev[c];
+            // layers 7..15: the "next layer" operand comes from shared memory
+            float4 nxt = As[tid];  // layer 8 (old)
+            {
+                const float nv[4] = {nxt.x, nxt.y, nxt.z, nxt.w};
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    a[kRegLayers - 1][c] = lse2_sel(((POLY_MASK >> (kRegLayers - 1)) & 1u) != 0,
+                                               mc.trans2[kRegLayers - 1] + q[c], nv[c]) + ev[c];
+            }
+#pragma unroll
+            for (int d = kRegLayers; d < kLayers; ++d) {
+                // old alpha[min(d+1,15)]; layers 14 and 15 both read old layer 15
+                if (d < kLayers - 1) nxt = As[(d + 1 - kRegLayers) * NT + tid];
+                const float nv[4] = {nxt.x, nxt.y, nxt.z, nxt.w};
+                float r[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const float v = d == 15 ? p.gamma + nv[c] : d == 14 ? p.synthetic + nv[c] : nv[c];
+                    r[c] = lse2_sel(((POLY_MASK >> d) & 1u) != 0, mc.trans2[d] + q[c], v) + ev[c];
+                }
+                As[(d - kRegLayers) * NT + tid] = make_float4(r[0], r[1], r[2], r[3]);
+            }
+            buf ^= 1u;
+        }
+        cluster_wait();
+
+        // final log-sum-exp over all states
+        float tmax = -INFINITY;
+#pragma unroll
+        for (int d = 0; d < kRegLayers; ++d)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmax = fmaxf(tmax, a[d][c]);
+#pragma unroll
+        for (int d = 0; d < kLayers - kRegLayers; ++d) {
+            const float4 v = As[d * NT + tid];
+            tmax = fmaxf(tmax, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
+        }
+        tmax = pb::warp_max(tmax);
+        if (lane == 0) s_warp[warp] = tmax;
+        __syncthreads();
+        if (tid < (int)CS) {
+            float m = -INFINITY;
+            for (int w = 0; w < nwarps; ++w) m = fmaxf(m, s_warp[w]);
+            st_cluster_f32(map_to_rank(cl_addr + 4u * rank, tid), m);
+        }
+        cluster_arrive();
+        cluster_wait();
+        float gmax = -INFINITY;
+        for (unsigned r = 0; r < CS; ++r) gmax = fmaxf(gmax, s_cl[r]);
+        float tsum = 0.0f;
+#pragma unroll
+        for (int d = 0; d < kRegLayers; ++d)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tsum += fast_exp(a[d][c] - gmax);
+#pragma unroll
+        for (int d = 0; d < kLayers - kRegLayers; ++d) {
+            const float4 v = As[d * NT + tid];
+            tsum += fast_exp(v.x - gmax) + fast_exp(v.y - gmax) + fast_exp(v.z - gmax) + fast_exp(v.w - gmax);
+        }
+        tsum = pb::warp_sum(tsum);
+        cluster_arrive();
+        cluster_wait();
+        if (lane == 0) s_warp[warp] = tsum;
+        __syncthreads();
+        if (tid < (int)CS) {
+            float sacc = 0.0f;
+            for (int w = 0; w < nwarps; ++w) sacc += s_warp[w];
+            st_cluster_f32(map_to_rank(cl_addr + 4u * rank, tid), sacc);
+        }
+        cluster_arrive();
+        cluster_wait();
+        if (rank == 0 && tid == 0) {
+            float sacc = 0.0f;
+            for (unsigned r = 0; r < CS; ++r) sacc += s_cl[r];
+            p.result[seq] = gmax + fast_log(sacc);
+        }
+        if (p.write_alpha) {
+            float *dst_alpha = ((len & 1) ? p.alpha1 : p.alpha2) + (long long)seq * (kLayers * (long long)K);
+#pragma unroll
+            for (int d = 0; d < kLayers; ++d) {
+                const float4 v = d < kRegLayers ? make_float4(a[d % kRegLayers][0], a[d % kRegLayers][1],
+                                                              a[d % kRegLayers][2], a[d % kRegLayers][3])
+                                                : As[(d - kRegLayers) * NT + tid];
+                *reinterpret_cast<float4 *>(dst_alpha + (long long)d * K + g) = v;
+            }
+        }
+    }
+}
+
 // ---- streaming kernels --------------------------------------------------------
 __global__ void hmm_stream_init(const FwdParams p) {
     const long long N = (long long)kLayers * p.K;
@@ -482,49 +716,74 @@ __global__ void hmm_stream_final(const FwdParams p) {
 // ---- host side ------------------------------------------------------------------
 struct Plan {
     int kpt = 0, nt = 0, cs = 0;
+    bool split = false;  // layers 8..15 in shared memory, 1024 threads per CTA
 };
 
 // Picks (k-mers per thread, threads per CTA, CTAs per cluster) with
 // K = kpt*nt*cs, or returns false when only the streaming kernel applies.
-bool make_plan(long long K, Plan *pl) {
+// `allow_split` permits the register/shared split layout (factored form only).
+bool make_plan(long long K, Plan *pl, bool allow_split) {
     if (K < 4 || (K & (K - 1)) != 0) return false;  // K = 4^k
     long long kpt = K >= 1024 ? 4 : 1;
-    long long threads = K / kpt;
-    long long nt = std::min<long long>(threads, kpt == 4 ? 512 : 1024);
-    // prefer whole warps; tiny state spaces run as one partial warp
-    long long cs = threads / nt;
-    if (cs > 16 || threads < 32) return false;  // whole warps only; tiny spaces stream
+    long long nt_max = kpt == 4 ? 512 : 1024;
     if (const char *env = getenv("PARPY_B200_FWD_KPT")) {
         const int v = atoi(env);
         if ((v == 1 || v == 4) && K >= 16) {
             kpt = v;
-            threads = K / kpt;
-            nt = std::min<long long>(threads, kpt == 4 ? 512 : 1024);
-            if (const char *e2 = getenv("PARPY_B200_FWD_NT")) {
-                const long long w = atoll(e2);
-                if (w >= 32 && w <= nt && (w & (w - 1)) == 0) nt = w;
-            }
-            cs = threads / nt;
-            if (cs > 16 || threads < 32) return false;
+            nt_max = kpt == 4 ? 512 : 1024;
         }
     }
+    if (const char *env = getenv("PARPY_B200_FWD_NT")) {
+        const long long w = atoll(env);
+        if (w >= 32 && w <= nt_max && (w & (w - 1)) == 0) nt_max = w;
+    }
+    const long long threads = K / kpt;
+    if (threads < 32) return false;  // whole warps only; tiny state spaces stream
+    long long nt = std::min<long long>(threads, nt_max);
+    long long cs = threads / nt;
+    bool split = false;
+    // Large state spaces: the split layout (1024 threads x 4 k-mers per CTA) halves
+    // the CTAs a sequence needs, so clusters pack the GPCs without idle SMs.
+    bool want_split = allow_split && kpt == 4 && K >= 4096;
+    if (const char *env = getenv("PARPY_B200_FWD_SPLIT")) want_split = want_split && atoi(env) != 0;
+    if (want_split) {
+        nt = 1024;
+        cs = K / 4 / 1024;
+        split = true;
+    }
+    if (cs > 16) return false;
     pl->kpt = (int)kpt;
     pl->nt = (int)nt;
     pl->cs = (int)cs;
+    pl->split = split;
     return true;
 }
 
 using ResidentKernel = void (*)(const FwdParams);
 
-ResidentKernel pick_kernel(int kpt, bool five) {
+ResidentKernel pick_kernel(const Plan &pl, bool five) {
+    const int kpt = pl.kpt;
+    if (pl.split && !five) {
+        // how many of the 16 layers take the polynomial exponential
+        int npoly = 5;
+        if (const char *env = getenv("PARPY_B200_FWD_POLY")) npoly = atoi(env);
+        switch (npoly) {
+            case 0: return hmm_forward_split<0x0000u>;
+            case 4: return hmm_forward_split<0x2222u>;   // layers 1,5,9,13
+            case 6: return hmm_forward_split<0x4A52u>;   // layers 1,4,6,9,11,14
+            case 8: return hmm_forward_split<0xAAAAu>;   // odd layers
+            default: return hmm_forward_split<0x2492u>;  // layers 1,4,7,10,13
+        }
+    }
     if (kpt == 4) return five ? hmm_forward_resident<4, true> : hmm_forward_resident<4, false>;
     return five ? hmm_forward_resident<1, true> : hmm_forward_resident<1, false>;
 }
 
 int32_t resident_config(const Plan &pl, bool five, cudaLaunchConfig_t *cfg,
                         cudaLaunchAttribute *attr, int *max_clusters, ResidentKernel *kern) {
-    ResidentKernel k = pick_kernel(pl.kpt, five);
-    const size_t smem = size_t(2) * 4 * (size_t(pl.nt) * pl.kpt / 4) * sizeof(float);
+    ResidentKernel k = pick_kernel(pl, five);
+    size_t smem = size_t(2) * 4 * (size_t(pl.nt) * pl.kpt / 4) * sizeof(float);
+    if (pl.split && !five) smem += size_t(4 + 8) * pl.nt * sizeof(float4);  // transition columns + layers 8..15
     if (pl.cs > 8) PB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
     PB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     memset(cfg, 0, sizeof(*cfg));
@@ -597,7 +856,7 @@ int32_t forward_impl(float gamma, const float *initial_prob, int64_t num_states,
                                     stream));
 
     Plan pl;
-    const bool resident = !streaming_forced && make_plan(K, &pl);
+    const bool resident = !streaming_forced && make_plan(K, &pl, !five);
     if (resident) {
         PB_REQUIRE(pl.kpt == 1 || (pb::aligned16(initial_prob) && pb::aligned16(output_prob) &&
                                    pb::aligned16(trans1) &&
@@ -686,7 +945,7 @@ int32_t parpy_b200_forward_plan(int64_t num_states, int64_t num_instances, int32
                                 int32_t *threads_per_cta, int32_t *ctas_per_cluster,
                                 int32_t *clusters) {
     Plan pl;
-    if (num_states < 64 || num_states % 64 != 0 || !make_plan(num_states / kLayers, &pl)) {
+    if (num_states < 64 || num_states % 64 != 0 || !make_plan(num_states / kLayers, &pl, true)) {
         pb::set_error("forward_plan: num_states=%lld has no resident mapping", (long long)num_states);
         return PB_ERR_UNSUPPORTED;
     }
@@ -759,7 +1018,7 @@ extern "C" int32_t parpy_b200_forward_noalloc(float gamma, const float *initial_
                "forward_noalloc: null table, observation or result pointer");
     const long long K = num_states / kLayers;
     Plan pl;
-    PB_REQUIRE(make_plan(K, &pl),
+    PB_REQUIRE(make_plan(K, &pl, true),
                "forward_noalloc: num_states=%lld has no resident mapping (the streaming kernel needs "
                "caller scratch: use parpy_b200_forward)", (long long)num_states);
     PB_REQUIRE(pl.kpt == 1 || (pb::aligned16(initial_prob) && pb::aligned16(output_prob) && pb::aligned16(trans1)),

@@ -150,6 +150,51 @@ def test_other_state_spaces_against_oracle(native, oracle_mod, k):
     assert max_rel(res.cpu().numpy(), exp) <= REL_ORACLE
 
 
+def test_kernel_layout_variants_agree_with_oracle(native, oracle_mod, monkeypatch):
+    # 7mer: register/shared split layout with 0..8 layers on the polynomial exponential, and
+    # the all-register 8-CTA layout; every variant against the CPU oracle on the same inputs.
+    from parpy_b200 import synthetic
+    hmm = synthetic.hmm_model(7, seed=5)
+    seqs = synthetic.hmm_sequences(6, 2, 90, seed=6)
+    exp, exp_alpha = oracle_mod.forward(hmm, seqs, want_alpha=True)
+    dh, ds = to_dev(hmm), to_dev(seqs)
+    settings = [{"PARPY_B200_FWD_SPLIT": "0"}] + [{"PARPY_B200_FWD_POLY": str(n)} for n in (0, 4, 5, 6, 8)]
+    for env in settings:
+        for k in ("PARPY_B200_FWD_SPLIT", "PARPY_B200_FWD_POLY"):
+            monkeypatch.delenv(k, raising=False)
+        for k, v in env.items():
+            monkeypatch.setenv(k, v)
+        rc, res, a1, a2 = cabi_forward(native, dh, ds, 2, alpha=True)
+        assert rc == 0, native.error_message()
+        assert max_rel(res.cpu().numpy(), exp) <= REL_ORACLE, env
+        for i in range(6):
+            a = (a1 if int(seqs["lens"][i]) & 1 else a2)[i].cpu().numpy()
+            assert max_rel(a, exp_alpha[i]) <= REL_ORACLE, env
+
+
+def test_8mer_runs_on_a_16_cta_cluster(native, oracle_mod):
+    # 4^8 k-mers x 16 layers = 1,048,576 states: non-portable cluster of 16 CTAs
+    from parpy_b200 import synthetic
+    hmm = synthetic.hmm_model(8, seed=8)
+    seqs = synthetic.hmm_sequences(3, 1, 16, seed=9)
+    exp = oracle_mod.forward(hmm, seqs)
+    rc, res, _, _ = cabi_forward(native, to_dev(hmm), to_dev(seqs))
+    assert rc == 0, native.error_message()
+    assert max_rel(res.cpu().numpy(), exp) <= REL_ORACLE
+
+
+def test_empty_batch_and_single_step(native):
+    from parpy_b200 import synthetic
+    hmm = to_dev(synthetic.hmm_model(5, seed=2))
+    seqs = to_dev(synthetic.hmm_sequences(3, 1, 1, seed=3))          # maxlen = 1: no time steps at all
+    rc, res, _, _ = cabi_forward(native, hmm, seqs)
+    assert rc == 0 and np.isfinite(res.cpu().numpy()).all()
+    empty = dict(seqs)
+    empty["num_instances"] = torch.tensor(0)
+    rc, _, _, _ = cabi_forward(native, hmm, empty)
+    assert rc == 0
+
+
 def test_zero_probability_emissions_stay_minus_inf(native, oracle_mod):
     hmm = load_model("3mer")
     seqs = load_signals(shortest_reads(3))
