@@ -50,7 +50,7 @@ def parse_args():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak",
                     help="weak: 500 sequences per GPU; strong: 500 sequences sharded over the GPUs")
-    ap.add_argument("--variant", choices=["auto", "five_term", "streaming"], default="auto")
+    ap.add_argument("--variant", choices=["auto", "five_term", "scaled", "streaming"], default="auto")
     ap.add_argument("--ref-cuda", action="store_true",
                     help="also time the reference's own CUDA implementation (oracle/_ref), once")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -89,6 +89,13 @@ int32_t forward_kernel_scratch_first(float gamma, float *initial_prob, int64_t n
  * log-sum-exp and operand order instead of the factored 4-way + 2-way form. */
 #define PARPY_B200_FWD_FIVE_TERM 4u
 
+/* Resident kernel, at least 1024 k-mers: evaluate the recurrence on probabilities
+ * with a per-thread base-2 exponent (extended-range linear arithmetic) instead of
+ * on log-probabilities. Mathematically the same quantity; rounding differs: this
+ * form agrees with a float64 evaluation to ~1e-8 relative, while fp32 log space
+ * (the reference's arithmetic) is itself 1e-6..1e-4 away from float64. */
+#define PARPY_B200_FWD_SCALED 8u
+
 /* Same computation as forward_kernel with explicit options. `trans2` is a
  * DEVICE pointer to 16 floats like everywhere else. `stream` is a
  * cudaStream_t (NULL = stream 0). Replaces the host stub + kernels the

@@ -64,6 +64,7 @@ FWD_AUTO = 0
 FWD_STREAMING = 1
 FWD_WRITE_ALPHA = 2
 FWD_FIVE_TERM = 4
+FWD_SCALED = 8
 
 
 class NativeLibraryMissing(RuntimeError):

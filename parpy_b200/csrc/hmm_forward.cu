@@ -41,6 +41,8 @@ struct ModelConsts {
     float trans2[kLayers];
 };
 __constant__ ModelConsts c_model[kModelSlots];
+// exp(trans2[d]) for the scaled (linear-domain) kernel, same slot discipline.
+__constant__ ModelConsts c_model_lin[kModelSlots];
 
 // Device status word. Bit 0: a sequence length outside [1, maxlen] was clamped.
 __device__ unsigned g_status;
@@ -72,6 +74,8 @@ struct FwdParams {
     int write_alpha;
     float gamma;
     float synthetic;
+    float gamma_lin;            // exp(gamma), exp(synthetic_248): scaled kernel only
+    float synthetic_lin;
 };
 
 // ---- cluster primitives (PTX) ----------------------------------------------
@@ -643,6 +647,253 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_split(const FwdParams p) 
     }
 }
 
+
+// ---- scaled (extended-range linear) kernel ------------------------------------------
+// The same recurrence evaluated on probabilities instead of log-probabilities:
+//   alpha'[d,s] = (A[d] * Q[s] + C[d] * alpha[d+1,s]) * E[s],   Q[s] = sum_j T[j,s] * alpha[0,p_j]
+// with A = exp(trans2), T = exp(trans1), E = exp(output_prob[o_t]), C[15] = exp(gamma),
+// C[14] = exp(synthetic_248), else 1. Two multiply-adds per state and no
+// transcendental in the inner loop (4 ex2 per thread and step for the emissions).
+// Range: every thread keeps one base-2 exponent W for its 64 states, value =
+// mantissa * 2^W with fp32 mantissas; W follows the data (largest incoming or own
+// magnitude) so mantissas stay near 1, and states more than 2^-126 below their
+// thread's largest value flush to zero. Layer 0 travels between CTAs as
+// (mantissa, exponent). Log-likelihoods are formed once per sequence. Against a
+// float64 evaluation of the reference formula this agrees to ~1e-8 relative; the
+// reference's own fp32 log-space result carries more rounding than that.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ int exponent_of(float x) {   // x >= 0; 0 and denormals give -127
+    return (__float_as_int(x) >> 23) - 127;
+}
+__device__ __forceinline__ float pow2_clamped(int e) {  // 2^e, +0.0 below 2^-126
+    e = max(e, -127);
+    e = min(e, 127);
+    return __int_as_float((e + 127) << 23);
+}
+__device__ __forceinline__ void st_cluster_v4i(unsigned addr, int a, int b, int c, int d) {
+    asm volatile("st.shared::cluster.v4.s32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
+                 : "memory");
+}
+
+constexpr int kExpFloor = -(1 << 28);  // exponent of an all-zero thread
+// Exponent that travels with a layer-0 mantissa: thread exponent + exponent of the
+// mantissa. A zero mantissa travels with an exponent so low that the receiver's
+// scale factor becomes +0.0 (its mantissa bits are rebuilt as 1.0, see below).
+__device__ __forceinline__ int export_exponent(float x, int W) {
+    return x > 0.0f ? W + exponent_of(x) : kExpFloor - 200;
+}
+
+__global__ void __launch_bounds__(512, 1) hmm_forward_scaled(const FwdParams p) {
+    extern __shared__ __align__(16) float smem_dyn[];   // [2][4][M] mantissas, then [2][4][M] exponents
+    __shared__ int s_seq;
+    __shared__ float s_warp[32];
+    __shared__ int s_warp_i[32];
+    __shared__ float s_cl[16];
+    __shared__ int s_cl_i[16];
+
+    const int tid = threadIdx.x;
+    const int NT = blockDim.x;
+    const unsigned rank = cluster_ctarank();
+    const unsigned CS = cluster_nctarank();
+    const int K = p.K;
+    const int Kq = K >> 2;
+    const int M = NT;
+    const int g = (rank * NT + tid) * 4;
+    const int lane = tid & 31, warp = tid >> 5, nwarps = (NT + 31) >> 5;
+    const ModelConsts &A = c_model_lin[p.slot];
+
+    float *a0x = smem_dyn;
+    int *a0e = reinterpret_cast<int *>(smem_dyn + 8 * M);
+
+    // T[j][c] = exp(trans1[p_j, (g+c)%4])
+    float T[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float4 v = __ldg(reinterpret_cast<const float4 *>(p.trans1) + (j * Kq + (g >> 2)));
+        T[j][0] = fast_exp(v.x);
+        T[j][1] = fast_exp(v.y);
+        T[j][2] = fast_exp(v.z);
+        T[j][3] = fast_exp(v.w);
+    }
+    unsigned dstx0, dste0;
+    {
+        const int dj = g / Kq, rem = g % Kq;
+        const int dr = rem / M, di = rem % M;
+        dstx0 = map_to_rank(smem_u32(a0x) + 4u * (dj * M + di), dr);
+        dste0 = map_to_rank(smem_u32(a0e) + 4u * (dj * M + di), dr);
+    }
+    const unsigned buf_bytes = 16u * M;
+    const unsigned seq_addr = smem_u32(&s_seq);
+    const unsigned cl_addr = smem_u32(s_cl);
+    const unsigned cli_addr = smem_u32(s_cl_i);
+
+    for (;;) {
+        if (rank == 0 && tid == 0) {
+            const int i = atomicAdd(p.counter, 1);
+            const int seq = i < p.B ? p.order[i] : -1;
+            for (unsigned r = 0; r < CS; ++r) st_cluster_s32(map_to_rank(seq_addr, r), seq);
+        }
+        cluster_arrive();
+        cluster_wait();
+        const int seq = s_seq;
+        if (seq < 0) break;
+
+        long long len = p.lens[seq];
+        if (len < 1 || len > p.maxlen) {
+            if (tid == 0 && rank == 0) atomicOr(&g_status, 1u);
+            len = len < 1 ? 1 : p.maxlen;
+        }
+        const uint8_t *obs = p.data + static_cast<long long>(seq) * p.maxlen;
+        const int T_len = static_cast<int>(len);
+
+        // ---- t = 0: x = exp(initial_prob) * exp(emission), W = 0 ------------------------
+        float x[kLayers][4];
+        float4 e_next;
+        int o_next;
+        int W = 0;       // exponent shared by this thread's 64 states
+        int kt;          // exponent of the largest mantissa (magnitude hint)
+        {
+            const int o0 = obs[0];
+            const int o1 = obs[T_len > 1 ? 1 : 0];
+            o_next = obs[T_len > 2 ? 2 : T_len - 1];
+            const float4 e0 = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o0 * K + g));
+            e_next = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o1 * K + g));
+            const float el[4] = {fast_exp(e0.x), fast_exp(e0.y), fast_exp(e0.z), fast_exp(e0.w)};
+            float m = 0.0f;
+#pragma unroll
+            for (int d = 0; d < kLayers; ++d) {
+                const float4 v = __ldg(reinterpret_cast<const float4 *>(p.initial_prob + d * K + g));
+                x[d][0] = fast_exp(v.x) * el[0];
+                x[d][1] = fast_exp(v.y) * el[1];
+                x[d][2] = fast_exp(v.z) * el[2];
+                x[d][3] = fast_exp(v.w) * el[3];
+                m = max3(m, fmaxf(x[d][0], x[d][1]), fmaxf(x[d][2], x[d][3]));
+            }
+            kt = exponent_of(m);
+        }
+        unsigned buf = 0;
+        st_cluster_v4(dstx0, x[0][0], x[0][1], x[0][2], x[0][3]);
+        st_cluster_v4i(dste0, export_exponent(x[0][0], W), export_exponent(x[0][1], W),
+                       export_exponent(x[0][2], W), export_exponent(x[0][3], W));
+        cluster_arrive();
+
+        for (int t = 1; t < T_len; ++t) {
+            // emission probabilities of o_t (log values were fetched a step ago)
+            const float el[4] = {fast_exp(e_next.x), fast_exp(e_next.y), fast_exp(e_next.z), fast_exp(e_next.w)};
+            e_next = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o_next * K + g));
+            o_next = obs[t + 2 < T_len ? t + 2 : T_len - 1];
+
+            cluster_wait();
+            const int off = (buf ? 4 * M : 0) + tid;
+            const float xa0 = a0x[off], xa1 = a0x[off + M], xa2 = a0x[off + 2 * M], xa3 = a0x[off + 3 * M];
+            // each predecessor arrives with "its exponent + exponent of its mantissa" so that
+            // the largest incoming magnitude is known without touching the mantissas
+            const int ea0 = a0e[off], ea1 = a0e[off + M], ea2 = a0e[off + 2 * M], ea3 = a0e[off + 3 * M];
+            const unsigned dstx = dstx0 + (buf ? 0u : buf_bytes);
+            const unsigned dste = dste0 + (buf ? 0u : buf_bytes);
+
+            // new exponent: the largest magnitude this thread is about to combine
+            int Wn = max(max(ea0, ea1), max(ea2, ea3));
+            Wn = max(Wn, W + kt);
+            Wn = max(Wn, kExpFloor);
+            // incoming layer-0 values relative to 2^Wn (ea = W_p + exponent_of(x) => x*2^(W_p-Wn) =
+            // mantissa-normalised x * 2^(ea - Wn))
+            const float y0 = __int_as_float((__float_as_int(xa0) & 0x007fffff) | 0x3f800000) * pow2_clamped(ea0 - Wn);
+            const float y1 = __int_as_float((__float_as_int(xa1) & 0x007fffff) | 0x3f800000) * pow2_clamped(ea1 - Wn);
+            const float y2 = __int_as_float((__float_as_int(xa2) & 0x007fffff) | 0x3f800000) * pow2_clamped(ea2 - Wn);
+            const float y3 = __int_as_float((__float_as_int(xa3) & 0x007fffff) | 0x3f800000) * pow2_clamped(ea3 - Wn);
+            const float own = pow2_clamped(W - Wn);
+            float QE[4], Eo[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float q = fmaf(T[3][c], y3, fmaf(T[2][c], y2, fmaf(T[1][c], y1, T[0][c] * y0)));
+                QE[c] = q * el[c];
+                Eo[c] = el[c] * own;
+            }
+            // layer 0 first: it is what the other CTAs wait for
+#pragma unroll
+            for (int c = 0; c < 4; ++c) x[0][c] = fmaf(A.trans2[0], QE[c], Eo[c] * x[1][c]);
+            st_cluster_v4(dstx, x[0][0], x[0][1], x[0][2], x[0][3]);
+            st_cluster_v4i(dste, export_exponent(x[0][0], Wn), export_exponent(x[0][1], Wn),
+                           export_exponent(x[0][2], Wn), export_exponent(x[0][3], Wn));
+            cluster_arrive();
+            float m = max3(fmaxf(x[0][0], x[0][1]), x[0][2], x[0][3]);
+#pragma unroll
+            for (int d = 1; d < kLayers; ++d) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const float nx = d == 15 ? p.gamma_lin * x[15][c]
+                                   : d == 14 ? p.synthetic_lin * x[15][c]
+                                             : x[d + 1 < kLayers ? d + 1 : 15][c];
+                    x[d][c] = fmaf(A.trans2[d], QE[c], Eo[c] * nx);
+                }
+                m = max3(m, fmaxf(x[d][0], x[d][1]), fmaxf(x[d][2], x[d][3]));
+            }
+            kt = exponent_of(m);
+            W = Wn;
+            buf ^= 1u;
+        }
+        cluster_wait();
+
+        // ---- log-likelihood: log(sum of all states) with a common exponent --------------
+        int gexp = W + kt;
+        gexp = __reduce_max_sync(0xffffffffu, gexp);
+        if (lane == 0) s_warp_i[warp] = gexp;
+        __syncthreads();
+        if (tid < (int)CS) {
+            int v = kExpFloor - 200;
+            for (int w = 0; w < nwarps; ++w) v = max(v, s_warp_i[w]);
+            st_cluster_s32(map_to_rank(cli_addr + 4u * rank, tid), v);
+        }
+        cluster_arrive();
+        cluster_wait();
+        int G = kExpFloor - 200;
+        for (unsigned r = 0; r < CS; ++r) G = max(G, s_cl_i[r]);
+        float tsum = 0.0f;
+#pragma unroll
+        for (int d = 0; d < kLayers; ++d) tsum += (x[d][0] + x[d][1]) + (x[d][2] + x[d][3]);
+        tsum *= pow2_clamped(W - G);
+        tsum = pb::warp_sum(tsum);
+        if (lane == 0) s_warp[warp] = tsum;
+        __syncthreads();
+        if (tid < (int)CS) {
+            float sacc = 0.0f;
+            for (int w = 0; w < nwarps; ++w) sacc += s_warp[w];
+            st_cluster_f32(map_to_rank(cl_addr + 4u * rank, tid), sacc);
+        }
+        cluster_arrive();
+        cluster_wait();
+        if (rank == 0 && tid == 0) {
+            double sacc = 0.0;
+            for (unsigned r = 0; r < CS; ++r) sacc += (double)s_cl[r];
+            // natural log of sum * 2^G; an impossible sequence (sum == 0) gives -inf
+            p.result[seq] = sacc > 0.0 ? (float)(log(sacc) + (double)G * 0.6931471805599453) : -INFINITY;
+        }
+        if (p.write_alpha) {
+            float *dst_alpha = ((len & 1) ? p.alpha1 : p.alpha2) + (long long)seq * (kLayers * (long long)K);
+            const float wl = (float)W * kLn2;
+#pragma unroll
+            for (int d = 0; d < kLayers; ++d) {
+                float4 v;
+                v.x = fast_log(x[d][0]) + wl;
+                v.y = fast_log(x[d][1]) + wl;
+                v.z = fast_log(x[d][2]) + wl;
+                v.w = fast_log(x[d][3]) + wl;
+                *reinterpret_cast<float4 *>(dst_alpha + (long long)d * K + g) = v;
+            }
+        }
+        // the pop at the top of the loop starts with a full cluster barrier
+    }
+}
+
+__global__ void hmm_linear_consts(const float *__restrict__ trans2, float *__restrict__ out) {
+    if (threadIdx.x < kLayers) out[threadIdx.x] = expf(trans2[threadIdx.x]);
+}
+
 // ---- streaming kernels --------------------------------------------------------
 __global__ void hmm_stream_init(const FwdParams p) {
     const long long N = (long long)kLayers * p.K;
@@ -717,6 +968,7 @@ __global__ void hmm_stream_final(const FwdParams p) {
 struct Plan {
     int kpt = 0, nt = 0, cs = 0;
     bool split = false;  // layers 8..15 in shared memory, 1024 threads per CTA
+    bool scaled = false; // extended-range linear arithmetic instead of log space
 };
 
 // Picks (k-mers per thread, threads per CTA, CTAs per cluster) with
@@ -763,6 +1015,7 @@ using ResidentKernel = void (*)(const FwdParams);
 
 ResidentKernel pick_kernel(const Plan &pl, bool five) {
     const int kpt = pl.kpt;
+    if (pl.scaled) return hmm_forward_scaled;
     if (pl.split && !five) {
         // how many of the 16 layers take the polynomial exponential
         int npoly = 5;
@@ -783,7 +1036,8 @@ int32_t resident_config(const Plan &pl, bool five, cudaLaunchConfig_t *cfg,
                         cudaLaunchAttribute *attr, int *max_clusters, ResidentKernel *kern) {
     ResidentKernel k = pick_kernel(pl, five);
     size_t smem = size_t(2) * 4 * (size_t(pl.nt) * pl.kpt / 4) * sizeof(float);
-    if (pl.split && !five) smem += size_t(4 + 8) * pl.nt * sizeof(float4);  // transition columns + layers 8..15
+    if (pl.scaled) smem *= 2;  // mantissas + exponents
+    else if (pl.split && !five) smem += size_t(4 + 8) * pl.nt * sizeof(float4);  // transition columns + layers 8..15
     if (pl.cs > 8) PB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
     PB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     memset(cfg, 0, sizeof(*cfg));
@@ -827,6 +1081,8 @@ int32_t forward_impl(float gamma, const float *initial_prob, int64_t num_states,
     const bool streaming_forced = flags & PARPY_B200_FWD_STREAMING;
     const bool write_alpha = flags & PARPY_B200_FWD_WRITE_ALPHA;
     const bool five = flags & PARPY_B200_FWD_FIVE_TERM;
+    const bool scaled = flags & PARPY_B200_FWD_SCALED;
+    PB_REQUIRE(!(five && scaled), "forward: FIVE_TERM and SCALED exclude each other");
     PB_REQUIRE(!write_alpha || (alpha1 && alpha2), "forward: WRITE_ALPHA needs alpha1 and alpha2");
 
     pb::DeviceInfo dev;
@@ -849,6 +1105,8 @@ int32_t forward_impl(float gamma, const float *initial_prob, int64_t num_states,
     p.K = static_cast<int>(K);
     p.gamma = gamma;
     p.synthetic = synthetic_248;
+    p.gamma_lin = expf(gamma);
+    p.synthetic_lin = expf(synthetic_248);
     p.write_alpha = write_alpha ? 1 : 0;
     p.slot = static_cast<int>(g_slot.fetch_add(1) % kModelSlots);
     PB_CUDA(cudaMemcpyToSymbolAsync(c_model, trans2, sizeof(ModelConsts),
@@ -856,7 +1114,10 @@ int32_t forward_impl(float gamma, const float *initial_prob, int64_t num_states,
                                     stream));
 
     Plan pl;
-    const bool resident = !streaming_forced && make_plan(K, &pl, !five);
+    const bool resident = !streaming_forced && make_plan(K, &pl, !five && !scaled);
+    PB_REQUIRE(!scaled || (resident && pl.kpt == 4),
+               "forward: the scaled kernel needs at least 1024 k-mers (num_states=%lld)", (long long)num_states);
+    pl.scaled = scaled;
     if (resident) {
         PB_REQUIRE(pl.kpt == 1 || (pb::aligned16(initial_prob) && pb::aligned16(output_prob) &&
                                    pb::aligned16(trans1) &&
@@ -875,6 +1136,14 @@ int32_t forward_impl(float gamma, const float *initial_prob, int64_t num_states,
         if (rc) return rc;
         int *order = static_cast<int *>(ws);
         int *counter = reinterpret_cast<int *>(static_cast<char *>(ws) + order_bytes);
+        if (scaled) {
+            float *lin = reinterpret_cast<float *>(static_cast<char *>(ws) + order_bytes + 256);
+            hmm_linear_consts<<<1, 32, 0, stream>>>(trans2, lin);
+            PB_CUDA(cudaGetLastError());
+            PB_CUDA(cudaMemcpyToSymbolAsync(c_model_lin, lin, sizeof(ModelConsts),
+                                            size_t(p.slot) * sizeof(ModelConsts),
+                                            cudaMemcpyDeviceToDevice, stream));
+        }
         p.order = order;
         p.counter = counter;
         const size_t sched_smem = p.B <= kSortLimit ? size_t(p.B) * sizeof(int) : 0;

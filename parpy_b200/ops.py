@@ -118,8 +118,11 @@ def _forward_flags(opts):
         flags |= _native.FWD_STREAMING
     elif mode == "five_term":
         flags |= _native.FWD_FIVE_TERM
+    elif mode == "scaled":
+        flags |= _native.FWD_SCALED
     elif mode != "auto":
-        raise RuntimeError(f"opts.b200['forward'] must be 'auto', 'five_term' or 'streaming', got {mode!r}")
+        raise RuntimeError("opts.b200['forward'] must be 'auto', 'five_term', 'scaled' or 'streaming', "
+                           f"got {mode!r}")
     if b.get("write_alpha", False):
         flags |= _native.FWD_WRITE_ALPHA
     return flags
