@@ -205,6 +205,23 @@ int32_t parpy_b200_sddmm_coo(const float *A, const float *B, const int64_t *rows
                              const float *cvalues, float *D, int64_t K, int64_t ncols, int64_t nnz,
                              double alpha, double beta, void *stream);
 
+/* ---- row normalisation, exp + row sum, CSR SpMM ---------------------------------------------
+ * normalize_rows: t[i,:] /= sum(t[i,:]) in place, the entry generated for
+ * test/test_normalize.py:7-15 `normalize_rows(t, nrows, ncols)`.
+ * parpy_b200_sum_exp_rows: x = exp(x) in place and out[r] = sum(x[r,:]) for fp32
+ * x[nrows, ncols]; with nrows = N*M and ncols = K this is test/test_sync.py:59-69
+ * `sum_exp_3d(x, N, M, out)` (whose generated entry has K compiled in).
+ * spmm_cell: C[i,j] += sum_a A.values[a] * B.values[A.cols[a], j], the entry
+ * generated for test/test_spmm.py:16-24 `spmm_cell(A, B, C)` with A = {cols, nrows,
+ * rows, values} and B = {ncols, values} (sorted keys); C fp32 [nrows, ncols]. */
+int32_t normalize_rows(float *t, int64_t nrows, int64_t ncols);
+int32_t parpy_b200_normalize_rows(float *t, int64_t nrows, int64_t ncols, void *stream);
+int32_t parpy_b200_sum_exp_rows(float *x, int64_t nrows, int64_t ncols, float *out, void *stream);
+int32_t spmm_cell(int64_t *A_cols, int64_t A_nrows, int64_t *A_rows, float *A_values, int64_t B_ncols,
+                  float *B_values, float *C);
+int32_t parpy_b200_spmm(const float *values, const int64_t *rows, const int64_t *cols, int64_t nrows,
+                        const float *B, int64_t ncols, float *C, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -79,3 +79,41 @@ void oracle_sddmm(const float *A, const float *B, const int64_t *rows, const int
         D[i] = (float)(alpha * (double)t + beta * (double)cvalues[i]);
     }
 }
+
+/* test/test_normalize.py:7-15: s = sum(t[i,:]) (double accumulator, order-free); t[i,:] /= s */
+void oracle_normalize_rows(float *t, int64_t nrows, int64_t ncols) {
+#pragma omp parallel for
+    for (int64_t i = 0; i < nrows; ++i) {
+        float *r = t + i * ncols;
+        double acc = 0.0;
+        for (int64_t j = 0; j < ncols; ++j) acc += r[j];
+        const float s = (float)acc;
+        for (int64_t j = 0; j < ncols; ++j) r[j] = r[j] / s;
+    }
+}
+
+/* test/test_sync.py:59-69 with rows = N*M: x = exp(x) in place; out[r] = sum(x[r,:]) */
+void oracle_sum_exp_rows(float *x, int64_t nrows, int64_t ncols, float *out) {
+#pragma omp parallel for
+    for (int64_t i = 0; i < nrows; ++i) {
+        float *r = x + i * ncols;
+        double acc = 0.0;
+        for (int64_t j = 0; j < ncols; ++j) {
+            r[j] = expf(r[j]);
+            acc += r[j];
+        }
+        out[i] = (float)acc;
+    }
+}
+
+/* test/test_spmm.py:16-24: C[i,j] += values[a] * B[cols[a], j], non-zeros in index order */
+void oracle_spmm(const float *values, const int64_t *rows, const int64_t *cols, int64_t nrows,
+                 const float *B, int64_t ncols, float *C) {
+#pragma omp parallel for
+    for (int64_t i = 0; i < nrows; ++i)
+        for (int64_t j = 0; j < ncols; ++j) {
+            float acc = C[i * ncols + j];
+            for (int64_t a = rows[i]; a < rows[i + 1]; ++a) acc += values[a] * B[cols[a] * ncols + j];
+            C[i * ncols + j] = acc;
+        }
+}

@@ -208,3 +208,36 @@ def sddmm(A, B, rows, cols, cvalues, alpha, beta):
     fn(A.ctypes.data, B.ctypes.data, rows.ctypes.data, cols.ctypes.data, cvalues.ctypes.data,
        D.ctypes.data, A.shape[1], B.shape[1], len(cols), float(alpha), float(beta))
     return D
+
+
+def normalize_rows(t):
+    """test/test_normalize.py:7-15; returns the normalised copy."""
+    t = _f32(t).copy()
+    fn = lib().oracle_normalize_rows
+    fn.restype = None
+    fn.argtypes = [_P, ctypes.c_int64, ctypes.c_int64]
+    fn(t.ctypes.data, t.shape[0], t.shape[1])
+    return t
+
+
+def sum_exp_rows(x):
+    """test/test_sync.py:59-69 on [rows, K]; returns (exp(x), row sums)."""
+    x = _f32(x).copy()
+    out = np.empty(x.shape[0], dtype=np.float32)
+    fn = lib().oracle_sum_exp_rows
+    fn.restype = None
+    fn.argtypes = [_P, ctypes.c_int64, ctypes.c_int64, _P]
+    fn(x.ctypes.data, x.shape[0], x.shape[1], out.ctypes.data)
+    return x, out
+
+
+def spmm(A, B, C):
+    """test/test_spmm.py:16-24; returns C + A @ B for the CSR dict A and dense B."""
+    values, rows, cols = _f32(A["values"]), _np(A["rows"], np.int64), _np(A["cols"], np.int64)
+    B, C = _f32(B), _f32(C).copy()
+    fn = lib().oracle_spmm
+    fn.restype = None
+    fn.argtypes = [_P, _P, _P, ctypes.c_int64, _P, ctypes.c_int64, _P]
+    fn(values.ctypes.data, rows.ctypes.data, cols.ctypes.data, len(rows) - 1, B.ctypes.data, B.shape[1],
+       C.ctypes.data)
+    return C

@@ -32,10 +32,11 @@ def reduce():
 
 
 def clear_cache():
-    """Drops cached scalar read-backs. There is no compile cache to clear: the
-    kernels are prebuilt (the reference removes ~/.cache/parpy here)."""
-    from . import ops
+    """Drops cached scalar read-backs and the shared objects built by
+    :func:`compile_string` (the reference removes ~/.cache/parpy here)."""
+    from . import ops, source
     ops._scalar_cache.clear()
+    source.clear_cache()
 
 
 def _check_kwargs(kwargs, fun_name):
@@ -144,18 +145,46 @@ def jit(fun):
 
 
 def print_compiled(fun, args, opts=None):
-    """The reference returns the generated CUDA C++ here. The kernels of this
-    package are hand-written and prebuilt; this returns the path and entry point
-    that serve ``fun`` so that ``len(...) != 0`` style checks keep working."""
+    """Returns CUDA C++ source for ``fun`` (python/parpy/__init__.py:177-199). The
+    reference prints what its compiler generates for the given arguments; here the
+    kernels are hand-written, so this is the amalgamated source of the kernel
+    file that serves ``fun`` — a complete translation unit that
+    :func:`compile_string` accepts back, edited or not."""
     import inspect
-    from . import _native, ops
+    from . import ops, source
     spec = _bound.get(fun) or ops.resolve(fun.__name__, tuple(inspect.signature(fun).parameters))
-    return (f"// {spec.name}({', '.join(spec.params)}): prebuilt sm_100a kernel in {_native.LIB_PATH}\n"
-            f"// reference source: {spec.doc}\n")
+    return source.kernel_source(spec.name)
 
 
 def compile_string(fun_name, code, opts=None):
-    raise RuntimeError("parpy_b200 ships prebuilt kernels and does not compile CUDA source at run time")
+    """Compiles CUDA source given as a string and returns a callable for its
+    ``extern "C"`` entry ``fun_name`` (python/parpy/__init__.py:161-175). The
+    callable takes the arguments positionally (no ``opts``), stages host arrays
+    to the device and copies every one of them back afterwards, as the
+    reference's wrapper does."""
+    import functools
+    from . import source
+    extra = tuple(getattr(opts, "extra_flags", ()) or ()) if opts is not None else ()
+    fn = source.wrapper(source.compile_source(code, extra), fun_name)
+
+    @functools.wraps(fn)
+    def inner(*args):
+        staged = []
+        dev_args = []
+        for i, arg in enumerate(args):
+            if isinstance(arg, dict):
+                dev_args.append({k: _stage_one(v, "inout", f"#{i+1}[\"{k}\"]", staged) for k, v in arg.items()})
+            else:
+                dev_args.append(_stage_one(arg, "inout", f"#{i+1}", staged))
+        try:
+            fn(*dev_args)
+        except Exception:
+            for b in staged:
+                b.forget_source()
+            raise
+        for b in staged:
+            b.release()
+    return inner
 
 
 def external(ext_name, backend, target, header=None, parallelize=None):

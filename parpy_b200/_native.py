@@ -54,6 +54,11 @@ SIGNATURES = {
                                      c_i64, c_i64, c_f64, c_f64, c_ptr]),
     "parpy_b200_sddmm_coo": (c_i32, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_i64, c_i64,
                                      c_f64, c_f64, c_ptr]),
+    "normalize_rows": (c_i32, [c_ptr, c_i64, c_i64]),
+    "parpy_b200_normalize_rows": (c_i32, [c_ptr, c_i64, c_i64, c_ptr]),
+    "parpy_b200_sum_exp_rows": (c_i32, [c_ptr, c_i64, c_i64, c_ptr, c_ptr]),
+    "spmm_cell": (c_i32, [c_ptr, c_i64, c_ptr, c_ptr, c_i64, c_ptr, c_ptr]),
+    "parpy_b200_spmm": (c_i32, [c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_i64, c_ptr, c_ptr]),
 }
 
 REDUCE_SUM, REDUCE_PROD, REDUCE_MAX, REDUCE_MIN = 0, 1, 2, 3

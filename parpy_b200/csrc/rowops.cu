@@ -25,53 +25,21 @@ constexpr float kLog2e = 1.4426950408889634f;
 
 __device__ __forceinline__ float fast_exp(float x) { return pb::ex2_approx(x * kLog2e); }
 
-// ---------------------------------------------------------------- softmax ----
-// One warp per row; the row lives in registers (VEC float4 per lane).
-template <int VEC>
-__global__ void __launch_bounds__(256) softmax_warp_rows(const float *__restrict__ x,
-                                                         float *__restrict__ out, long long N, int M) {
-    const int lane = threadIdx.x & 31;
-    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= N) return;
-    const float4 *src = reinterpret_cast<const float4 *>(x + row * M);
-    float4 *dst = reinterpret_cast<float4 *>(out + row * M);
-    const int nvec = M >> 2;
-    float4 v[VEC];
-    float m = -INFINITY;
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) {
-        const int idx = lane + 32 * i;
-        if (idx < nvec) {
-            v[i] = __ldcs(src + idx);
-            m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
-        }
-    }
-    m = pb::warp_max(m);
-    float s = 0.0f;
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) {
-        const int idx = lane + 32 * i;
-        if (idx < nvec) {
-            v[i].x = fast_exp(v[i].x - m);
-            v[i].y = fast_exp(v[i].y - m);
-            v[i].z = fast_exp(v[i].z - m);
-            v[i].w = fast_exp(v[i].w - m);
-            s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
-        }
-    }
-    s = pb::warp_sum(s);
-    const float inv = 1.0f / s;
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) {
-        const int idx = lane + 32 * i;
-        if (idx < nvec) {
-            v[i].x *= inv;
-            v[i].y *= inv;
-            v[i].z *= inv;
-            v[i].w *= inv;
-            __stcs(dst + idx, v[i]);
-        }
-    }
+// ---------------------------------------------- softmax and its relatives ----
+// One family of single-read / single-write row kernels with three modes:
+//   kSoftmax    out = exp(x - max) / sum(exp(x - max))          (test/test_softmax.py:11-26)
+//   kNormalize  out = x / sum(x)                                 (test/test_normalize.py:7-15)
+//   kExpSum     out = exp(x), rowsum = sum(exp(x))               (test/test_sync.py:59-69)
+// `out` may alias `x` (normalize_rows and sum_exp_3d work in place).
+enum RowMode { kSoftmax = 0, kNormalize = 1, kExpSum = 2 };
+
+template <int MODE>
+__device__ __forceinline__ float row_map(float v, float m) {
+    return MODE == kSoftmax ? fast_exp(v - m) : MODE == kExpSum ? fast_exp(v) : v;
+}
+template <int MODE>
+__device__ __forceinline__ float row_finish(float v, float s, float inv) {
+    return MODE == kSoftmax ? v * inv : MODE == kNormalize ? v / s : v;
 }
 
 __device__ __forceinline__ float block_max(float v, float *s_red) {
@@ -96,11 +64,60 @@ __device__ __forceinline__ float block_sum(float v, float *s_red) {
     return r;
 }
 
+// One warp per row; the row lives in registers (VEC float4 per lane).
+template <int MODE, int VEC>
+__global__ void __launch_bounds__(256) rowmap_warp_rows(const float *x, float *out,
+                                                        float *__restrict__ rowsum, long long N, int M) {
+    const int lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= N) return;
+    const float4 *src = reinterpret_cast<const float4 *>(x + row * M);
+    float4 *dst = reinterpret_cast<float4 *>(out + row * M);
+    const int nvec = M >> 2;
+    float4 v[VEC];
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+        const int idx = lane + 32 * i;
+        if (idx < nvec) {
+            v[i] = __ldcs(src + idx);
+            if (MODE == kSoftmax) m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+        }
+    }
+    if (MODE == kSoftmax) m = pb::warp_max(m);
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+        const int idx = lane + 32 * i;
+        if (idx < nvec) {
+            v[i].x = row_map<MODE>(v[i].x, m);
+            v[i].y = row_map<MODE>(v[i].y, m);
+            v[i].z = row_map<MODE>(v[i].z, m);
+            v[i].w = row_map<MODE>(v[i].w, m);
+            s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+        }
+    }
+    s = pb::warp_sum(s);
+    const float inv = 1.0f / s;
+    if (MODE == kExpSum && lane == 0) rowsum[row] = s;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+        const int idx = lane + 32 * i;
+        if (idx < nvec) {
+            v[i].x = row_finish<MODE>(v[i].x, s, inv);
+            v[i].y = row_finish<MODE>(v[i].y, s, inv);
+            v[i].z = row_finish<MODE>(v[i].z, s, inv);
+            v[i].w = row_finish<MODE>(v[i].w, s, inv);
+            __stcs(dst + idx, v[i]);
+        }
+    }
+}
+
 // One CTA per row, the row held in registers (VEC float4 per thread): a single
 // global read and a single write for rows of up to blockDim * 4 * VEC floats.
-template <int VEC>
-__global__ void __launch_bounds__(1024) softmax_block_regs(const float *__restrict__ x,
-                                                           float *__restrict__ out, long long N, int M) {
+template <int MODE, int VEC>
+__global__ void __launch_bounds__(1024) rowmap_block_regs(const float *x, float *out,
+                                                          float *__restrict__ rowsum, long long N, int M) {
     __shared__ float s_red[32];
     const int nvec = M >> 2;
     for (long long row = blockIdx.x; row < N; row += gridDim.x) {
@@ -113,70 +130,125 @@ __global__ void __launch_bounds__(1024) softmax_block_regs(const float *__restri
             const int idx = threadIdx.x + blockDim.x * i;
             if (idx < nvec) {
                 v[i] = __ldcs(src + idx);
-                m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+                if (MODE == kSoftmax) m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
             }
         }
-        m = block_max(m, s_red);
+        if (MODE == kSoftmax) m = block_max(m, s_red);
         float s = 0.0f;
 #pragma unroll
         for (int i = 0; i < VEC; ++i) {
             const int idx = threadIdx.x + blockDim.x * i;
             if (idx < nvec) {
-                v[i].x = fast_exp(v[i].x - m);
-                v[i].y = fast_exp(v[i].y - m);
-                v[i].z = fast_exp(v[i].z - m);
-                v[i].w = fast_exp(v[i].w - m);
+                v[i].x = row_map<MODE>(v[i].x, m);
+                v[i].y = row_map<MODE>(v[i].y, m);
+                v[i].z = row_map<MODE>(v[i].z, m);
+                v[i].w = row_map<MODE>(v[i].w, m);
                 s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
             }
         }
         s = block_sum(s, s_red);
         const float inv = 1.0f / s;
+        if (MODE == kExpSum && threadIdx.x == 0) rowsum[row] = s;
 #pragma unroll
         for (int i = 0; i < VEC; ++i) {
             const int idx = threadIdx.x + blockDim.x * i;
             if (idx < nvec) {
-                v[i].x *= inv;
-                v[i].y *= inv;
-                v[i].z *= inv;
-                v[i].w *= inv;
+                v[i].x = row_finish<MODE>(v[i].x, s, inv);
+                v[i].y = row_finish<MODE>(v[i].y, s, inv);
+                v[i].z = row_finish<MODE>(v[i].z, s, inv);
+                v[i].w = row_finish<MODE>(v[i].w, s, inv);
                 __stcs(dst + idx, v[i]);
             }
         }
     }
 }
 
-// One CTA per row (grid-stride over rows). STAGE: keep the row in dynamic shared
-// memory between the passes; otherwise re-read it from global memory.
-template <bool STAGE>
-__global__ void __launch_bounds__(1024) softmax_block_rows(const float *__restrict__ x,
-                                                           float *__restrict__ out, long long N,
-                                                           long long M) {
+// One CTA per row (grid-stride over rows) for everything else: unaligned or very
+// long rows. STAGE: keep the row in dynamic shared memory between the passes;
+// otherwise re-read it from global memory (the input is only overwritten in the
+// last pass, so in-place use stays correct).
+template <int MODE, bool STAGE>
+__global__ void __launch_bounds__(1024) rowmap_block_rows(const float *x, float *out,
+                                                          float *__restrict__ rowsum, long long N,
+                                                          long long M) {
     extern __shared__ __align__(16) float s_row[];
     __shared__ float s_red[32];
     for (long long row = blockIdx.x; row < N; row += gridDim.x) {
         const float *src = x + row * M;
         float *dst = out + row * M;
         float m = -INFINITY;
-        for (long long i = threadIdx.x; i < M; i += blockDim.x) {
-            const float v = src[i];
-            if (STAGE) s_row[i] = v;
-            m = fmaxf(m, v);
+        if (MODE == kSoftmax || STAGE) {
+            for (long long i = threadIdx.x; i < M; i += blockDim.x) {
+                const float v = src[i];
+                if (STAGE) s_row[i] = v;
+                m = fmaxf(m, v);
+            }
+            if (MODE == kSoftmax) m = block_max(m, s_red);
+            else __syncthreads();
         }
-        m = block_max(m, s_red);
         float s = 0.0f;
         for (long long i = threadIdx.x; i < M; i += blockDim.x) {
-            const float e = fast_exp((STAGE ? s_row[i] : src[i]) - m);
+            const float e = row_map<MODE>(STAGE ? s_row[i] : src[i], m);
             if (STAGE) s_row[i] = e;
             s += e;
         }
         s = block_sum(s, s_red);
         const float inv = 1.0f / s;
+        if (MODE == kExpSum && threadIdx.x == 0) rowsum[row] = s;
         for (long long i = threadIdx.x; i < M; i += blockDim.x) {
-            const float e = STAGE ? s_row[i] : fast_exp(src[i] - m);
-            dst[i] = e * inv;
+            const float e = STAGE ? s_row[i] : row_map<MODE>(src[i], m);
+            dst[i] = row_finish<MODE>(e, s, inv);
         }
         __syncthreads();
     }
+}
+
+template <int MODE>
+int32_t launch_rowmap(const float *x, float *out, float *rowsum, int64_t N, int64_t M, cudaStream_t stream,
+                      const char *what) {
+    PB_REQUIRE(N >= 0 && M >= 0, "%s: negative shape (%lld, %lld)", what, (long long)N, (long long)M);
+    if (N == 0 || M == 0) return PB_OK;
+    PB_REQUIRE(x && out && (MODE != kExpSum || rowsum), "%s: null pointer", what);
+    pb::DeviceInfo dev;
+    int32_t rc = pb::device_info(&dev);
+    if (rc) return rc;
+    const bool vec_ok = (M % 4 == 0) && pb::aligned16(x) && pb::aligned16(out);
+    if (vec_ok && M <= 2048) {
+        const int wpb = 4;
+        const long long blocks = (N + wpb - 1) / wpb;
+        PB_REQUIRE(blocks <= 0x7fffffffLL, "%s: too many rows", what);
+        const int nvec = (int)(M / 4);
+        if (nvec <= 32 * 2) rowmap_warp_rows<MODE, 2><<<(unsigned)blocks, wpb * 32, 0, stream>>>(x, out, rowsum, N, (int)M);
+        else if (nvec <= 32 * 4) rowmap_warp_rows<MODE, 4><<<(unsigned)blocks, wpb * 32, 0, stream>>>(x, out, rowsum, N, (int)M);
+        else if (nvec <= 32 * 8) rowmap_warp_rows<MODE, 8><<<(unsigned)blocks, wpb * 32, 0, stream>>>(x, out, rowsum, N, (int)M);
+        else rowmap_warp_rows<MODE, 16><<<(unsigned)blocks, wpb * 32, 0, stream>>>(x, out, rowsum, N, (int)M);
+        PB_CUDA(cudaGetLastError());
+        return PB_OK;
+    }
+    if (vec_ok && M <= 32768) {
+        // row in registers of one CTA: threads x VEC float4
+        const int nvec = (int)(M / 4);
+        const int threads = nvec <= 2048 ? 256 : nvec <= 4096 ? 512 : 1024;
+        const int per = (nvec + threads - 1) / threads;
+        const long long g = std::min<long long>(N, (long long)dev.sm_count * (2048 / threads) * 2);
+        if (per <= 2) rowmap_block_regs<MODE, 2><<<(unsigned)g, threads, 0, stream>>>(x, out, rowsum, N, (int)M);
+        else if (per <= 4) rowmap_block_regs<MODE, 4><<<(unsigned)g, threads, 0, stream>>>(x, out, rowsum, N, (int)M);
+        else rowmap_block_regs<MODE, 8><<<(unsigned)g, threads, 0, stream>>>(x, out, rowsum, N, (int)M);
+        PB_CUDA(cudaGetLastError());
+        return PB_OK;
+    }
+    const long long grid = std::min<long long>(N, 8LL * dev.sm_count);
+    const size_t smem = (size_t)M * sizeof(float);
+    const int threads = M >= 4096 ? 1024 : 256;
+    if (smem <= 192 * 1024) {
+        PB_CUDA(cudaFuncSetAttribute(rowmap_block_rows<MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     192 * 1024));
+        rowmap_block_rows<MODE, true><<<(unsigned)grid, threads, smem, stream>>>(x, out, rowsum, N, M);
+    } else {
+        rowmap_block_rows<MODE, false><<<(unsigned)grid, threads, 0, stream>>>(x, out, rowsum, N, M);
+    }
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
 }
 
 // ------------------------------------------------------------- reductions ----
@@ -448,50 +520,20 @@ int32_t launch_reduce(const float *x, float *out, long long N, long long M, cuda
 extern "C" {
 
 int32_t parpy_b200_softmax(const float *x, int64_t N, int64_t M, float *out, void *stream_) {
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    PB_REQUIRE(N >= 0 && M >= 0, "softmax: negative shape (%lld, %lld)", (long long)N, (long long)M);
-    if (N == 0 || M == 0) return PB_OK;
-    PB_REQUIRE(x && out, "softmax: null pointer");
-    pb::DeviceInfo dev;
-    int32_t rc = pb::device_info(&dev);
-    if (rc) return rc;
-    const bool vec_ok = (M % 4 == 0) && pb::aligned16(x) && pb::aligned16(out);
-    if (vec_ok && M <= 2048) {
-        const int wpb = 4;
-        const long long blocks = (N + wpb - 1) / wpb;
-        PB_REQUIRE(blocks <= 0x7fffffffLL, "softmax: too many rows");
-        const int nvec = (int)(M / 4);
-        if (nvec <= 32 * 2) softmax_warp_rows<2><<<(unsigned)blocks, wpb * 32, 0, stream>>>(x, out, N, (int)M);
-        else if (nvec <= 32 * 4) softmax_warp_rows<4><<<(unsigned)blocks, wpb * 32, 0, stream>>>(x, out, N, (int)M);
-        else if (nvec <= 32 * 8) softmax_warp_rows<8><<<(unsigned)blocks, wpb * 32, 0, stream>>>(x, out, N, (int)M);
-        else softmax_warp_rows<16><<<(unsigned)blocks, wpb * 32, 0, stream>>>(x, out, N, (int)M);
-        PB_CUDA(cudaGetLastError());
-        return PB_OK;
-    }
-    if (vec_ok && M <= 32768) {
-        // row in registers of one CTA: threads x VEC float4
-        const int nvec = (int)(M / 4);
-        const int threads = nvec <= 2048 ? 256 : nvec <= 4096 ? 512 : 1024;
-        const int per = (nvec + threads - 1) / threads;
-        const long long g = std::min<long long>(N, (long long)dev.sm_count * (2048 / threads) * 2);
-        if (per <= 2) softmax_block_regs<2><<<(unsigned)g, threads, 0, stream>>>(x, out, N, (int)M);
-        else if (per <= 4) softmax_block_regs<4><<<(unsigned)g, threads, 0, stream>>>(x, out, N, (int)M);
-        else softmax_block_regs<8><<<(unsigned)g, threads, 0, stream>>>(x, out, N, (int)M);
-        PB_CUDA(cudaGetLastError());
-        return PB_OK;
-    }
-    const long long grid = std::min<long long>(N, 8LL * dev.sm_count);
-    const size_t smem = (size_t)M * sizeof(float);
-    const int threads = M >= 4096 ? 1024 : 256;
-    if (smem <= 192 * 1024) {
-        PB_CUDA(cudaFuncSetAttribute(softmax_block_rows<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     192 * 1024));
-        softmax_block_rows<true><<<(unsigned)grid, threads, smem, stream>>>(x, out, N, M);
-    } else {
-        softmax_block_rows<false><<<(unsigned)grid, threads, 0, stream>>>(x, out, N, M);
-    }
-    PB_CUDA(cudaGetLastError());
-    return PB_OK;
+    return launch_rowmap<kSoftmax>(x, out, nullptr, N, M, static_cast<cudaStream_t>(stream_), "softmax");
+}
+
+int32_t parpy_b200_normalize_rows(float *t, int64_t nrows, int64_t ncols, void *stream_) {
+    return launch_rowmap<kNormalize>(t, t, nullptr, nrows, ncols, static_cast<cudaStream_t>(stream_),
+                                     "normalize_rows");
+}
+
+int32_t normalize_rows(float *t, int64_t nrows, int64_t ncols) {
+    return parpy_b200_normalize_rows(t, nrows, ncols, nullptr);
+}
+
+int32_t parpy_b200_sum_exp_rows(float *x, int64_t nrows, int64_t ncols, float *out, void *stream_) {
+    return launch_rowmap<kExpSum>(x, x, out, nrows, ncols, static_cast<cudaStream_t>(stream_), "sum_exp");
 }
 
 int32_t softmax(float *x, int64_t N, int64_t M, float *out) {

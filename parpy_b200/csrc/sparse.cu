@@ -23,11 +23,7 @@
 namespace {
 
 // ------------------------------------------------------------------- SpMV ----
-constexpr int kSpmvThreads = 256;
-constexpr int kSpmvPerThread = 8;
-constexpr int kSpmvChunk = kSpmvThreads * kSpmvPerThread;  // non-zeros per CTA
-constexpr int kLongRow = 64;                                // segments above this get a warp
-constexpr int kMaxLong = kSpmvChunk / kLongRow;
+constexpr int kLongRow = 64;   // segments above this get a warp
 
 // first_row[c] = the row that contains non-zero c * kSpmvChunk, i.e. the largest
 // r with rows[r] <= c * kSpmvChunk. One thread per row writes the entries of the
@@ -35,7 +31,7 @@ constexpr int kMaxLong = kSpmvChunk / kLongRow;
 // built with one coalesced pass over the row pointers and no search; the pass
 // also leaves the row pointers in L2 for the main kernel.
 __global__ void spmv_first_rows(const int64_t *__restrict__ rows, long long nrows,
-                                int *__restrict__ first_row) {
+                                int *__restrict__ first_row, int kSpmvChunk) {
     const long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= nrows) return;
     const long long start = __ldg(rows + r), end = __ldg(rows + r + 1);
@@ -44,6 +40,7 @@ __global__ void spmv_first_rows(const int64_t *__restrict__ rows, long long nrow
         first_row[c] = (int)r;
 }
 
+template <int kSpmvThreads, int kSpmvPerThread>
 __global__ void __launch_bounds__(kSpmvThreads) spmv_chunks(const float *__restrict__ values,
                                                             const int64_t *__restrict__ cols,
                                                             const int64_t *__restrict__ rows,
@@ -51,6 +48,8 @@ __global__ void __launch_bounds__(kSpmvThreads) spmv_chunks(const float *__restr
                                                             const float *__restrict__ x,
                                                             float *__restrict__ y,
                                                             const int *__restrict__ first_row) {
+    constexpr int kSpmvChunk = kSpmvThreads * kSpmvPerThread;   // non-zeros per CTA
+    constexpr int kMaxLong = kSpmvChunk / kLongRow;
     __shared__ float s_prod[kSpmvChunk];
     __shared__ int s_nlong;
     __shared__ long long s_long_row[kMaxLong];
@@ -210,6 +209,45 @@ __global__ void __launch_bounds__(256) sddmm_nnz(const float *__restrict__ A, co
     }
 }
 
+
+// ------------------------------------------------------------------- SpMM ----
+// C[i, j] += sum over the non-zeros a of row i of values[a] * B[cols[a], j]
+// (test/test_spmm.py:16-24). The reference gives every cell (i, j) its own
+// 32-thread block; here a CTA covers one row and a contiguous run of columns, so
+// every non-zero turns into one coalesced read of a B row segment.
+template <bool VEC>
+__global__ void __launch_bounds__(128) spmm_rows(const float *__restrict__ values,
+                                                 const int64_t *__restrict__ rows,
+                                                 const int64_t *__restrict__ cols,
+                                                 const float *__restrict__ B, long long K,
+                                                 float *__restrict__ C) {
+    const long long i = blockIdx.y;
+    const long long a0 = __ldg(rows + i), a1 = __ldg(rows + i + 1);
+    if (VEC) {
+        const long long j = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+        if (j >= K) return;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (long long a = a0; a < a1; ++a) {
+            const float v = __ldg(values + a);
+            const float4 b = __ldg(reinterpret_cast<const float4 *>(B + __ldg(cols + a) * K + j));
+            acc.x = fmaf(v, b.x, acc.x);
+            acc.y = fmaf(v, b.y, acc.y);
+            acc.z = fmaf(v, b.z, acc.z);
+            acc.w = fmaf(v, b.w, acc.w);
+        }
+        float4 *dst = reinterpret_cast<float4 *>(C + i * K + j);
+        float4 c = *dst;
+        c.x += acc.x; c.y += acc.y; c.z += acc.z; c.w += acc.w;
+        *dst = c;
+    } else {
+        const long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+        if (j >= K) return;
+        float acc = 0.f;
+        for (long long a = a0; a < a1; ++a) acc = fmaf(__ldg(values + a), __ldg(B + __ldg(cols + a) * K + j), acc);
+        C[i * K + j] += acc;
+    }
+}
+
 int32_t sddmm_common(const float *A, const float *B, const int64_t *rows, const int64_t *cols,
                      const float *cvalues, float *D, int64_t K, int64_t ncols, int64_t nnz,
                      double alpha, double beta, cudaStream_t stream) {
@@ -248,15 +286,25 @@ int32_t parpy_b200_spmv(const float *values, const int64_t *rows, const int64_t 
     PB_REQUIRE(nrows >= 0 && nnz >= 0, "spmv: negative size (nrows=%lld, nnz=%lld)", (long long)nrows, (long long)nnz);
     if (nrows == 0 || nnz == 0) return PB_OK;
     PB_REQUIRE(values && rows && cols && x && y, "spmv: null pointer");
-    const long long blocks = (nnz + kSpmvChunk - 1) / kSpmvChunk;
+    // CTA shape: 128 threads x 16 non-zeros measured best on B200 (the kernel is bound by the
+    // L2 sector traffic of the x gathers, so the differences are a few percent)
+    int cfg = 3;
+    if (const char *env = getenv("PARPY_B200_SPMV_CFG")) cfg = atoi(env);
+    const int threads = cfg == 2 ? 512 : cfg == 3 ? 128 : 256;
+    const int per = cfg == 1 || cfg == 3 ? 16 : 8;
+    const int chunk = threads * per;
+    const long long blocks = (nnz + chunk - 1) / chunk;
     PB_REQUIRE(blocks <= 0x7fffffffLL && nrows <= 0x7fffffffLL, "spmv: matrix too large");
     void *ws = nullptr;
     int32_t rc = pb::workspace((size_t)blocks * sizeof(int), &ws, stream, 3);
     if (rc) return rc;
     int *first_row = static_cast<int *>(ws);
-    spmv_first_rows<<<(unsigned)((nrows + 255) / 256), 256, 0, stream>>>(rows, nrows, first_row);
+    spmv_first_rows<<<(unsigned)((nrows + 255) / 256), 256, 0, stream>>>(rows, nrows, first_row, chunk);
     PB_CUDA(cudaGetLastError());
-    spmv_chunks<<<(unsigned)blocks, kSpmvThreads, 0, stream>>>(values, cols, rows, nrows, nnz, x, y, first_row);
+    if (cfg == 1) spmv_chunks<256, 16><<<(unsigned)blocks, 256, 0, stream>>>(values, cols, rows, nrows, nnz, x, y, first_row);
+    else if (cfg == 2) spmv_chunks<512, 8><<<(unsigned)blocks, 512, 0, stream>>>(values, cols, rows, nrows, nnz, x, y, first_row);
+    else if (cfg == 3) spmv_chunks<128, 16><<<(unsigned)blocks, 128, 0, stream>>>(values, cols, rows, nrows, nnz, x, y, first_row);
+    else spmv_chunks<256, 8><<<(unsigned)blocks, 256, 0, stream>>>(values, cols, rows, nrows, nnz, x, y, first_row);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }
@@ -271,6 +319,28 @@ int32_t spmv_row(int64_t *cols, int64_t nrows, int64_t *rows, float *values, flo
     PB_CUDA(cudaMemcpyAsync(&nnz, rows + nrows, sizeof(nnz), cudaMemcpyDeviceToHost, 0));
     PB_CUDA(cudaStreamSynchronize(0));
     return parpy_b200_spmv(values, rows, cols, nrows, nnz, x, y, nullptr);
+}
+
+
+int32_t parpy_b200_spmm(const float *values, const int64_t *rows, const int64_t *cols, int64_t nrows,
+                        const float *B, int64_t ncols, float *C, void *stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    PB_REQUIRE(nrows >= 0 && ncols >= 0, "spmm: negative size");
+    if (nrows == 0 || ncols == 0) return PB_OK;
+    PB_REQUIRE(values && rows && cols && B && C, "spmm: null pointer");
+    PB_REQUIRE(nrows <= 65535, "spmm: more than 65535 rows are not supported");
+    const bool vec = (ncols % 4 == 0) && pb::aligned16(B) && pb::aligned16(C);
+    const long long per_block = vec ? 128 * 4 : 128;
+    dim3 grid((unsigned)((ncols + per_block - 1) / per_block), (unsigned)nrows, 1);
+    if (vec) spmm_rows<true><<<grid, 128, 0, stream>>>(values, rows, cols, B, ncols, C);
+    else spmm_rows<false><<<grid, 128, 0, stream>>>(values, rows, cols, B, ncols, C);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+int32_t spmm_cell(int64_t *A_cols, int64_t A_nrows, int64_t *A_rows, float *A_values, int64_t B_ncols,
+                  float *B_values, float *C) {
+    return parpy_b200_spmm(A_values, A_rows, A_cols, A_nrows, B_values, B_ncols, C, nullptr);
 }
 
 int32_t parpy_b200_sddmm_decompress_csr(const int64_t *crows, int64_t *rows_out, int64_t N, void *stream_) {

@@ -60,3 +60,18 @@ def sum_max(x):
                                           P(out.data_ptr() + 4), P(torch.cuda.current_stream().cuda_stream))
     _native.check(rc, "sum_max")
     return out
+
+
+@jit
+def normalize_rows(t, nrows, ncols):
+    """t[i,:] /= sum(t[i,:]), in place"""
+
+
+@jit
+def sum_exp_3d(x, N, M, out):
+    """x = exp(x) in place; out[i,j] = sum(x[i,j,:])"""
+
+
+@jit
+def spmm_cell(A, B, C):
+    """C[i,j] += sum over row i's non-zeros of A.values[a] * B.values[A.cols[a], j]"""

@@ -323,3 +323,50 @@ register(OpSpec("parpy_sddmm_coo_kernel", ("A", "B", "C", "D", "alpha", "beta"),
                 {"A": "in", "B": "in", "D": "out",
                  "C": {"rows": "in", "cols": "in", "values": "in", "nnz": "in"}},
                 _sddmm_coo_call, doc="benchmarks/sddmm.py:63-70"))
+
+
+# ---- row normalisation, exp + row sum, SpMM (test_normalize.py, test_sync.py, test_spmm.py) ----
+def _normalize_call(opts, t, nrows, ncols):
+    import torch
+    tt = tensor(t, "t", torch.float32, 2)
+    n, m = int(scalar(nrows, "nrows")), int(scalar(ncols, "ncols"))
+    if tuple(tt.shape) != (n, m):
+        raise RuntimeError(f"normalize_rows: t {tuple(tt.shape)} does not match nrows={n}, ncols={m}")
+    _native.check(_native.lib().parpy_b200_normalize_rows(ptr(tt), n, m, current_stream()), "normalize_rows")
+
+
+def _sum_exp_3d_call(opts, x, N, M, out):
+    import torch
+    xt = tensor(x, "x", torch.float32, 3)
+    ot = tensor(out, "out", torch.float32, 2)
+    n, m = int(scalar(N, "N")), int(scalar(M, "M"))
+    if tuple(xt.shape[:2]) != (n, m) or tuple(ot.shape) != (n, m):
+        raise RuntimeError(f"sum_exp_3d: x {tuple(xt.shape)} / out {tuple(ot.shape)} do not match N={n}, M={m}")
+    _native.check(_native.lib().parpy_b200_sum_exp_rows(ptr(xt), n * m, xt.shape[2], ptr(ot), current_stream()),
+                  "sum_exp_3d")
+
+
+def _spmm_call(opts, A, B, C):
+    import torch
+    values = tensor(A["values"], "A['values']", torch.float32, 1)
+    rows = tensor(A["rows"], "A['rows']", torch.int64, 1)
+    cols = tensor(A["cols"], "A['cols']", torch.int64, 1)
+    nrows = int(scalar(A["nrows"], "A['nrows']"))
+    Bv = tensor(B["values"], "B['values']", torch.float32, 2)
+    ncols = int(scalar(B["ncols"], "B['ncols']"))
+    Ct = tensor(C, "C", torch.float32, 2)
+    if rows.shape[0] != nrows + 1 or Bv.shape[1] != ncols or tuple(Ct.shape) != (nrows, ncols):
+        raise RuntimeError(f"spmm_cell: rows {tuple(rows.shape)}, B {tuple(Bv.shape)}, C {tuple(Ct.shape)} "
+                           f"do not match nrows={nrows}, ncols={ncols}")
+    _native.check(_native.lib().parpy_b200_spmm(ptr(values), ptr(rows), ptr(cols), nrows, ptr(Bv), ncols,
+                                                ptr(Ct), current_stream()), "spmm_cell")
+
+
+register(OpSpec("normalize_rows", ("t", "nrows", "ncols"), {"t": "inout"}, _normalize_call,
+                doc="test/test_normalize.py:7-15"))
+register(OpSpec("sum_exp_3d", ("x", "N", "M", "out"), {"x": "inout", "out": "out"}, _sum_exp_3d_call,
+                doc="test/test_sync.py:59-69"))
+register(OpSpec("spmm_cell", ("A", "B", "C"),
+                {"A": {"values": "in", "rows": "in", "cols": "in", "nrows": "in"},
+                 "B": {"values": "in", "ncols": "in"}, "C": "inout"},
+                _spmm_call, doc="test/test_spmm.py:16-24"))

@@ -152,3 +152,22 @@ def test_synthetic_generators_are_seeded_and_shaped():
     lens = r["lens"]
     assert lens.min() >= 10 and lens.max() <= 40 and int(r["maxlen"]) == int(lens.max())
     assert synthetic.state_steps(h1, s) == 16384 * 200000
+
+
+def test_print_compiled_returns_a_self_contained_translation_unit(tmp_path, monkeypatch):
+    # python/parpy/__init__.py:177-199; test/test_softmax.py:57-66 asserts len(s) != 0
+    import shutil
+    from parpy_b200 import kernels, source
+    src = parpy.print_compiled(kernels.softmax, [])
+    assert len(src) != 0 and "rowmap_warp_rows" in src and 'extern "C"' in src
+    assert '#include "' not in src                      # local includes are inlined
+    for op in ("forward_kernel", "spmv_row", "sum_rows", "parpy_sddmm_coo_kernel", "spmm_cell"):
+        assert len(source.kernel_source(op)) > 1000
+    if shutil.which("nvcc"):
+        monkeypatch.setenv("PARPY_B200_CACHE", str(tmp_path))
+        lib = source.compile_source(src)                # cross-compiles without a GPU
+        import ctypes
+        assert hasattr(ctypes.CDLL(lib), "softmax")
+        assert source.compile_source(src) == lib        # cached by content
+        with pytest.raises(RuntimeError, match="Compilation of CUDA source failed"):
+            source.compile_source("this is not CUDA")

@@ -236,3 +236,80 @@ def test_sddmm_decompress_entry(native, oracle_mod):
     rows_h = np.zeros(C["nnz"], dtype=np.int64)
     kernels.parpy_sddmm_decompress_csr(C["crows"].numpy(), rows_h, 1000, opts=parpy.par({}))
     assert np.array_equal(rows_h, oracle_mod.sddmm_decompress(C["crows"]))
+
+
+# ---- normalize_rows, sum_exp_3d, spmm_cell ----------------------------------------------------------
+@pytest.mark.parametrize("shape", [(1, 1024), (256, 1024), (7, 33), (5, 4100), (3, 40000), (2, 70001)])
+def test_normalize_rows_like_reference_test(oracle_mod, shape):
+    # test/test_normalize.py:17-45: ones (and positive random rows), compared with L1 normalisation
+    t = torch.ones(shape, dtype=torch.float32)
+    out = t.clone()
+    kernels.normalize_rows(out, shape[0], shape[1], opts=opts(i=parpy.threads(256), j1=parpy.threads(128).reduce()))
+    assert torch.allclose(torch.nn.functional.normalize(t, p=1, dim=1), out, 1e-5)
+    r = torch.rand(shape, generator=torch.Generator().manual_seed(9)) + 0.05
+    dev = r.cuda()
+    kernels.normalize_rows(dev, shape[0], shape[1], opts=parpy.par({}))
+    assert max_rel(dev.cpu().numpy(), oracle_mod.normalize_rows(r)) <= 1e-5
+
+
+@pytest.mark.parametrize("dims", [(10, 20, 30), (4, 8, 1024), (3, 5, 8192), (2, 2, 50000)])
+def test_sum_exp_3d_like_reference_test(oracle_mod, dims):
+    # test/test_sync.py:71-80
+    N, M, K = dims
+    x = np.random.RandomState(1).randn(N, M, K).astype(np.float32)
+    ref_x, ref_out = oracle_mod.sum_exp_rows(x.reshape(N * M, K))
+    out = np.zeros((N, M), dtype=np.float32)
+    kernels.sum_exp_3d(x, N, M, out, opts=opts(N=parpy.threads(N), M=parpy.threads(M), K_1=parpy.threads(32),
+                                               K_2=parpy.threads(64)))
+    assert np.allclose(out.reshape(-1), ref_out, atol=1e-5, rtol=1e-5)
+    assert max_rel(x.reshape(N * M, K), ref_x) <= 1e-5          # x was exponentiated in place
+
+
+@pytest.mark.parametrize("N,M,K", [(1024, 256, 512), (100, 77, 33), (5, 9, 4)])
+def test_spmm_like_reference_test(native, oracle_mod, N, M, K):
+    # test/test_spmm.py:53-87: uniform random CSR at 1 % (denser for the tiny cases), dense B
+    A = synthetic.zipf_csr(N, M, mean_nnz=max(2, M // 100), cap=M, seed=N)
+    B = torch.randn(M, K, generator=torch.Generator().manual_seed(4))
+    C0 = torch.randn(N, K, generator=torch.Generator().manual_seed(5))      # C is accumulated into
+    exp = oracle_mod.spmm(A, B, C0.numpy())
+    Ad = {"values": A["values"], "rows": A["rows"], "cols": A["cols"], "nrows": N}
+    C = C0.clone()
+    kernels.spmm_cell(Ad, {"values": B, "ncols": K}, C, opts=opts(i=parpy.threads(N), j=parpy.threads(K),
+                                                                  aidx=parpy.threads(32).reduce()))
+    assert np.allclose(C.numpy(), exp, atol=1e-5, rtol=1e-5)
+    # reference-shaped C entry on device memory
+    d = {k: v.cuda() for k, v in A.items() if isinstance(v, torch.Tensor)}
+    Bd, Cd = B.cuda(), C0.cuda()
+    rc = native.lib().spmm_cell(P(d["cols"].data_ptr()), N, P(d["rows"].data_ptr()), P(d["values"].data_ptr()), K,
+                                P(Bd.data_ptr()), P(Cd.data_ptr()))
+    torch.cuda.synchronize()
+    assert rc == 0 and np.allclose(Cd.cpu().numpy(), exp, atol=1e-5, rtol=1e-5)
+
+
+def test_compile_string_round_trip(oracle_mod, tmp_path, monkeypatch):
+    # the reference's workflow: print the CUDA for a function, edit it, compile the string, call it
+    monkeypatch.setenv("PARPY_B200_CACHE", str(tmp_path))
+    src = parpy.print_compiled(kernels.softmax, [])
+    edited = src.replace("// parpy_b200: amalgamated source", "// edited copy of the amalgamated source", 1)
+    fn = parpy.compile_string("softmax", edited)
+    x = torch.randn((64, 512), generator=torch.Generator().manual_seed(3))
+    out = torch.zeros_like(x)
+    fn(x, 64, 512, out)
+    assert max_rel(out.numpy(), oracle_mod.softmax(x)) <= 1e-4
+    # a small hand-written kernel with a dict argument, flattened in sorted-key order
+    code = r"""
+    #include <cstdint>
+    __global__ void k(const float* a, float s, float* y, int64_t n) {
+        int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+        if (i < n) y[i] = s * a[i] + y[i];
+    }
+    extern "C" int32_t scale_add(float* a, float s, float* y, int64_t n) {
+        k<<<(unsigned)((n + 255) / 256), 256>>>(a, s, y, n);
+        return (int32_t)cudaGetLastError();
+    }
+    """
+    f2 = parpy.compile_string("scale_add", code)
+    a = np.arange(1000, dtype=np.float32)
+    y = np.ones(1000, dtype=np.float32)
+    f2({"a": a, "s": np.float32(2.0)}, y, 1000)
+    assert np.array_equal(y, 2.0 * a + 1.0)

@@ -59,3 +59,18 @@ def test_zipf_csr_generator_shape():
     assert lens.max() <= 4096 and abs(lens.mean() - 32) < 1.0
     assert (lens >= 1024).sum() > 0 and np.median(lens) < 16    # heavy tail next to short rows
     assert A["cols"].min() >= 0 and A["cols"].max() < 200000
+
+
+def test_normalize_sum_exp_and_spmm_oracles():
+    # test/test_normalize.py:26-31, test/test_sync.py:71-80, test/test_spmm.py:80-87
+    t = torch.rand((17, 100), generator=torch.Generator().manual_seed(3)) + 0.1
+    assert torch.allclose(torch.nn.functional.normalize(t, p=1, dim=1), torch.from_numpy(oracle.normalize_rows(t)), 1e-5)
+    x = np.random.RandomState(5).randn(10 * 20, 30).astype(np.float32)
+    ex, sums = oracle.sum_exp_rows(x)
+    assert np.allclose(ex, np.exp(x), rtol=1e-6) and np.allclose(sums, np.exp(x).sum(axis=1), atol=1e-5, rtol=1e-6)
+    A = synthetic.zipf_csr(64, 48, mean_nnz=3, cap=20, seed=8)
+    B = torch.randn(48, 40, generator=torch.Generator().manual_seed(2))
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        dense = torch.sparse_csr_tensor(A["rows"], A["cols"], A["values"], (64, 48)).to_dense()
+    assert np.allclose(oracle.spmm(A, B, np.zeros((64, 40), np.float32)), (dense @ B).numpy(), atol=1e-5)
