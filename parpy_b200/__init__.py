@@ -167,15 +167,25 @@ def compile_string(fun_name, code, opts=None):
     extra = tuple(getattr(opts, "extra_flags", ()) or ()) if opts is not None else ()
     fn = source.wrapper(source.compile_source(code, extra), fun_name)
 
+    def stage(arg, where, staged):
+        # 0-d host arrays travel by value in their own dtype (python/parpy/compile.py:157-170)
+        if not isinstance(arg, (int, float, dict)) and not hasattr(arg, "__cuda_array_interface__") and \
+                (hasattr(arg, "__array_interface__") or hasattr(arg, "__array__")):
+            from .buffer import _extract_array_interface, _host_view
+            shape, dtype, _ = _extract_array_interface(arg)
+            if len(shape) == 0:
+                return source.Scalar(dtype.to_ctype(), _host_view(arg).reshape(()).item())
+        return _stage_one(arg, "inout", where, staged)
+
     @functools.wraps(fn)
     def inner(*args):
         staged = []
         dev_args = []
         for i, arg in enumerate(args):
             if isinstance(arg, dict):
-                dev_args.append({k: _stage_one(v, "inout", f"#{i+1}[\"{k}\"]", staged) for k, v in arg.items()})
+                dev_args.append({k: stage(v, f"#{i+1}[\"{k}\"]", staged) for k, v in arg.items()})
             else:
-                dev_args.append(_stage_one(arg, "inout", f"#{i+1}", staged))
+                dev_args.append(stage(arg, f"#{i+1}", staged))
         try:
             fn(*dev_args)
         except Exception:

@@ -973,21 +973,25 @@ struct Plan {
 
 // Picks (k-mers per thread, threads per CTA, CTAs per cluster) with
 // K = kpt*nt*cs, or returns false when only the streaming kernel applies.
-// `allow_split` permits the register/shared split layout (factored form only).
-bool make_plan(long long K, Plan *pl, bool allow_split) {
+// `allow_split` permits the register/shared split layout (factored log form
+// only); `need_kpt4` is set by the scaled kernel, which owns 4 k-mers per thread.
+// Shapes for K <= 1024 follow measurements on the 100-sequence 5-mer workload:
+// small CTAs in clusters of 4 spread one sequence over several SMs.
+bool make_plan(long long K, Plan *pl, bool allow_split, bool need_kpt4 = false) {
     if (K < 4 || (K & (K - 1)) != 0) return false;  // K = 4^k
-    long long kpt = K >= 1024 ? 4 : 1;
-    long long nt_max = kpt == 4 ? 512 : 1024;
+    long long kpt = (K >= 4096 || need_kpt4) ? 4 : 1;
+    if (need_kpt4 && K < 1024) return false;
+    long long nt_max = kpt == 4 ? (K <= 1024 ? 64 : 512) : (K == 1024 ? 256 : 1024);
     if (const char *env = getenv("PARPY_B200_FWD_KPT")) {
         const int v = atoi(env);
-        if ((v == 1 || v == 4) && K >= 16) {
+        if ((v == 1 || v == 4) && K >= 16 && !(need_kpt4 && v != 4)) {
             kpt = v;
             nt_max = kpt == 4 ? 512 : 1024;
         }
     }
     if (const char *env = getenv("PARPY_B200_FWD_NT")) {
         const long long w = atoll(env);
-        if (w >= 32 && w <= nt_max && (w & (w - 1)) == 0) nt_max = w;
+        if (w >= 32 && w <= (kpt == 4 ? 512 : 1024) && (w & (w - 1)) == 0) nt_max = w;
     }
     const long long threads = K / kpt;
     if (threads < 32) return false;  // whole warps only; tiny state spaces stream
@@ -1114,7 +1118,7 @@ int32_t forward_impl(float gamma, const float *initial_prob, int64_t num_states,
                                     stream));
 
     Plan pl;
-    const bool resident = !streaming_forced && make_plan(K, &pl, !five && !scaled);
+    const bool resident = !streaming_forced && make_plan(K, &pl, !five && !scaled, scaled);
     PB_REQUIRE(!scaled || (resident && pl.kpt == 4),
                "forward: the scaled kernel needs at least 1024 k-mers (num_states=%lld)", (long long)num_states);
     pl.scaled = scaled;

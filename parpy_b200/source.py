@@ -91,6 +91,14 @@ def clear_cache():
         shutil.rmtree(cache)
 
 
+class Scalar:
+    """A 0-d array argument: passed by value in the C type of its dtype."""
+
+    def __init__(self, ctype, value):
+        self.ctype = ctype
+        self.value = value
+
+
 def wrapper(libpath, name):
     """A Python callable for ``extern "C" int32_t name(...)`` in ``libpath`` that
     flattens its arguments the way the reference does: dictionaries expanded in
@@ -108,6 +116,8 @@ def wrapper(libpath, name):
             return ctypes.c_int64, int(arg)
         if isinstance(arg, float):
             return ctypes.c_double, arg
+        if isinstance(arg, Scalar):
+            return arg.ctype, arg.value
         if isinstance(arg, Buffer):
             if len(arg.shape) == 0:
                 return arg.dtype.to_ctype(), arg.numpy().item()

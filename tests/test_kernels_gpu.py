@@ -311,5 +311,5 @@ def test_compile_string_round_trip(oracle_mod, tmp_path, monkeypatch):
     f2 = parpy.compile_string("scale_add", code)
     a = np.arange(1000, dtype=np.float32)
     y = np.ones(1000, dtype=np.float32)
-    f2({"a": a, "s": np.float32(2.0)}, y, 1000)
+    f2({"a": a, "s": np.array(2.0, dtype=np.float32)}, y, 1000)
     assert np.array_equal(y, 2.0 * a + 1.0)
