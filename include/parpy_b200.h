@@ -17,6 +17,12 @@
  *   2. parpy_b200_* entries take the shapes the reference bakes in at JIT time
  *      as explicit arguments, plus a stream (a cudaStream_t passed as void*;
  *      NULL = legacy default stream) and option flags.
+ *
+ * Concurrency: entry points may be called from several host threads and on
+ * several streams. Library-owned scratch is kept per (device, stream). The
+ * forward kernels read 16 per-call constants from one of 16 constant-memory
+ * slots handed out round-robin: more than 16 forward calls in flight at once on
+ * different streams of one device would share a slot.
  */
 #ifndef PARPY_B200_H
 #define PARPY_B200_H

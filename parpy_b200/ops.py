@@ -91,6 +91,11 @@ def tensor(v, what, dtype=None, ndim=None, allow_none=False):
     if not isinstance(v, Buffer):
         raise TypeError(f"{what}: expected an array, got {type(v)}")
     t = v.buf
+    if t.is_cuda:
+        import torch
+        if t.device.index != torch.cuda.current_device():
+            raise RuntimeError(f"{what}: array lives on cuda:{t.device.index} but the current device is "
+                               f"cuda:{torch.cuda.current_device()}")
     if dtype is not None:
         dts = dtype if isinstance(dtype, (tuple, list)) else (dtype,)
         if t.dtype not in dts:
@@ -178,7 +183,9 @@ _SEQ_ROLES = {k: "in" for k in ("data", "lens", "maxlen", "num_instances")}
 
 
 def _alpha_role(opts):
-    return "out" if forward_wants_alpha(opts) else "skip"
+    # Copied both ways when the kernel writes them: only one of alpha1 / alpha2 receives a
+    # given sequence's final vector, the other keeps the caller's contents.
+    return "inout" if forward_wants_alpha(opts) else "skip"
 
 
 register(OpSpec(

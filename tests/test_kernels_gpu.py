@@ -313,3 +313,65 @@ def test_compile_string_round_trip(oracle_mod, tmp_path, monkeypatch):
     y = np.ones(1000, dtype=np.float32)
     f2({"a": a, "s": np.array(2.0, dtype=np.float32)}, y, 1000)
     assert np.array_equal(y, 2.0 * a + 1.0)
+
+
+# ---- the BASELINE configurations at full size ---------------------------------------------------------
+def test_full_size_sddmm_config(oracle_mod):
+    # CSR mask 8192 x 8192 at 1 % density, A [8192, 64], B [64, 8192]; (alpha, beta) = (1, 0) and (1.5, 2)
+    N, K = 8192, 64
+    C = synthetic.uniform_csr(N, N, 0.01, seed=1234)
+    g = torch.Generator().manual_seed(1234)
+    A, B = torch.randn(N, K, generator=g), torch.randn(K, N, generator=g)
+    rows = oracle_mod.sddmm_decompress(C["crows"])
+    Ad, Bd = A.cuda(), B.cuda()
+    for alpha, beta in ((1.0, 0.0), (1.5, 2.0)):
+        exp = oracle_mod.sddmm(A, B, rows, C["cols"], C["values"], alpha, beta)
+        Cd = {"crows": C["crows"].cuda(), "rows": torch.empty(C["nnz"], dtype=torch.int64, device="cuda"),
+              "cols": C["cols"].cuda(), "values": C["values"].cuda(), "nnz": C["nnz"]}
+        D = torch.empty(C["nnz"], device="cuda")
+        kernels.parpy_sddmm_csr_kernel(Ad, Bd, Cd, D, N, alpha, beta, opts=parpy.par({"nnz": parpy.threads(C["nnz"])}))
+        assert np.array_equal(Cd["rows"].cpu().numpy(), rows)
+        got = D.cpu().numpy()
+        assert np.all(np.abs(got - exp) <= 1e-5 + 2e-7 * K + 1e-4 * np.abs(exp))
+
+
+def test_full_size_spmv_config(native, oracle_mod):
+    # 4,194,304 x 4,194,304 CSR, Zipf(1.5) row lengths with mean 32 capped at 4096, x ~ N(0,1)
+    n = 1 << 22
+    A = synthetic.zipf_csr(n, n, mean_nnz=32, cap=4096, seed=1234)
+    x = torch.randn(n, generator=torch.Generator().manual_seed(1234))
+    exp = oracle_mod.spmv(A, x, np.zeros(n, dtype=np.float32))
+    d = {k: v.cuda() for k, v in A.items() if isinstance(v, torch.Tensor)}
+    xd, yd = x.cuda(), torch.zeros(n, device="cuda")
+    rc = native.lib().parpy_b200_spmv(P(d["values"].data_ptr()), P(d["rows"].data_ptr()), P(d["cols"].data_ptr()),
+                                      n, d["values"].numel(), P(xd.data_ptr()), P(yd.data_ptr()),
+                                      P(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0, native.error_message()
+    got = yd.cpu().numpy()
+    lens = np.diff(A["rows"].numpy())
+    assert np.all(np.abs(got - exp) <= 1e-4 * np.maximum(np.abs(exp), np.sqrt(np.maximum(lens, 1))))
+    assert np.array_equal(got[lens == 0], np.zeros(int((lens == 0).sum()), dtype=np.float32))
+    # linearity: A(2x) = 2 A(x) exactly in binary floating point
+    y2 = torch.zeros(n, device="cuda")
+    x2 = (2.0 * x).cuda()
+    rc = native.lib().parpy_b200_spmv(P(d["values"].data_ptr()), P(d["rows"].data_ptr()), P(d["cols"].data_ptr()),
+                                      n, d["values"].numel(), P(x2.data_ptr()), P(y2.data_ptr()),
+                                      P(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    short = lens <= 64                      # rows summed by one thread in index order: bit-exact doubling
+    assert np.array_equal(y2.cpu().numpy()[short], 2.0 * got[short])
+
+
+def test_full_size_sum_and_max_over_2_to_30():
+    n = 1 << 30
+    v = torch.empty(n, dtype=torch.float32, device="cuda").normal_(generator=torch.Generator(device="cuda").manual_seed(1234))
+    r = kernels.sum_max(v).cpu().numpy()
+    assert r[1] == float(v.max())
+    ref = float(v.sum(dtype=torch.float64))
+    assert abs(r[0] - ref) <= 1e-4 * max(abs(ref), np.sqrt(n))
+    out = np.zeros(1, dtype=np.float32)
+    o = torch.zeros(1, device="cuda")
+    kernels.max_2d(v.view(1 << 15, 1 << 15), o, 1 << 15, opts=parpy.par({"outer": parpy.threads(1024)}))
+    assert float(o[0]) == r[1]
+    kernels.min_2d(v.view(1 << 15, 1 << 15), o, 1 << 15, opts=parpy.par({"outer": parpy.threads(1024)}))
+    assert float(o[0]) == float(v.min())
