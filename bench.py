@@ -222,7 +222,9 @@ def main():
     # ---- inputs: identical tables on every rank, per-rank sequences -------------------
     hmm = synthetic.hmm_model(args.kmer, seed=SEED)
     if args.scaling == "weak":
-        seqs = synthetic.hmm_sequences(args.batch, args.min_len, args.max_len, seed=SEED + 17 * rank)
+        # same lengths on every rank (equal work per GPU), rank-specific observations
+        seqs = synthetic.hmm_sequences(args.batch, args.min_len, args.max_len, seed=SEED,
+                                       data_seed=None if rank == 0 else SEED + 17 * rank)
         global_lens = None
     else:
         all_seqs = synthetic.hmm_sequences(args.batch, args.min_len, args.max_len, seed=SEED)
@@ -290,7 +292,8 @@ def main():
     d2h = host_result.numel() * 4
 
     def step_e2e():
-        hmm_mod.forward_kernel(pin_hmm, pin_seqs, host_result, None, None, opts=opts)
+        a1, a2 = alpha if alpha is not None else (None, None)   # streaming variant: device scratch
+        hmm_mod.forward_kernel(pin_hmm, pin_seqs, host_result, a1, a2, opts=opts)
         if world > 1 and args.scaling == "weak":
             td.all_gather(gather_buf, host_result.cuda(non_blocking=True))
 

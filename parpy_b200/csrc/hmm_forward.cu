@@ -1165,8 +1165,8 @@ int32_t forward_impl(float gamma, const float *initial_prob, int64_t num_states,
     }
 
     // streaming path
-    PB_REQUIRE(alpha1 && alpha2, "forward: the streaming kernel needs alpha1 and alpha2 scratch "
-                                 "(num_states=%lld has no resident mapping)", (long long)num_states);
+    PB_REQUIRE(alpha1 && alpha2, "forward: the streaming kernel needs alpha1 and alpha2 scratch (%s)",
+               streaming_forced ? "streaming was requested" : "this state space has no resident mapping");
     PB_REQUIRE(num_instances <= 65535, "forward: streaming kernel supports at most 65535 sequences");
     const int tpb = 256;
     dim3 grid((unsigned)((num_states + tpb - 1) / tpb), (unsigned)num_instances, 1);

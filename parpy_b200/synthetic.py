@@ -37,18 +37,22 @@ def hmm_model(k, seed=1234, tail_factor=0.605):
     }
 
 
-def hmm_sequences(batch, min_len, max_len, seed=1234, pad_value=None):
+def hmm_sequences(batch, min_len, max_len, seed=1234, pad_value=None, data_seed=None):
     """Observation batch in the reference's layout (benchmarks/forward.py:74-86):
     ``data`` int8 [B, maxlen] with levels in [0, 101), ``lens`` int64 [B] uniform
     in [min_len, max_len]. Entries past a sequence's length are padding; with
     ``pad_value=None`` they hold out-of-range garbage (the benchmark pads with
-    uninitialised memory), which a correct kernel must never use."""
+    uninitialised memory), which a correct kernel must never use. ``data_seed``
+    redraws the observations only, keeping the lengths that ``seed`` gives."""
     g = torch.Generator().manual_seed(seed + 1)
     if min_len == max_len:
         lens = torch.full((batch,), max_len, dtype=torch.int64)
     else:
         lens = torch.randint(min_len, max_len + 1, (batch,), generator=g, dtype=torch.int64)
     maxlen = int(lens.max())
+    if data_seed is not None:
+        # same lengths for every data_seed (e.g. one per rank), different observations
+        g = torch.Generator().manual_seed(data_seed)
     data = torch.randint(0, N_OBS, (batch, maxlen), generator=g, dtype=torch.int64).to(torch.int8)
     pad = -7 if pad_value is None else pad_value
     mask = torch.arange(maxlen).unsqueeze(0) >= lens.unsqueeze(1)
