@@ -228,6 +228,22 @@ int32_t spmm_cell(int64_t *A_cols, int64_t A_nrows, int64_t *A_rows, float *A_va
 int32_t parpy_b200_spmm(const float *values, const int64_t *rows, const int64_t *cols, int64_t nrows,
                         const float *B, int64_t ncols, float *C, void *stream);
 
+/* ---- HMM input preparation on the device ------------------------------------------------
+ * Replaces the host loops of the reference's loader (benchmarks/forward.py:20-87,
+ * test/test_forward.py:11-78). prepare_tables: from the raw probability tables of
+ * a model file (ObservationProbabilities [n_obs, 4^k], TransitionProbabilities
+ * [4, 4^k], DurationProbabilities [16]; all float32 or all float64, device
+ * memory) to output_prob [n_obs, K] (log, columns permuted by base reversal),
+ * trans1 [K, 4] (log, transposed), trans2 [16] (log) and initial_prob [16 K]
+ * (log(1/K) in layer 0, -inf elsewhere). pad_signals: from the concatenated int16
+ * signals and their offsets [num_signals + 1] to the zero-padded int8 matrix
+ * [num_signals, maxlen] and the int64 lengths. */
+int32_t parpy_b200_hmm_prepare_tables(const void *obs_prob, const void *trans_prob, const void *dur_prob,
+                                      int32_t is_f64, int32_t k, int64_t n_obs, float *output_prob,
+                                      float *trans1, float *trans2, float *initial_prob, void *stream);
+int32_t parpy_b200_hmm_pad_signals(const int16_t *flat, const int64_t *offsets, int64_t num_signals,
+                                   int64_t maxlen, int8_t *data, int64_t *lens, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -59,6 +59,9 @@ SIGNATURES = {
     "parpy_b200_sum_exp_rows": (c_i32, [c_ptr, c_i64, c_i64, c_ptr, c_ptr]),
     "spmm_cell": (c_i32, [c_ptr, c_i64, c_ptr, c_ptr, c_i64, c_ptr, c_ptr]),
     "parpy_b200_spmm": (c_i32, [c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_i64, c_ptr, c_ptr]),
+    "parpy_b200_hmm_prepare_tables": (c_i32, [c_ptr, c_ptr, c_ptr, c_i32, c_i32, c_i64, c_ptr, c_ptr, c_ptr,
+                                              c_ptr, c_ptr]),
+    "parpy_b200_hmm_pad_signals": (c_i32, [c_ptr, c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_ptr]),
 }
 
 REDUCE_SUM, REDUCE_PROD, REDUCE_MAX, REDUCE_MIN = 0, 1, 2, 3

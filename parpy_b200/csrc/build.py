@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
 OUT = os.path.join(PKG, "libparpy_b200.so")
-SOURCES = ["runtime.cu", "hmm_forward.cu", "rowops.cu", "sparse.cu"]
+SOURCES = ["runtime.cu", "hmm_forward.cu", "rowops.cu", "sparse.cu", "hmm_prepare.cu"]
 HEADERS = ["common.cuh", os.path.join("..", "..", "include", "parpy_b200.h")]
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",

@@ -1,7 +1,6 @@
-"""Minimal pure-Python reader for the subset of HDF5 the HMM fixtures use.
-
-Test infrastructure only. It exists because neither h5py nor libhdf5 is
-installed where the golden fixtures are generated. It understands exactly what
+"""Minimal pure-Python reader for the subset of HDF5 the HMM model and signal
+files use, for environments without h5py / libhdf5 (the reference's loaders,
+benchmarks/forward.py:40-55, use h5py). It understands exactly what
 the nanopore model / signal files need: superblock version 0, version-1 object
 headers (with continuation blocks), old-style groups (symbol table message ->
 v1 B-tree -> symbol nodes -> local heap), simple dataspaces, fixed-point and

@@ -50,3 +50,75 @@ def to_device(tables, device="cuda", pin=False):
         else:
             out[k] = v
     return out
+
+
+def read_trellis_inputs(model_path, signals_path):
+    """The loader of the reference's benchmark (benchmarks/forward.py:40-87) with
+    the table work done on the device: reads the model and signal HDF5 files
+    (h5py when installed, otherwise the package's minimal reader), uploads the raw
+    probability tables and the concatenated signals once, and builds the log
+    tables, the permuted emission matrix and the padded int8 batch with two
+    kernels. Returns ``(hmm, seqs)`` with CUDA tensors, 0-d entries included, as
+    the benchmark's version does."""
+    import ctypes
+    import numpy as np
+    import torch
+    from . import _native
+    try:
+        import h5py
+        opener = lambda p: h5py.File(p, "r")
+        read = lambda ds: ds[:]
+    except ImportError:
+        from .hdf5_min import H5File
+        opener = H5File
+        read = lambda ds: ds.read()
+
+    f = opener(model_path)
+    tables = f["Tables"]
+    obs = np.ascontiguousarray(read(tables["ObservationProbabilities"]))
+    trans = np.ascontiguousarray(read(tables["TransitionProbabilities"]))
+    dur = np.ascontiguousarray(read(tables["DurationProbabilities"]))
+    tail = np.log(tables["DurationProbabilities"].attrs["TailFactor"])       # forward.py:48
+    k = int(f["Parameters"].attrs["KMerLength"])
+    K = 4 ** k
+    is_f64 = obs.dtype == np.float64
+    want = np.float64 if is_f64 else np.float32
+    d_obs, d_trans, d_dur = (torch.from_numpy(a.astype(want, copy=False)).cuda() for a in (obs, trans, dur))
+    n_obs = obs.shape[0]
+    out_prob = torch.empty((n_obs, K), dtype=torch.float32, device="cuda")
+    trans1 = torch.empty((K, 4), dtype=torch.float32, device="cuda")
+    trans2 = torch.empty(16, dtype=torch.float32, device="cuda")
+    init = torch.empty(16 * K, dtype=torch.float32, device="cuda")
+    P = ctypes.c_void_p
+    stream = P(torch.cuda.current_stream().cuda_stream)
+    _native.check(_native.lib().parpy_b200_hmm_prepare_tables(
+        P(d_obs.data_ptr()), P(d_trans.data_ptr()), P(d_dur.data_ptr()), int(is_f64), k, n_obs,
+        P(out_prob.data_ptr()), P(trans1.data_ptr()), P(trans2.data_ptr()), P(init.data_ptr()), stream),
+        "hmm_prepare_tables")
+    synthetic_248 = np.log(np.exp(0.0) - np.exp(tail))                      # forward.py:56
+    hmm = {
+        "gamma": torch.tensor(tail, dtype=torch.float32, device="cuda"),
+        "trans1": trans1, "trans2": trans2, "output_prob": out_prob, "initial_prob": init,
+        "synthetic_248": torch.tensor(synthetic_248, dtype=torch.float32, device="cuda"),
+        "num_states": torch.tensor(16 * K, dtype=torch.int64, device="cuda"),
+    }
+
+    s = opener(signals_path)
+    keys = sorted(s.keys())
+    signals = [np.asarray(read(s[key]["Raw"]["Signal"]), dtype=np.int16) for key in keys]
+    offsets = np.zeros(len(signals) + 1, dtype=np.int64)
+    np.cumsum([len(x) for x in signals], out=offsets[1:])
+    maxlen = int(max(len(x) for x in signals))
+    flat = torch.from_numpy(np.concatenate(signals)).cuda()
+    d_off = torch.from_numpy(offsets).cuda()
+    data = torch.empty((len(signals), maxlen), dtype=torch.int8, device="cuda")
+    lens = torch.empty(len(signals), dtype=torch.int64, device="cuda")
+    _native.check(_native.lib().parpy_b200_hmm_pad_signals(
+        P(flat.data_ptr()), P(d_off.data_ptr()), len(signals), maxlen, P(data.data_ptr()),
+        P(lens.data_ptr()), stream), "hmm_pad_signals")
+    seqs = {
+        "data": data, "lens": lens,
+        "maxlen": torch.tensor(maxlen, dtype=torch.int64, device="cuda"),
+        "num_instances": torch.tensor(len(signals), dtype=torch.int64, device="cuda"),
+    }
+    return hmm, seqs

@@ -19,8 +19,8 @@ import sys
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-sys.path.insert(0, HERE)
-from hdf5_min import H5File  # noqa: E402
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+from parpy_b200.hdf5_min import H5File  # noqa: E402
 
 
 def reverse_index(i, k):

@@ -171,3 +171,23 @@ def test_print_compiled_returns_a_self_contained_translation_unit(tmp_path, monk
         assert source.compile_source(src) == lib        # cached by content
         with pytest.raises(RuntimeError, match="Compilation of CUDA source failed"):
             source.compile_source("this is not CUDA")
+
+
+def test_hdf5_reader_reproduces_the_committed_fixtures():
+    # the minimal HDF5 reader + the loader steps of benchmarks/forward.py:40-56 against tests/golden/*.npz
+    import os
+    import sys
+    ref = os.environ.get("PARPY_REFERENCE_ROOT", "/root/reference")
+    if not os.path.isdir(os.path.join(ref, "test", "data")):
+        pytest.skip("reference checkout with test/data not present")
+    from conftest import GOLDEN
+    sys.path.insert(0, GOLDEN)
+    import make_golden
+    for name in ("3mer", "5mer"):
+        built = make_golden.build_model(os.path.join(ref, "test", "data", f"{name}-model.hdf5"))
+        stored = np.load(os.path.join(GOLDEN, f"hmm_{name}.npz"))
+        for key in stored.files:
+            assert np.array_equal(np.asarray(built[key]), stored[key], equal_nan=True), (name, key)
+    sig = make_golden.build_signals(os.path.join(ref, "test", "data", "signals.hdf5"))
+    stored = np.load(os.path.join(GOLDEN, "signals.npz"))
+    assert np.array_equal(sig["data"], stored["data"]) and np.array_equal(sig["lens"], stored["lens"])

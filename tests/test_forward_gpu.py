@@ -358,3 +358,56 @@ def test_reference_cuda_agrees_on_5mer_fixture(native, oracle_mod):
     assert np.allclose(ref, exp, atol=1e-5, rtol=1e-5), max_rel(ref, exp)
     rc, res, _, _ = cabi_forward(native, to_dev(hmm), to_dev(seqs))
     assert rc == 0 and max_rel(res.cpu().numpy(), ref) <= REL_ORACLE
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_device_table_preparation_matches_the_reference_loader(native, dtype):
+    # benchmarks/forward.py:20-63 restated in NumPy (logs in the file's dtype, base-reversal column
+    # permutation, [4,K] -> [K,4]) against parpy_b200_hmm_prepare_tables
+    k, n_obs = 4, 101
+    K = 4 ** k
+    rng = np.random.default_rng(5)
+    obs = rng.random((n_obs, K)).astype(dtype)
+    obs[3, 7] = 0.0                                              # zero probability -> -inf
+    trans = rng.random((4, K)).astype(dtype)
+    dur = rng.random(16).astype(dtype)
+    with np.errstate(divide="ignore"):
+        lobs = np.log(obs)
+    rev = np.array([sum(((i // 4 ** x) % 4) * 4 ** (k - x - 1) for x in range(k)) for i in range(K)])
+    exp_out = lobs[:, rev].astype(np.float32)
+    exp_t1 = np.log(trans).reshape(4, K).transpose(1, 0).astype(np.float32)
+    exp_t2 = np.log(dur).astype(np.float32)
+    exp_init = np.full((16, K), -np.inf, dtype=np.float32)
+    exp_init[0, :] = np.log(1.0 / float(K))
+    P = ctypes.c_void_p
+    d_obs, d_tr, d_du = (torch.from_numpy(a).cuda() for a in (obs, trans, dur))
+    out = torch.empty((n_obs, K), device="cuda")
+    t1 = torch.empty((K, 4), device="cuda")
+    t2 = torch.empty(16, device="cuda")
+    init = torch.empty(16 * K, device="cuda")
+    rc = native.lib().parpy_b200_hmm_prepare_tables(
+        P(d_obs.data_ptr()), P(d_tr.data_ptr()), P(d_du.data_ptr()), int(dtype == np.float64), k, n_obs,
+        P(out.data_ptr()), P(t1.data_ptr()), P(t2.data_ptr()), P(init.data_ptr()), None)
+    torch.cuda.synchronize()
+    assert rc == 0, native.error_message()
+    assert np.array_equal(init.cpu().numpy().reshape(16, K), exp_init)
+    for got, exp in ((out, exp_out), (t1, exp_t1), (t2, exp_t2)):
+        g = got.cpu().numpy()
+        assert np.array_equal(np.isneginf(g), np.isneginf(exp))
+        fin = np.isfinite(exp)
+        assert np.all(np.abs(g[fin] - exp[fin]) <= 2.5e-7 * np.maximum(np.abs(exp[fin]), 1.0))   # <= ~2 ulp of the logs
+    # padded int8 batch (benchmarks/forward.py:74-79)
+    sigs = [rng.integers(4, 97, n).astype(np.int16) for n in (5, 1, 300, 17)]
+    offs = np.zeros(5, dtype=np.int64)
+    np.cumsum([len(s) for s in sigs], out=offs[1:])
+    flat, d_off = torch.from_numpy(np.concatenate(sigs)).cuda(), torch.from_numpy(offs).cuda()
+    data = torch.full((4, 300), 99, dtype=torch.int8, device="cuda")
+    lens = torch.zeros(4, dtype=torch.int64, device="cuda")
+    rc = native.lib().parpy_b200_hmm_pad_signals(P(flat.data_ptr()), P(d_off.data_ptr()), 4, 300,
+                                                 P(data.data_ptr()), P(lens.data_ptr()), None)
+    torch.cuda.synchronize()
+    assert rc == 0 and lens.cpu().tolist() == [5, 1, 300, 17]
+    exp = np.zeros((4, 300), dtype=np.int8)
+    for i, s in enumerate(sigs):
+        exp[i, :len(s)] = s
+    assert np.array_equal(data.cpu().numpy(), exp)
