@@ -52,27 +52,27 @@ def to_device(tables, device="cuda", pin=False):
     return out
 
 
-def read_trellis_inputs(model_path, signals_path):
-    """The loader of the reference's benchmark (benchmarks/forward.py:40-87) with
-    the table work done on the device: reads the model and signal HDF5 files
-    (h5py when installed, otherwise the package's minimal reader), uploads the raw
-    probability tables and the concatenated signals once, and builds the log
-    tables, the permuted emission matrix and the padded int8 batch with two
-    kernels. Returns ``(hmm, seqs)`` with CUDA tensors, 0-d entries included, as
-    the benchmark's version does."""
+def _hdf5_access():
+    """(open, read-dataset) functions: h5py when installed, else the package's reader."""
+    try:
+        import h5py
+        return (lambda p: h5py.File(p, "r")), (lambda ds: ds[:])
+    except ImportError:
+        from .hdf5_min import H5File
+        return H5File, (lambda ds: ds.read())
+
+
+def read_model(model_path):
+    """Model half of the reference's loader (benchmarks/forward.py:43-72) with the
+    table work on the device: uploads the raw probability tables once and builds
+    the log tables, the base-reversal permuted emission matrix, the transposed
+    transition table and the initial distribution with one kernel. Returns the
+    ``hmm`` dictionary with CUDA tensors (0-d entries included)."""
     import ctypes
     import numpy as np
     import torch
     from . import _native
-    try:
-        import h5py
-        opener = lambda p: h5py.File(p, "r")
-        read = lambda ds: ds[:]
-    except ImportError:
-        from .hdf5_min import H5File
-        opener = H5File
-        read = lambda ds: ds.read()
-
+    opener, read = _hdf5_access()
     f = opener(model_path)
     tables = f["Tables"]
     obs = np.ascontiguousarray(read(tables["ObservationProbabilities"]))
@@ -90,19 +90,28 @@ def read_trellis_inputs(model_path, signals_path):
     trans2 = torch.empty(16, dtype=torch.float32, device="cuda")
     init = torch.empty(16 * K, dtype=torch.float32, device="cuda")
     P = ctypes.c_void_p
-    stream = P(torch.cuda.current_stream().cuda_stream)
     _native.check(_native.lib().parpy_b200_hmm_prepare_tables(
         P(d_obs.data_ptr()), P(d_trans.data_ptr()), P(d_dur.data_ptr()), int(is_f64), k, n_obs,
-        P(out_prob.data_ptr()), P(trans1.data_ptr()), P(trans2.data_ptr()), P(init.data_ptr()), stream),
-        "hmm_prepare_tables")
+        P(out_prob.data_ptr()), P(trans1.data_ptr()), P(trans2.data_ptr()), P(init.data_ptr()),
+        P(torch.cuda.current_stream().cuda_stream)), "hmm_prepare_tables")
     synthetic_248 = np.log(np.exp(0.0) - np.exp(tail))                      # forward.py:56
-    hmm = {
+    return {
         "gamma": torch.tensor(tail, dtype=torch.float32, device="cuda"),
         "trans1": trans1, "trans2": trans2, "output_prob": out_prob, "initial_prob": init,
         "synthetic_248": torch.tensor(synthetic_248, dtype=torch.float32, device="cuda"),
         "num_states": torch.tensor(16 * K, dtype=torch.int64, device="cuda"),
     }
 
+
+def read_signals(signals_path):
+    """Signal half of the reference's loader (benchmarks/forward.py:53-55,74-86):
+    one upload of the concatenated int16 signals, padded int8 matrix and lengths
+    built on the device. Returns the ``seqs`` dictionary with CUDA tensors."""
+    import ctypes
+    import numpy as np
+    import torch
+    from . import _native
+    opener, read = _hdf5_access()
     s = opener(signals_path)
     keys = sorted(s.keys())
     signals = [np.asarray(read(s[key]["Raw"]["Signal"]), dtype=np.int16) for key in keys]
@@ -113,12 +122,17 @@ def read_trellis_inputs(model_path, signals_path):
     d_off = torch.from_numpy(offsets).cuda()
     data = torch.empty((len(signals), maxlen), dtype=torch.int8, device="cuda")
     lens = torch.empty(len(signals), dtype=torch.int64, device="cuda")
+    P = ctypes.c_void_p
     _native.check(_native.lib().parpy_b200_hmm_pad_signals(
         P(flat.data_ptr()), P(d_off.data_ptr()), len(signals), maxlen, P(data.data_ptr()),
-        P(lens.data_ptr()), stream), "hmm_pad_signals")
-    seqs = {
+        P(lens.data_ptr()), P(torch.cuda.current_stream().cuda_stream)), "hmm_pad_signals")
+    return {
         "data": data, "lens": lens,
         "maxlen": torch.tensor(maxlen, dtype=torch.int64, device="cuda"),
         "num_instances": torch.tensor(len(signals), dtype=torch.int64, device="cuda"),
     }
-    return hmm, seqs
+
+
+def read_trellis_inputs(model_path, signals_path):
+    """benchmarks/forward.py:40-87: ``(hmm, seqs)`` for a model file and a signal file."""
+    return read_model(model_path), read_signals(signals_path)

@@ -411,3 +411,22 @@ def test_device_table_preparation_matches_the_reference_loader(native, dtype):
     for i, s in enumerate(sigs):
         exp[i, :len(s)] = s
     assert np.array_equal(data.cpu().numpy(), exp)
+
+
+def test_read_model_from_the_reference_3mer_file_and_score_the_fixture(native):
+    # tests/golden/3mer-model.hdf5 is the reference's test/data/3mer-model.hdf5, byte for byte
+    import os
+    from conftest import GOLDEN
+    from parpy_b200 import hmm as hmm_mod
+    hmm = hmm_mod.read_model(os.path.join(GOLDEN, "3mer-model.hdf5"))
+    stored = load_model("3mer")
+    for key in ("trans1", "trans2", "output_prob", "initial_prob"):
+        g, e = hmm[key].cpu().numpy().reshape(-1), stored[key].numpy().reshape(-1)
+        assert np.array_equal(np.isneginf(g), np.isneginf(e)), key
+        fin = np.isfinite(e)
+        assert np.all(np.abs(g[fin] - e[fin]) <= 2.5e-7 * np.maximum(np.abs(e[fin]), 1.0)), key
+    assert float(hmm["gamma"]) == float(stored["gamma"]) and int(hmm["num_states"]) == 1024
+    assert float(hmm["synthetic_248"]) == float(stored["synthetic_248"])
+    seqs = to_dev(load_signals())
+    res = hmm_mod.forward_parpy(hmm, seqs, 512).cpu().numpy()
+    assert np.allclose(res, load_expected("3mer"), atol=1e-5, rtol=1e-5)
