@@ -430,3 +430,40 @@ def test_read_model_from_the_reference_3mer_file_and_score_the_fixture(native):
     seqs = to_dev(load_signals())
     res = hmm_mod.forward_parpy(hmm, seqs, 512).cpu().numpy()
     assert np.allclose(res, load_expected("3mer"), atol=1e-5, rtol=1e-5)
+
+
+def test_large_batches_long_sequences_and_side_streams(native, oracle_mod):
+    from parpy_b200 import synthetic
+    hmm = synthetic.hmm_model(5, seed=41)
+    dh = to_dev(hmm)
+    # 5000 sequences (more than the 4096 the scheduler sorts): every result equals the small-batch result
+    many = synthetic.hmm_sequences(5000, 1, 40, seed=42)
+    rc, res, _, _ = cabi_forward(native, dh, to_dev(many))
+    assert rc == 0, native.error_message()
+    got = res.cpu().numpy()
+    idx = np.arange(0, 5000, 97)
+    sub = {"data": many["data"][idx].contiguous(), "lens": many["lens"][idx].contiguous(),
+           "maxlen": many["maxlen"], "num_instances": torch.tensor(len(idx))}
+    rc, res2, _, _ = cabi_forward(native, dh, to_dev(sub))
+    assert rc == 0 and np.array_equal(res2.cpu().numpy(), got[idx])
+    assert max_rel(got[idx], oracle_mod.forward(hmm, sub)) <= REL_ORACLE
+    # one long sequence (40000 steps): finite, and a prefix is more likely than the whole
+    longs = synthetic.hmm_sequences(2, 40000, 40000, seed=43)
+    longs["lens"][1] = 20000
+    rc, res, _, _ = cabi_forward(native, dh, to_dev(longs))
+    r = res.cpu().numpy()
+    assert rc == 0 and np.isfinite(r).all() and r[1] > r[0]
+    # two side streams in flight at once: each has its own scratch
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    a, b = to_dev(synthetic.hmm_sequences(300, 5, 200, seed=44)), to_dev(synthetic.hmm_sequences(200, 5, 200, seed=45))
+    torch.cuda.synchronize()
+    with torch.cuda.stream(s1):
+        rc1, r1, _, _ = cabi_forward(native, dh, a)
+    with torch.cuda.stream(s2):
+        rc2, r2, _, _ = cabi_forward(native, dh, b)
+    torch.cuda.synchronize()
+    rc3, e1, _, _ = cabi_forward(native, dh, a)
+    rc4, e2, _, _ = cabi_forward(native, dh, b)
+    torch.cuda.synchronize()
+    assert rc1 == rc2 == rc3 == rc4 == 0
+    assert torch.equal(r1, e1) and torch.equal(r2, e2)
