@@ -244,6 +244,23 @@ int32_t parpy_b200_hmm_prepare_tables(const void *obs_prob, const void *trans_pr
 int32_t parpy_b200_hmm_pad_signals(const int16_t *flat, const int64_t *offsets, int64_t num_signals,
                                    int64_t maxlen, int8_t *data, int64_t *lens, void *stream);
 
+/* ---- windowed Viterbi decoding ------------------------------------------------------------
+ * Most likely state sequence of every observation sequence under the same model
+ * tables as forward_kernel, with the semantics of the CUDA the reference ships
+ * (benchmarks/7mer/hmm.cu:116-176,352-508,569-657, driven by
+ * benchmarks/7mer/trellis.py:25-83 with batch_size 1024 and batch_overlap 128):
+ * windows of batch_size steps advancing by batch_size - batch_overlap, each later
+ * window restarted from the state decoded just before it. out is uint32
+ * [num_instances, out_stride] (out_stride >= maxlen); row i holds lens[i] decoded
+ * states (state = layer * K + kmer), the rest of the row is unspecified. The
+ * reference's entry takes host pointers and returns malloc'ed host memory; this
+ * one works on device memory. State spaces from 4^5 to 4^8 k-mers. */
+int32_t parpy_b200_viterbi(float gamma, const float *initial_prob, int64_t num_states,
+                           const float *output_prob, float synthetic_248, const float *trans1,
+                           const float *trans2, const void *data, const int64_t *lens, int64_t maxlen,
+                           int64_t num_instances, int64_t batch_size, int64_t batch_overlap,
+                           uint32_t *out, int64_t out_stride, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

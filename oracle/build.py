@@ -20,7 +20,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB = os.path.join(HERE, "liboracle.so")
 REF_DIR = os.path.join(HERE, "_ref")
-C_SOURCES = ["hmm_oracle.c", "kernels_oracle.c"]
+C_SOURCES = ["hmm_oracle.c", "kernels_oracle.c", "viterbi_oracle.c"]
 
 
 def _run(cmd):

@@ -241,3 +241,59 @@ def spmm(A, B, C):
     fn(values.ctypes.data, rows.ctypes.data, cols.ctypes.data, len(rows) - 1, B.ctypes.data, B.shape[1],
        C.ctypes.data)
     return C
+
+
+# ---- Viterbi -----------------------------------------------------------------------------
+def viterbi(hmm, seqs, batch_size=1024, batch_overlap=128):
+    """Windowed Viterbi decoding as the reference's CUDA does it
+    (benchmarks/7mer/hmm.cu:116-176,352-508,569-657). Returns a list of uint32
+    state arrays, one per sequence, trimmed to the sequence's length."""
+    n = int(hmm["num_states"])
+    init, outp = _np(hmm["initial_prob"], np.float32), _np(hmm["output_prob"], np.float32)
+    t1, t2 = _np(hmm["trans1"], np.float32), _np(hmm["trans2"], np.float32)
+    data = _np(seqs["data"], None).view(np.uint8)
+    lens = _np(seqs["lens"], np.int64)
+    batch, maxlen = data.shape
+    out = np.zeros((batch, maxlen), dtype=np.uint32)
+    fn = lib().oracle_viterbi
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_float, _P, ctypes.c_int64, _P, ctypes.c_float, _P, _P, _P, _P, ctypes.c_int64,
+                   ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, _P, ctypes.c_int64]
+    rc = fn(float(hmm["gamma"]), init.ctypes.data, n, outp.ctypes.data, float(hmm["synthetic_248"]),
+            t1.ctypes.data, t2.ctypes.data, data.ctypes.data, lens.ctypes.data, maxlen, batch,
+            batch_size, batch_overlap, out.ctypes.data, maxlen)
+    if rc != 0:
+        raise RuntimeError("oracle_viterbi rejected its arguments")
+    return [out[i, :int(lens[i])].copy() for i in range(batch)]
+
+
+def trellis_viterbi(k, hmm, seqs, num_parallel=1):
+    """The reference's own CUDA Viterbi (oracle/_ref), driven as
+    benchmarks/7mer/trellis.py:25-83 does: observations padded to a whole number of
+    windows plus the overlap, true lengths passed separately. Needs a GPU."""
+    path = os.path.join(_build.REF_DIR, f"trellis_{k}mer.so")
+    t = ctypes.CDLL(path)
+    t1 = _np(hmm["trans1"], np.float32)
+    t2 = _np(hmm["trans2"], np.float32)
+    outp = _np(hmm["output_prob"], np.float32)
+    init = _np(hmm["initial_prob"], np.float32)
+    t.init.argtypes = [ctypes.c_float, _P, _P, _P, _P, ctypes.c_float]
+    t.init.restype = None
+    t.init(float(hmm["gamma"]), t1.ctypes.data, t2.ctypes.data, outp.ctypes.data, init.ctypes.data,
+           float(hmm["synthetic_248"]))
+    data = _np(seqs["data"], None).view(np.uint8)
+    lens = _np(seqs["lens"], np.int32)
+    bos, overlap = 1024 - 128, 128
+    plens = (lens + bos - 1) // bos * bos + overlap
+    maxlen = int(plens.max())
+    padded = np.zeros((len(lens), maxlen), dtype=np.uint8)
+    for i, n in enumerate(lens):
+        padded[i, :n] = data[i, :n]
+    padded = np.ascontiguousarray(padded.reshape(-1))
+    lens = np.ascontiguousarray(lens)
+    t.viterbi.argtypes = [_P, _P, ctypes.c_int, ctypes.c_int, ctypes.c_int]
+    t.viterbi.restype = ctypes.POINTER(ctypes.c_uint32)
+    ptr = t.viterbi(padded.ctypes.data, lens.ctypes.data, maxlen, int(num_parallel), len(lens))
+    res = np.ctypeslib.as_array(ptr, shape=(len(lens), maxlen)).copy()
+    ctypes.CDLL(None).free(ptr)
+    return [res[i, :int(lens[i])].copy() for i in range(len(lens))]

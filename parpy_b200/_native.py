@@ -62,6 +62,8 @@ SIGNATURES = {
     "parpy_b200_hmm_prepare_tables": (c_i32, [c_ptr, c_ptr, c_ptr, c_i32, c_i32, c_i64, c_ptr, c_ptr, c_ptr,
                                               c_ptr, c_ptr]),
     "parpy_b200_hmm_pad_signals": (c_i32, [c_ptr, c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_ptr]),
+    "parpy_b200_viterbi": (c_i32, [c_f32, c_ptr, c_i64, c_ptr, c_f32, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_i64,
+                                   c_i64, c_i64, c_ptr, c_i64, c_ptr]),
 }
 
 REDUCE_SUM, REDUCE_PROD, REDUCE_MAX, REDUCE_MIN = 0, 1, 2, 3

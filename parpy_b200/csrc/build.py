@@ -13,8 +13,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
 OUT = os.path.join(PKG, "libparpy_b200.so")
-SOURCES = ["runtime.cu", "hmm_forward.cu", "rowops.cu", "sparse.cu", "hmm_prepare.cu"]
-HEADERS = ["common.cuh", os.path.join("..", "..", "include", "parpy_b200.h")]
+SOURCES = ["runtime.cu", "hmm_forward.cu", "rowops.cu", "sparse.cu", "hmm_prepare.cu", "hmm_viterbi.cu"]
+HEADERS = ["common.cuh", "cluster.cuh", os.path.join("..", "..", "include", "parpy_b200.h")]
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",
     "-gencode", "arch=compute_100a,code=sm_100a",

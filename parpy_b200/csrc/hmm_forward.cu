@@ -26,6 +26,7 @@
 
 #include "../../include/parpy_b200.h"
 #include "common.cuh"
+#include "cluster.cuh"
 
 namespace {
 
@@ -77,44 +78,6 @@ struct FwdParams {
     float gamma_lin;            // exp(gamma), exp(synthetic_248): scaled kernel only
     float synthetic_lin;
 };
-
-// ---- cluster primitives (PTX) ----------------------------------------------
-__device__ __forceinline__ unsigned cluster_ctarank() {
-    unsigned r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ unsigned cluster_nctarank() {
-    unsigned r;
-    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ void cluster_arrive() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void cluster_wait() {
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ unsigned smem_u32(const void *p) {
-    return static_cast<unsigned>(__cvta_generic_to_shared(p));
-}
-// Address of the same shared-memory offset inside CTA `rank` of this cluster.
-__device__ __forceinline__ unsigned map_to_rank(unsigned saddr, unsigned rank) {
-    unsigned r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ void st_cluster_f32(unsigned addr, float v) {
-    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
-}
-__device__ __forceinline__ void st_cluster_v4(unsigned addr, float a, float b, float c, float d) {
-    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b),
-                 "f"(c), "f"(d)
-                 : "memory");
-}
-__device__ __forceinline__ void st_cluster_s32(unsigned addr, int v) {
-    asm volatile("st.shared::cluster.s32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
-}
 
 // ---- log-sum-exp building blocks -------------------------------------------
 // exp and log are the fast intrinsics the reference's CUDA backend prints for
@@ -673,10 +636,6 @@ __device__ __forceinline__ float pow2_clamped(int e) {  // 2^e, +0.0 below 2^-12
     e = max(e, -127);
     e = min(e, 127);
     return __int_as_float((e + 127) << 23);
-}
-__device__ __forceinline__ void st_cluster_v4i(unsigned addr, int a, int b, int c, int d) {
-    asm volatile("st.shared::cluster.v4.s32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
-                 : "memory");
 }
 
 constexpr int kExpFloor = -(1 << 28);  // exponent of an all-zero thread

@@ -1,0 +1,396 @@
+// Windowed Viterbi decoding over the k-mer x 16-duration-layer HMM for sm_100a,
+// with the semantics of the CUDA the reference ships for the same model
+// (benchmarks/7mer/hmm.cu:116-176, 352-508, 569-657): windows of `batch` time
+// steps that advance by `batch - overlap`, a window after the first restarts from
+// the state decoded at t-1, candidates compared in the order j = 0..3 then the
+// duration-chain predecessor with a strict '>', and the final arg-max of a full
+// window taken one step before its end, as the reference's buffer swap has it.
+//
+// Layout: the resident design of the forward kernel. A cluster owns one sequence
+// at a time, each thread keeps the 16 layers of its 4 k-mers (64 chi values) in
+// registers, only layer 0 crosses CTAs (distributed shared memory, one split
+// barrier.cluster per step). The reference stores a 4-byte back pointer per state
+// and step (1 MiB per step for the 7-mer model); here a back pointer is one of
+// five choices, stored as a nibble: 32 bytes per thread and step, 128 KiB per
+// step for the 7-mer model, written with two 16-byte stores. The cluster leader
+// walks the window backwards through these nibbles.
+#include <algorithm>
+#include <atomic>
+
+#include "../../include/parpy_b200.h"
+#include "common.cuh"
+#include "cluster.cuh"
+
+namespace {
+
+constexpr int kLayers = 16;
+constexpr unsigned kNoPred = 15u;   // nibble of a state no candidate reached (all -inf)
+
+struct VitParams {
+    const float *initial_prob;  // [16*K]
+    const float *output_prob;   // [n_obs, K]
+    const float *trans1;        // [K, 4]
+    const float *trans2;        // [16]
+    const uint8_t *data;        // [B, maxlen]
+    const int64_t *lens;        // [B]
+    uint32_t *out;              // [B, out_stride] decoded states
+    const int *order;           // [B] sequence ids, longest first
+    int *counter;               // work-queue head
+    uint4 *codes;               // back-pointer nibbles, one block per resident cluster
+    long long codes_per_cluster;  // uint4 elements per cluster block
+    long long maxlen;
+    long long out_stride;
+    int B;
+    int K;
+    int batch;
+    int overlap;
+    float gamma;
+    float synthetic;
+};
+
+__global__ void vit_schedule(const int64_t *__restrict__ lens, int B, int *__restrict__ order,
+                             int *__restrict__ counter) {
+    extern __shared__ int s_len[];
+    if (B <= 4096) {
+        for (int i = threadIdx.x; i < B; i += blockDim.x) {
+            long long l = lens[i];
+            s_len[i] = l > 0x7fffffffLL ? 0x7fffffff : (l < 0 ? 0 : static_cast<int>(l));
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < B; i += blockDim.x) {
+            const int li = s_len[i];
+            int rank = 0;
+            for (int j = 0; j < B; ++j) rank += (s_len[j] > li) || (s_len[j] == li && j < i);
+            order[rank] = i;
+        }
+    } else {
+        for (int i = threadIdx.x; i < B; i += blockDim.x) order[i] = i;
+    }
+    if (threadIdx.x == 0) *counter = 0;
+}
+
+// (value, index) arg-max with the lowest index among equal values.
+__device__ __forceinline__ void argmax_combine(float &v, unsigned &i, float ov, unsigned oi) {
+    if (ov > v || (ov == v && oi < i)) {
+        v = ov;
+        i = oi;
+    }
+}
+
+__global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p) {
+    extern __shared__ __align__(16) float a0s[];  // [2][4][M] layer-0 values this CTA consumes
+    __shared__ float s_t2[kLayers];
+    __shared__ int s_seq;
+    __shared__ unsigned s_last;
+    __shared__ float s_warp_v[32];
+    __shared__ unsigned s_warp_i[32];
+    __shared__ float s_cl_v[16];
+    __shared__ unsigned s_cl_i[16];
+
+    const int tid = threadIdx.x;
+    const int NT = blockDim.x;
+    const unsigned rank = cluster_ctarank();
+    const unsigned CS = cluster_nctarank();
+    const int K = p.K;
+    const int Kq = K >> 2;
+    const int M = NT;
+    const int gthread = rank * NT + tid;     // thread index within the sequence, 0 .. K/4-1
+    const int g = gthread * 4;               // first global k-mer
+    const int lane = tid & 31, warp = tid >> 5, nwarps = (NT + 31) >> 5;
+    const int bos = p.batch - p.overlap;
+    uint4 *codes = p.codes + (long long)(blockIdx.x / CS) * p.codes_per_cluster;
+
+    if (tid < kLayers) s_t2[tid] = __ldg(p.trans2 + tid);
+    float T[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float4 v = __ldg(reinterpret_cast<const float4 *>(p.trans1) + (j * Kq + (g >> 2)));
+        T[j][0] = v.x; T[j][1] = v.y; T[j][2] = v.z; T[j][3] = v.w;
+    }
+    const unsigned a0_base = smem_u32(a0s);
+    unsigned dst0;
+    {
+        const int dj = g / Kq, rem = g % Kq;
+        dst0 = map_to_rank(a0_base + 4u * (dj * M + rem % M), rem / M);
+    }
+    const unsigned buf_bytes = 16u * M;
+    const unsigned seq_addr = smem_u32(&s_seq);
+    const unsigned last_addr = smem_u32(&s_last);
+    const unsigned clv_addr = smem_u32(s_cl_v);
+    const unsigned cli_addr = smem_u32(s_cl_i);
+    __syncthreads();
+
+    for (;;) {
+        if (rank == 0 && tid == 0) {
+            const int i = atomicAdd(p.counter, 1);
+            const int seq = i < p.B ? p.order[i] : -1;
+            for (unsigned r = 0; r < CS; ++r) st_cluster_s32(map_to_rank(seq_addr, r), seq);
+        }
+        cluster_arrive();
+        cluster_wait();
+        const int seq = s_seq;
+        if (seq < 0) break;
+        long long len64 = p.lens[seq];
+        len64 = len64 < 1 ? 1 : (len64 > p.maxlen ? p.maxlen : len64);
+        const int len = static_cast<int>(len64);
+        const uint8_t *obs = p.data + (long long)seq * p.maxlen;
+        uint32_t *res = p.out + (long long)seq * p.out_stride;
+
+        for (int t = 0; t < len; t += bos) {
+            const int L = min(len - t, p.batch);        // positions of this window that exist
+            // The step whose chi the arg-max reads: the reference takes it from its first chi
+            // buffer, which after a full window with an odd last step holds the step before.
+            const int karg = (L == p.batch && ((p.batch - 1) & 1)) ? p.batch - 2 : L - 1;
+
+            // ---- window start (hmm.cu:352-376) ------------------------------------------
+            float chi[kLayers][4];
+            float e[4];
+            {
+                const float4 v = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)obs[t] * K + g));
+                e[0] = v.x; e[1] = v.y; e[2] = v.z; e[3] = v.w;
+            }
+            if (t == 0) {
+#pragma unroll
+                for (int d = 0; d < kLayers; ++d) {
+                    const float4 v = __ldg(reinterpret_cast<const float4 *>(p.initial_prob + d * K + g));
+                    chi[d][0] = v.x + e[0]; chi[d][1] = v.y + e[1]; chi[d][2] = v.z + e[2]; chi[d][3] = v.w + e[3];
+                }
+            } else {
+                const unsigned last = s_last;
+#pragma unroll
+                for (int d = 0; d < kLayers; ++d)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        chi[d][c] = (unsigned)(d * K + g + c) == last ? e[c] : -INFINITY;
+            }
+            unsigned buf = 0;
+            st_cluster_v4(dst0, chi[0][0], chi[0][1], chi[0][2], chi[0][3]);
+            cluster_arrive();
+
+            float best_v = -INFINITY;
+            unsigned best_i = 0;
+            // Arg-max over all states of the cluster, lowest index among equal maxima. Must be
+            // entered with no arrive pending; leaves none pending.
+            auto cluster_argmax = [&]() {
+                float v = chi[0][0];
+                unsigned i = (unsigned)g;
+#pragma unroll
+                for (int d = 0; d < kLayers; ++d)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) argmax_combine(v, i, chi[d][c], (unsigned)(d * K + g + c));
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+                    const unsigned oi = __shfl_xor_sync(0xffffffffu, i, o);
+                    argmax_combine(v, i, ov, oi);
+                }
+                if (lane == 0) { s_warp_v[warp] = v; s_warp_i[warp] = i; }
+                __syncthreads();
+                if (tid < (int)CS) {
+                    float bv = s_warp_v[0];
+                    unsigned bi = s_warp_i[0];
+                    for (int w = 1; w < nwarps; ++w) argmax_combine(bv, bi, s_warp_v[w], s_warp_i[w]);
+                    st_cluster_f32(map_to_rank(clv_addr + 4u * rank, tid), bv);
+                    st_cluster_s32(map_to_rank(cli_addr + 4u * rank, tid), (int)bi);
+                }
+                cluster_arrive();
+                cluster_wait();
+                best_v = s_cl_v[0];
+                best_i = s_cl_i[0];
+                for (unsigned r = 1; r < CS; ++r) argmax_combine(best_v, best_i, s_cl_v[r], s_cl_i[r]);
+                cluster_arrive();   // everyone has read s_cl_* before it can be rewritten
+                cluster_wait();
+            };
+            if (karg == 0) {
+                cluster_wait();
+                cluster_argmax();
+                cluster_arrive();
+            }
+
+            // ---- forward steps with back pointers (hmm.cu:116-176, 378-412) ----------------
+            for (int k = 1; k < L; ++k) {
+                {
+                    const float4 v = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)obs[t + k] * K + g));
+                    e[0] = v.x; e[1] = v.y; e[2] = v.z; e[3] = v.w;
+                }
+                cluster_wait();
+                const float *seg = a0s + (buf ? 4 * M : 0) + tid;
+                const float a[4] = {seg[0], seg[M], seg[2 * M], seg[3 * M]};
+                const unsigned dst = dst0 + (buf ? 0u : buf_bytes);
+                unsigned words[8];
+#pragma unroll
+                for (int d = 0; d < kLayers; ++d) {
+                    const float t2 = s_t2[d];
+                    unsigned packed = 0;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        float best = -INFINITY;
+                        unsigned code = kNoPred;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float pj = (T[j][c] + t2) + a[j];
+                            if (pj > best) { best = pj; code = j; }
+                        }
+                        const float p5 = d == 15 ? p.gamma + chi[15][c]
+                                       : d == 14 ? p.synthetic + chi[15][c]
+                                                 : 0.0f + chi[d + 1 < kLayers ? d + 1 : 15][c];
+                        if (p5 > best) { best = p5; code = 4u; }
+                        chi[d][c] = best + e[c];
+                        packed |= code << (4 * c);
+                    }
+                    if (d & 1) words[d >> 1] |= packed << 16;
+                    else words[d >> 1] = packed;
+                    if (d == 0) {
+                        st_cluster_v4(dst, chi[0][0], chi[0][1], chi[0][2], chi[0][3]);
+                        cluster_arrive();
+                    }
+                }
+                uint4 *slot = codes + ((long long)(k - 1) * Kq + gthread) * 2;
+                __stcg(slot, make_uint4(words[0], words[1], words[2], words[3]));
+                __stcg(slot + 1, make_uint4(words[4], words[5], words[6], words[7]));
+                buf ^= 1u;
+                if (k == karg && k < L - 1) {   // full window: arg-max one step before the end
+                    cluster_wait();
+                    cluster_argmax();
+                    cluster_arrive();
+                }
+            }
+            cluster_wait();
+            if (karg == L - 1 && karg > 0) cluster_argmax();
+
+            // ---- backward pass (hmm.cu:436-508) -----------------------------------------------
+            __threadfence();   // the nibbles of every CTA must be visible to the leader
+            cluster_arrive();
+            cluster_wait();
+            if (rank == 0) {
+                // positions L-1 .. batch-1 all hold the arg-max state (identity back pointers)
+                const long long hi = min((long long)t + p.batch, p.out_stride);
+                for (long long pos = t + L - 1 + tid; pos < hi; pos += NT) res[pos] = best_i;
+                if (tid == 0) {
+                    unsigned cur = best_i;
+                    unsigned anchor = cur;
+                    for (int j = L - 2; j >= 0; --j) {
+                        const unsigned s = cur % (unsigned)K, d = cur / (unsigned)K;
+                        const unsigned *w = reinterpret_cast<const unsigned *>(codes + ((long long)j * Kq + (s >> 2)) * 2);
+                        const unsigned word = __ldcg(w + (d >> 1));
+                        const unsigned code = (word >> (16 * (d & 1) + 4 * (s & 3))) & 15u;
+                        if (code < 4u) cur = code * (unsigned)Kq + (s >> 2);
+                        else if (code == 4u) cur = d == 15u ? cur : cur + (unsigned)K;
+                        res[t + j] = cur;
+                        if (j == bos - 1) anchor = cur;
+                    }
+                    if (L - 1 == bos - 1) anchor = best_i;
+                    // the next window restarts from the state decoded at its t-1
+                    for (unsigned r = 0; r < CS; ++r) st_cluster_s32(map_to_rank(last_addr, r), (int)anchor);
+                }
+            }
+            cluster_arrive();
+            cluster_wait();
+        }
+    }
+}
+
+struct VitPlan {
+    int nt = 0, cs = 0;
+};
+
+bool vit_plan(long long K, VitPlan *pl) {
+    if (K < 1024 || (K & (K - 1)) != 0) return false;
+    const long long threads = K / 4;
+    long long nt = K <= 1024 ? 64 : 512;
+    long long cs = threads / nt;
+    if (cs > 16) return false;
+    pl->nt = (int)nt;
+    pl->cs = (int)cs;
+    return true;
+}
+
+}  // namespace
+
+extern "C" int32_t parpy_b200_viterbi(float gamma, const float *initial_prob, int64_t num_states,
+                                      const float *output_prob, float synthetic_248,
+                                      const float *trans1, const float *trans2, const void *data,
+                                      const int64_t *lens, int64_t maxlen, int64_t num_instances,
+                                      int64_t batch_size, int64_t batch_overlap, uint32_t *out,
+                                      int64_t out_stride, void *stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    PB_REQUIRE(num_states >= 64 && num_states % 64 == 0, "viterbi: num_states=%lld must be a positive multiple of 64",
+               (long long)num_states);
+    PB_REQUIRE(num_instances >= 0 && num_instances <= 0x7fffffffLL, "viterbi: num_instances out of range");
+    PB_REQUIRE(maxlen >= 1 && maxlen <= 0x7fffffffLL, "viterbi: maxlen=%lld out of range", (long long)maxlen);
+    PB_REQUIRE(batch_size >= 2 && batch_size <= 65536 && batch_overlap >= 0 && batch_overlap < batch_size,
+               "viterbi: window of %lld steps with overlap %lld is not valid", (long long)batch_size,
+               (long long)batch_overlap);
+    PB_REQUIRE(out_stride >= maxlen, "viterbi: out_stride=%lld is smaller than maxlen=%lld", (long long)out_stride,
+               (long long)maxlen);
+    if (num_instances == 0) return PB_OK;
+    PB_REQUIRE(initial_prob && output_prob && trans1 && trans2 && data && lens && out, "viterbi: null pointer");
+    PB_REQUIRE(pb::aligned16(initial_prob) && pb::aligned16(output_prob) && pb::aligned16(trans1),
+               "viterbi: tables must be 16-byte aligned");
+    const long long K = num_states / kLayers;
+    VitPlan pl;
+    PB_REQUIRE(vit_plan(K, &pl), "viterbi: needs 4^k k-mers with 5 <= k <= 8 (num_states=%lld)", (long long)num_states);
+    pb::DeviceInfo dev;
+    int32_t rc = pb::device_info(&dev);
+    if (rc) return rc;
+    PB_REQUIRE(dev.cc_major >= 10, "viterbi: needs compute capability 10.x, found %d.%d", dev.cc_major, dev.cc_minor);
+
+    const size_t smem = size_t(2) * 4 * pl.nt * sizeof(float);
+    if (pl.cs > 8) PB_CUDA(cudaFuncSetAttribute(hmm_viterbi_resident, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    PB_CUDA(cudaFuncSetAttribute(hmm_viterbi_resident, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = pl.cs;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.gridDim = dim3(pl.cs, 1, 1);
+    cfg.blockDim = dim3(pl.nt, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cfg.stream = stream;
+    int max_clusters = 0;
+    PB_CUDA(cudaOccupancyMaxActiveClusters(&max_clusters, hmm_viterbi_resident, &cfg));
+    PB_REQUIRE(max_clusters >= 1, "viterbi: no cluster of %d CTAs x %d threads fits this device", pl.cs, pl.nt);
+
+    // back-pointer nibbles: (batch - 1) steps x K/4 threads x 32 bytes per resident cluster,
+    // at most ~3 GiB in total
+    const long long per_cluster = (batch_size - 1) * (K / 4) * 2;   // uint4 elements
+    const long long budget = (3LL << 30) / (per_cluster * (long long)sizeof(uint4));
+    long long clusters = std::min<long long>(std::min<long long>(max_clusters, num_instances), std::max<long long>(budget, 1));
+    void *ws_codes = nullptr, *ws = nullptr;
+    rc = pb::workspace((size_t)clusters * (size_t)per_cluster * sizeof(uint4), &ws_codes, stream, 4);
+    if (rc) return rc;
+    const size_t order_bytes = ((size_t)num_instances * sizeof(int) + 255) & ~size_t(255);
+    rc = pb::workspace(order_bytes + 512, &ws, stream, 0);
+    if (rc) return rc;
+
+    VitParams p{};
+    p.initial_prob = initial_prob;
+    p.output_prob = output_prob;
+    p.trans1 = trans1;
+    p.trans2 = trans2;
+    p.data = static_cast<const uint8_t *>(data);
+    p.lens = lens;
+    p.out = out;
+    p.order = static_cast<int *>(ws);
+    p.counter = reinterpret_cast<int *>(static_cast<char *>(ws) + order_bytes);
+    p.codes = static_cast<uint4 *>(ws_codes);
+    p.codes_per_cluster = per_cluster;
+    p.maxlen = maxlen;
+    p.out_stride = out_stride;
+    p.B = (int)num_instances;
+    p.K = (int)K;
+    p.batch = (int)batch_size;
+    p.overlap = (int)batch_overlap;
+    p.gamma = gamma;
+    p.synthetic = synthetic_248;
+    const size_t sched_smem = p.B <= 4096 ? size_t(p.B) * sizeof(int) : 0;
+    vit_schedule<<<1, 1024, sched_smem, stream>>>(lens, p.B, const_cast<int *>(p.order), p.counter);
+    PB_CUDA(cudaGetLastError());
+    cfg.gridDim = dim3(pl.cs * (unsigned)clusters, 1, 1);
+    PB_CUDA(cudaLaunchKernelEx(&cfg, hmm_viterbi_resident, p));
+    return PB_OK;
+}

@@ -136,3 +136,40 @@ def read_signals(signals_path):
 def read_trellis_inputs(model_path, signals_path):
     """benchmarks/forward.py:40-87: ``(hmm, seqs)`` for a model file and a signal file."""
     return read_model(model_path), read_signals(signals_path)
+
+
+def viterbi(hmm, seqs, batch_size=1024, batch_overlap=128):
+    """Most likely state path of every sequence (windowed Viterbi with the
+    semantics of benchmarks/7mer/trellis.py:25-83 and benchmarks/7mer/hmm.cu).
+    ``hmm`` and ``seqs`` are the dictionaries ``forward_kernel`` takes, on the
+    device. Returns a uint32-valued int64 CUDA tensor [B, maxlen] whose row i holds
+    ``lens[i]`` decoded states, and the lengths; use ``viterbi_paths`` for a list
+    of per-sequence NumPy arrays."""
+    import ctypes
+    import torch
+    from . import _native
+    from .buffer import from_array
+    from .ops import scalar
+    n = int(scalar(from_array(hmm["num_states"]), "num_states")) if hasattr(hmm["num_states"], "shape") else int(hmm["num_states"])
+    data, lens = seqs["data"], seqs["lens"]
+    if lens.dtype != torch.int64:
+        lens = lens.to(torch.int64)
+    batch, maxlen = data.shape
+    out = torch.zeros((batch, maxlen), dtype=torch.int32, device=data.device)
+    P = ctypes.c_void_p
+    rc = _native.lib().parpy_b200_viterbi(
+        float(hmm["gamma"]), P(hmm["initial_prob"].data_ptr()), n, P(hmm["output_prob"].data_ptr()),
+        float(hmm["synthetic_248"]), P(hmm["trans1"].data_ptr()), P(hmm["trans2"].data_ptr()),
+        P(data.data_ptr()), P(lens.data_ptr()), maxlen, batch, batch_size, batch_overlap,
+        P(out.data_ptr()), maxlen, P(torch.cuda.current_stream().cuda_stream))
+    _native.check(rc, "viterbi")
+    return out, lens
+
+
+def viterbi_paths(hmm, seqs, batch_size=1024, batch_overlap=128):
+    """``viterbi`` with the result trimmed per sequence, as the reference's wrapper
+    returns it (benchmarks/7mer/trellis.py:64-66): a list of uint32 NumPy arrays."""
+    import numpy as np
+    out, lens = viterbi(hmm, seqs, batch_size, batch_overlap)
+    host, hl = out.cpu().numpy().view(np.uint32), lens.cpu().numpy()
+    return [host[i, :int(hl[i])].copy() for i in range(host.shape[0])]

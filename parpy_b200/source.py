@@ -59,7 +59,11 @@ def kernel_source(op_name):
         raise RuntimeError(f"no kernel source registered for '{op_name}'")
     parts = [f"// parpy_b200: amalgamated source for '{op_name}' (sm_100a)\n"
              f"// build: nvcc -std=c++17 -O3 -gencode arch=compute_100a,code=sm_100a -shared -Xcompiler -fPIC\n"]
-    for path in (_HEADER, _CSRC / "common.cuh", _CSRC / "runtime.cu", _CSRC / KERNEL_FILES[op_name]):
+    files = [_HEADER, _CSRC / "common.cuh"]
+    if KERNEL_FILES[op_name].startswith("hmm_"):
+        files.append(_CSRC / "cluster.cuh")
+    files += [_CSRC / "runtime.cu", _CSRC / KERNEL_FILES[op_name]]
+    for path in files:
         parts.append(f"\n// ======== {path.name} ========\n")
         parts.append(_strip_local_includes(path.read_text()))
     return "".join(parts)

@@ -1,0 +1,136 @@
+"""Windowed Viterbi decoding: the CPU oracle against an independent NumPy
+restatement (CPU), and against the reference's own CUDA and the library's kernel
+(GPU). Decoded states are integers: every comparison is exact."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import load_model, load_signals, shortest_reads
+from oracle import oracle
+from parpy_b200 import synthetic
+
+
+def viterbi_numpy_single_window(hmm, obs):
+    """Plain Viterbi over one window (no re-anchoring), vectorised over states,
+    candidate order and strict '>' as in benchmarks/7mer/hmm.cu:116-176."""
+    f = np.float32
+    N = int(hmm["num_states"])
+    K = N // 16
+    t1, t2 = hmm["trans1"].numpy(), hmm["trans2"].numpy()
+    outp, init = hmm["output_prob"].numpy(), hmm["initial_prob"].numpy()
+    gamma, syn = f(float(hmm["gamma"])), f(float(hmm["synthetic_248"]))
+    s = np.arange(N)
+    kmer, layer = s % K, s // K
+    preds = np.stack([j * (K // 4) + (s // 4) % (K // 4) for j in range(4)])           # [4, N]
+    tr = (t1[preds % K, s % 4] + t2[layer][None, :]).astype(f)
+    p5 = np.where(layer == 15, s, s + K)
+    c5 = np.where(layer == 15, gamma, np.where(layer == 14, syn, f(0.0))).astype(f)
+    chi = (init + outp[obs[0]][kmer]).astype(f)
+    back = []
+    with np.errstate(invalid="ignore"):
+        for t in range(1, len(obs)):
+            cand = np.concatenate([(tr + chi[preds]).astype(f), (c5 + chi[np.minimum(p5, N - 1)]).astype(f)[None]])
+            idx = np.concatenate([preds, p5[None]])
+            best = np.full(N, -np.inf, dtype=f)
+            arg = np.full(N, -1, dtype=np.int64)
+            for j in range(5):
+                take = cand[j] > best
+                best = np.where(take, cand[j], best)
+                arg = np.where(take, idx[j], arg)
+            back.append(arg)
+            chi = (best + outp[obs[t]][kmer]).astype(f)
+    cur = int(np.argmax(chi))          # first maximum
+    path = [cur]
+    for arg in reversed(back):
+        cur = int(arg[cur]) if arg[cur] >= 0 else cur
+        path.append(cur)
+    return np.array(path[::-1], dtype=np.uint32)
+
+
+def test_oracle_matches_plain_viterbi_inside_one_window():
+    hmm = load_model("3mer")
+    seqs = load_signals(shortest_reads(2))
+    for i in range(2):
+        obs = seqs["data"][i, :300].numpy().view(np.uint8)
+        one = {"data": seqs["data"][i:i + 1, :300].contiguous(), "lens": torch.tensor([300])}
+        got = oracle.viterbi(hmm, one, batch_size=1024, batch_overlap=128)[0]
+        assert np.array_equal(got, viterbi_numpy_single_window(hmm, obs))
+
+
+def test_oracle_windowing_rules():
+    hmm = synthetic.hmm_model(3, seed=3)
+    seqs = synthetic.hmm_sequences(5, 1, 90, seed=4)
+    paths = oracle.viterbi(hmm, seqs, batch_size=16, batch_overlap=4)
+    for i, path in enumerate(paths):
+        n = int(seqs["lens"][i])
+        assert len(path) == n and path.max() < 1024
+        # every consecutive pair is an allowed transition of the model, except at a window
+        # start, where the reference pins the state at t to the state decoded at t-1
+        # (hmm.cu:364-376): there the pair repeats
+        K = 64
+        for pos, (a, b) in enumerate(zip(path[:-1], path[1:]), start=1):
+            la, ka, lb, kb = a // K, a % K, b // K, b % K
+            chain = (ka == kb) and (la == lb + 1 or (la == 15 and lb == 15))
+            shift = (la == 0) and (kb // 4 == ka % (K // 4))
+            restart = pos % (16 - 4) == 0 and a == b
+            assert chain or shift or restart, (i, pos, a, b)
+    # a window at least as long as the sequence is plain Viterbi
+    obs = seqs["data"][0, :int(seqs["lens"][0])].numpy().view(np.uint8)
+    whole = oracle.viterbi(hmm, {"data": seqs["data"][:1], "lens": seqs["lens"][:1]}, 1024, 128)[0]
+    assert np.array_equal(whole, viterbi_numpy_single_window(hmm, obs))
+
+
+# ---- GPU ------------------------------------------------------------------------------------
+def _dev(d):
+    return {k: (v.cuda() if isinstance(v, torch.Tensor) and v.dim() > 0 else v) for k, v in d.items()}
+
+
+@pytest.mark.gpu
+def test_oracle_agrees_with_the_reference_cuda_on_the_5mer_fixture():
+    if not oracle.trellis_available(5):
+        pytest.skip("oracle/_ref/trellis_5mer.so has not been built")
+    hmm, seqs = load_model("5mer"), load_signals(shortest_reads(3))      # ~2800 steps: 4 windows each
+    ref = oracle.trellis_viterbi(5, hmm, seqs)
+    ours = oracle.viterbi(hmm, seqs)
+    for r, o in zip(ref, ours):
+        assert np.array_equal(r, o)
+
+
+@pytest.mark.gpu
+def test_kernel_matches_oracle_on_the_5mer_fixture():
+    from parpy_b200 import hmm as hmm_mod
+    hmm, seqs = load_model("5mer"), load_signals(shortest_reads(5))
+    got = hmm_mod.viterbi_paths(_dev(hmm), _dev(seqs))
+    exp = oracle.viterbi(hmm, seqs)
+    for g, e in zip(got, exp):
+        assert np.array_equal(g, e)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("k,batch,overlap,nseq,maxlen", [(5, 16, 4, 23, 120), (5, 7, 2, 9, 40), (5, 2, 0, 4, 9),
+                                                       (6, 32, 8, 5, 100), (7, 1024, 128, 2, 1100)])
+def test_kernel_matches_oracle_small_windows_and_ragged_lengths(k, batch, overlap, nseq, maxlen):
+    from parpy_b200 import hmm as hmm_mod
+    hmm = synthetic.hmm_model(k, seed=10 + k)
+    seqs = synthetic.hmm_sequences(nseq, 1, maxlen, seed=20 + k)
+    seqs["lens"][0] = 1
+    if nseq > 2:
+        seqs["lens"][1] = min(maxlen, batch - overlap)           # exactly one window stride
+        seqs["lens"][2] = min(maxlen, batch)                     # exactly one full window
+    if k == 7:
+        seqs["lens"][0], seqs["lens"][1] = 1100, 897             # full window + remainder; stride + 1
+    exp = oracle.viterbi(hmm, seqs, batch, overlap)
+    got = hmm_mod.viterbi_paths(_dev(hmm), _dev(seqs), batch, overlap)
+    for i, (g, e) in enumerate(zip(got, exp)):
+        assert np.array_equal(g, e), (i, int(seqs["lens"][i]))
+
+
+@pytest.mark.gpu
+def test_viterbi_argument_checks(native):
+    from parpy_b200 import hmm as hmm_mod
+    hmm, seqs = _dev(synthetic.hmm_model(3)), _dev(synthetic.hmm_sequences(2, 5, 9))
+    with pytest.raises(RuntimeError, match="5 <= k <= 8"):
+        hmm_mod.viterbi(hmm, seqs)
+    hmm5 = _dev(synthetic.hmm_model(5))
+    with pytest.raises(RuntimeError, match="window of"):
+        hmm_mod.viterbi(hmm5, seqs, batch_size=8, batch_overlap=8)
