@@ -64,6 +64,9 @@ def report(name, ms, nbytes, extra=None):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--quick", action="store_true", help="smaller SpMV / reduction sizes")
+    ap.add_argument("--ref-cuda", action="store_true",
+                    help="also time the reference's CUDA Viterbi (needs oracle/_ref, built where the "
+                         "reference checkout is present) on a few sequences")
     ap.add_argument("--profile", action="store_true",
                     help="one warm-up and one timed launch per kernel (for captures under a profiler)")
     args = ap.parse_args()
@@ -136,6 +139,30 @@ def main():
     ms = timed(lambda: hmm_mod.forward_parpy(dh, ds), flush=flush)
     report("hmm_forward_5mer[B=100,T=2000]", ms, synthetic.forward_algorithmic_bytes(hmm, seqs),
            {"state_steps_per_s": synthetic.state_steps(hmm, seqs) / statistics.median(ms) * 1e3})
+
+    # windowed Viterbi decoding (windows of 1024 steps, overlap 128), 5-mer and 7-mer models
+    for k, nseq, lo, hi in ((5, 100, 2000, 2000), (7, 66, 1000, 4000)):
+        hmm = synthetic.hmm_model(k)
+        seqs = synthetic.hmm_sequences(nseq, lo, hi)
+        dh, ds = hmm_mod.to_device(hmm), hmm_mod.to_device(seqs)
+        ms = timed(lambda: hmm_mod.viterbi(dh, ds), reps=3 if args.profile is False else 1, warmup=1, flush=flush)
+        work = synthetic.state_steps(hmm, seqs)
+        extra = {"state_steps_per_s": work / statistics.median(ms) * 1e3,
+                 "backpointer_bytes": int(seqs["lens"].sum()) * (4 ** k // 4) * 32}
+        if args.ref_cuda:
+            import time
+            sys.path.insert(0, ROOT)
+            from oracle import oracle
+            if oracle.trellis_available(k):
+                n = 4
+                sub = {"data": seqs["data"][:n].contiguous(), "lens": seqs["lens"][:n].contiguous()}
+                oracle.trellis_viterbi(k, hmm, {"data": sub["data"][:1], "lens": sub["lens"][:1]})
+                t0 = time.perf_counter()
+                oracle.trellis_viterbi(k, hmm, sub, num_parallel=n)
+                dt = time.perf_counter() - t0
+                extra["reference_cuda_state_steps_per_s"] = int(hmm["num_states"]) * int(sub["lens"].sum()) / dt
+                extra["reference_cuda_sample"] = f"first {n} sequences, num_parallel={n}, host arrays in and out"
+        report(f"viterbi_{k}mer[B={nseq}, len {lo}-{hi}]", ms, synthetic.forward_algorithmic_bytes(hmm, seqs), extra)
 
 
 if __name__ == "__main__":
