@@ -291,9 +291,11 @@ def trellis_viterbi(k, hmm, seqs, num_parallel=1):
         padded[i, :n] = data[i, :n]
     padded = np.ascontiguousarray(padded.reshape(-1))
     lens = np.ascontiguousarray(lens)
+    # state_t is uint16 in the 5-mer build and uint32 in the 7-mer build (hmm.cu:4)
+    ctype = ctypes.c_uint16 if k == 5 else ctypes.c_uint32
     t.viterbi.argtypes = [_P, _P, ctypes.c_int, ctypes.c_int, ctypes.c_int]
-    t.viterbi.restype = ctypes.POINTER(ctypes.c_uint32)
+    t.viterbi.restype = ctypes.POINTER(ctype)
     ptr = t.viterbi(padded.ctypes.data, lens.ctypes.data, maxlen, int(num_parallel), len(lens))
-    res = np.ctypeslib.as_array(ptr, shape=(len(lens), maxlen)).copy()
+    res = np.ctypeslib.as_array(ptr, shape=(len(lens), maxlen)).astype(np.uint32)
     ctypes.CDLL(None).free(ptr)
     return [res[i, :int(lens[i])].copy() for i in range(len(lens))]

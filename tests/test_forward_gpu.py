@@ -71,7 +71,7 @@ def test_7mer_against_oracle_with_final_alpha(native, oracle_mod):
     # checks every state of the final alpha vector, not just the scalar.
     from parpy_b200 import synthetic
     hmm = synthetic.hmm_model(7)
-    seqs = synthetic.hmm_sequences(5, 1, 120, seed=99)
+    seqs = synthetic.hmm_sequences(5, 2, 120, seed=99)     # lengths are only ever shortened below
     seqs["lens"][0] = 1
     seqs["lens"][1] = 2
     exp, exp_alpha = oracle_mod.forward(hmm, seqs, want_alpha=True)

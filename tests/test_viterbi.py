@@ -112,13 +112,16 @@ def test_kernel_matches_oracle_on_the_5mer_fixture():
 def test_kernel_matches_oracle_small_windows_and_ragged_lengths(k, batch, overlap, nseq, maxlen):
     from parpy_b200 import hmm as hmm_mod
     hmm = synthetic.hmm_model(k, seed=10 + k)
-    seqs = synthetic.hmm_sequences(nseq, 1, maxlen, seed=20 + k)
-    seqs["lens"][0] = 1
+    # observations valid over the whole width, then ragged lengths on top (never beyond the data)
+    seqs = synthetic.hmm_sequences(nseq, maxlen, maxlen, seed=20 + k)
+    lens = torch.randint(1, maxlen + 1, (nseq,), generator=torch.Generator().manual_seed(30 + k))
+    lens[0] = 1
     if nseq > 2:
-        seqs["lens"][1] = min(maxlen, batch - overlap)           # exactly one window stride
-        seqs["lens"][2] = min(maxlen, batch)                     # exactly one full window
+        lens[1] = min(maxlen, batch - overlap)           # exactly one window stride
+        lens[2] = min(maxlen, batch)                     # exactly one full window
     if k == 7:
-        seqs["lens"][0], seqs["lens"][1] = 1100, 897             # full window + remainder; stride + 1
+        lens[0], lens[1] = 1100, 897                     # full window + remainder; stride + 1
+    seqs["lens"] = lens
     exp = oracle.viterbi(hmm, seqs, batch, overlap)
     got = hmm_mod.viterbi_paths(_dev(hmm), _dev(seqs), batch, overlap)
     for i, (g, e) in enumerate(zip(got, exp)):
