@@ -269,36 +269,43 @@ struct Red {
     }
 };
 
-// Reduces x[begin, end) with the calling CTA: 4 independent accumulators per
-// thread, 128-bit loads on the aligned middle part. Every thread returns the
-// CTA-wide value.
+// Reduces the part of x[0, n) that belongs to CTA `part` of `parts`: tiles of
+// 4 x blockDim float4 dealt round-robin to the CTAs (so that the CTAs of a row read
+// one contiguous region at any moment), 4 independent accumulators per thread,
+// 128-bit streaming loads; CTA 0 also takes the unaligned ends. Every thread returns
+// the CTA-wide value.
 template <int OP>
-__device__ float block_reduce_range(const float *__restrict__ x, long long begin, long long end,
+__device__ float block_reduce_tiles(const float *__restrict__ x, long long n, int part, int parts,
                                     float *s_red) {
     using R = Red<OP>;
     float a0 = R::neutral(), a1 = R::neutral(), a2 = R::neutral(), a3 = R::neutral();
-    // scalar head up to a 16-byte boundary
-    long long head = begin;
-    while (head < end && (reinterpret_cast<uintptr_t>(x + head) & 15u)) ++head;
-    for (long long i = begin + threadIdx.x; i < head; i += blockDim.x) a0 = R::apply(a0, x[i]);
-    const long long nvec = (end - head) >> 2;
+    long long head = 0;
+    while (head < n && (reinterpret_cast<uintptr_t>(x + head) & 15u)) ++head;
+    const long long nvec = (n - head) >> 2;
     const float4 *xv = reinterpret_cast<const float4 *>(x + head);
-    long long i = threadIdx.x;
-    for (; i + 3LL * blockDim.x < nvec; i += 4LL * blockDim.x) {
-        const float4 p = __ldcs(xv + i);
-        const float4 q = __ldcs(xv + i + blockDim.x);
-        const float4 r = __ldcs(xv + i + 2LL * blockDim.x);
-        const float4 t = __ldcs(xv + i + 3LL * blockDim.x);
-        a0 = R::apply(a0, R::apply(R::apply(p.x, p.y), R::apply(p.z, p.w)));
-        a1 = R::apply(a1, R::apply(R::apply(q.x, q.y), R::apply(q.z, q.w)));
-        a2 = R::apply(a2, R::apply(R::apply(r.x, r.y), R::apply(r.z, r.w)));
-        a3 = R::apply(a3, R::apply(R::apply(t.x, t.y), R::apply(t.z, t.w)));
+    const long long bd = blockDim.x, tile = 4 * bd;
+    for (long long base = part * tile; base < nvec; base += (long long)parts * tile) {
+        const long long i = base + threadIdx.x;
+        if (base + tile <= nvec) {
+            const float4 p = __ldcs(xv + i);
+            const float4 q = __ldcs(xv + i + bd);
+            const float4 r = __ldcs(xv + i + 2 * bd);
+            const float4 t = __ldcs(xv + i + 3 * bd);
+            a0 = R::apply(a0, R::apply(R::apply(p.x, p.y), R::apply(p.z, p.w)));
+            a1 = R::apply(a1, R::apply(R::apply(q.x, q.y), R::apply(q.z, q.w)));
+            a2 = R::apply(a2, R::apply(R::apply(r.x, r.y), R::apply(r.z, r.w)));
+            a3 = R::apply(a3, R::apply(R::apply(t.x, t.y), R::apply(t.z, t.w)));
+        } else {
+            for (long long j = i; j < nvec; j += bd) {
+                const float4 p = __ldcs(xv + j);
+                a0 = R::apply(a0, R::apply(R::apply(p.x, p.y), R::apply(p.z, p.w)));
+            }
+        }
     }
-    for (; i < nvec; i += blockDim.x) {
-        const float4 p = __ldcs(xv + i);
-        a0 = R::apply(a0, R::apply(R::apply(p.x, p.y), R::apply(p.z, p.w)));
+    if (part == 0) {
+        for (long long j = threadIdx.x; j < head; j += bd) a1 = R::apply(a1, x[j]);
+        for (long long j = head + (nvec << 2) + threadIdx.x; j < n; j += bd) a1 = R::apply(a1, x[j]);
     }
-    for (long long j = head + (nvec << 2) + threadIdx.x; j < end; j += blockDim.x) a1 = R::apply(a1, x[j]);
     float v = R::apply(R::apply(a0, a1), R::apply(a2, a3));
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
     v = R::warp(v);
@@ -325,10 +332,12 @@ __global__ void __launch_bounds__(256) reduce_warp_rows(const float *__restrict_
         const float4 *sv = reinterpret_cast<const float4 *>(src);
         const long long nvec = M >> 2;
         long long i = lane;
-        for (; i + 32 < nvec; i += 64) {
-            const float4 p = __ldcs(sv + i), q = __ldcs(sv + i + 32);
+        for (; i + 96 < nvec; i += 128) {   // four 128-bit loads in flight per lane
+            const float4 p = __ldcs(sv + i), q = __ldcs(sv + i + 32), r = __ldcs(sv + i + 64), t = __ldcs(sv + i + 96);
             a = R::apply(a, R::apply(R::apply(p.x, p.y), R::apply(p.z, p.w)));
             b = R::apply(b, R::apply(R::apply(q.x, q.y), R::apply(q.z, q.w)));
+            a = R::apply(a, R::apply(R::apply(r.x, r.y), R::apply(r.z, r.w)));
+            b = R::apply(b, R::apply(R::apply(t.x, t.y), R::apply(t.z, t.w)));
         }
         for (; i < nvec; i += 32) {
             const float4 p = __ldcs(sv + i);
@@ -355,10 +364,7 @@ __global__ void __launch_bounds__(512) reduce_split_rows(const float *__restrict
     __shared__ bool s_last;
     const long long row = blockIdx.y;
     const int part = blockIdx.x;
-    const long long chunk = (((M + parts - 1) / parts) + 3) & ~3LL;
-    const long long begin = pb::ll_min(M, part * chunk);
-    const long long end = pb::ll_min(M, begin + chunk);
-    const float v = block_reduce_range<OP>(x + row * M, begin, end, s_red);
+    const float v = block_reduce_tiles<OP>(x + row * M, M, part, parts, s_red);
     if (parts == 1) {
         if (threadIdx.x == 0) out[row] = v;
         return;
@@ -397,39 +403,44 @@ __global__ void __launch_bounds__(512) sum_max_fused(const float *__restrict__ x
     __shared__ float s_a[32], s_b[32];
     __shared__ bool s_last;
     const int part = blockIdx.x;
-    const long long chunk = (((n + parts - 1) / parts) + 3) & ~3LL;
-    const long long begin = pb::ll_min(n, part * chunk);
-    const long long end = pb::ll_min(n, begin + chunk);
+    // Tiles of 4 x blockDim float4 dealt round-robin to the CTAs, so that at any moment the
+    // whole grid reads one contiguous region of the vector. CTA 0 takes the unaligned ends.
     float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f, m0 = -INFINITY, m1 = -INFINITY;
-    long long head = begin;
-    while (head < end && (reinterpret_cast<uintptr_t>(x + head) & 15u)) ++head;
-    for (long long i = begin + threadIdx.x; i < head; i += blockDim.x) {
-        s0 += x[i];
-        m0 = fmaxf(m0, x[i]);
-    }
-    const long long nvec = (end - head) >> 2;
+    long long head = 0;
+    while (head < n && (reinterpret_cast<uintptr_t>(x + head) & 15u)) ++head;
+    const long long nvec = (n - head) >> 2;
     const float4 *xv = reinterpret_cast<const float4 *>(x + head);
-    long long i = threadIdx.x;
-    for (; i + 3LL * blockDim.x < nvec; i += 4LL * blockDim.x) {
-        const float4 p = __ldcs(xv + i);
-        const float4 q = __ldcs(xv + i + blockDim.x);
-        const float4 r = __ldcs(xv + i + 2LL * blockDim.x);
-        const float4 t = __ldcs(xv + i + 3LL * blockDim.x);
-        s0 += (p.x + p.y) + (p.z + p.w);
-        s1 += (q.x + q.y) + (q.z + q.w);
-        s2 += (r.x + r.y) + (r.z + r.w);
-        s3 += (t.x + t.y) + (t.z + t.w);
-        m0 = fmaxf(m0, fmaxf(fmaxf(fmaxf(p.x, p.y), fmaxf(p.z, p.w)), fmaxf(fmaxf(q.x, q.y), fmaxf(q.z, q.w))));
-        m1 = fmaxf(m1, fmaxf(fmaxf(fmaxf(r.x, r.y), fmaxf(r.z, r.w)), fmaxf(fmaxf(t.x, t.y), fmaxf(t.z, t.w))));
+    const long long bd = blockDim.x, tile = 4 * bd;
+    for (long long base = part * tile; base < nvec; base += (long long)parts * tile) {
+        const long long i = base + threadIdx.x;
+        if (base + tile <= nvec) {
+            const float4 p = __ldcs(xv + i);
+            const float4 q = __ldcs(xv + i + bd);
+            const float4 r = __ldcs(xv + i + 2 * bd);
+            const float4 t = __ldcs(xv + i + 3 * bd);
+            s0 += (p.x + p.y) + (p.z + p.w);
+            s1 += (q.x + q.y) + (q.z + q.w);
+            s2 += (r.x + r.y) + (r.z + r.w);
+            s3 += (t.x + t.y) + (t.z + t.w);
+            m0 = fmaxf(m0, fmaxf(fmaxf(fmaxf(p.x, p.y), fmaxf(p.z, p.w)), fmaxf(fmaxf(q.x, q.y), fmaxf(q.z, q.w))));
+            m1 = fmaxf(m1, fmaxf(fmaxf(fmaxf(r.x, r.y), fmaxf(r.z, r.w)), fmaxf(fmaxf(t.x, t.y), fmaxf(t.z, t.w))));
+        } else {
+            for (long long j = i; j < nvec; j += bd) {
+                const float4 p = __ldcs(xv + j);
+                s0 += (p.x + p.y) + (p.z + p.w);
+                m0 = fmaxf(m0, fmaxf(fmaxf(p.x, p.y), fmaxf(p.z, p.w)));
+            }
+        }
     }
-    for (; i < nvec; i += blockDim.x) {
-        const float4 p = __ldcs(xv + i);
-        s0 += (p.x + p.y) + (p.z + p.w);
-        m0 = fmaxf(m0, fmaxf(fmaxf(p.x, p.y), fmaxf(p.z, p.w)));
-    }
-    for (long long j = head + (nvec << 2) + threadIdx.x; j < end; j += blockDim.x) {
-        s1 += x[j];
-        m1 = fmaxf(m1, x[j]);
+    if (part == 0) {
+        for (long long j = threadIdx.x; j < head; j += bd) {
+            s1 += x[j];
+            m1 = fmaxf(m1, x[j]);
+        }
+        for (long long j = head + (nvec << 2) + threadIdx.x; j < n; j += bd) {
+            s1 += x[j];
+            m1 = fmaxf(m1, x[j]);
+        }
     }
     float s = (s0 + s1) + (s2 + s3), m = fmaxf(m0, m1);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
@@ -490,15 +501,17 @@ __global__ void __launch_bounds__(512) sum_max_fused(const float *__restrict__ x
 template <int OP>
 int32_t launch_reduce(const float *x, float *out, long long N, long long M, cudaStream_t stream,
                       const pb::DeviceInfo &dev) {
-    if (M <= 4096 && N >= 4LL * dev.sm_count) {
+    if (M <= 16384 && N >= 8LL * dev.sm_count) {
         const int wpb = 8;
         const long long blocks = (N + wpb - 1) / wpb;
         reduce_warp_rows<OP><<<(unsigned)blocks, wpb * 32, 0, stream>>>(x, out, N, M);
         PB_CUDA(cudaGetLastError());
         return PB_OK;
     }
-    // CTAs per row so that the grid fills the machine (8 CTAs of 512 threads per SM at most 4)
-    const long long target = 4LL * dev.sm_count;
+    // CTAs per row so that the grid is one resident wave
+    int per_sm = 1;
+    PB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, reduce_split_rows<OP>, 512, 0));
+    const long long target = (long long)std::max(per_sm, 1) * dev.sm_count;
     long long parts = std::max<long long>(1, std::min<long long>((target + N - 1) / N, (M + 8191) / 8192));
     parts = std::min<long long>(parts, 1024);
     PB_REQUIRE(N <= 65535, "reduce: more than 65535 rows of more than 4096 elements are not supported");
@@ -566,7 +579,10 @@ int32_t parpy_b200_sum_max(const float *x, int64_t n, float *out_sum, float *out
     pb::DeviceInfo dev;
     int32_t rc = pb::device_info(&dev);
     if (rc) return rc;
-    long long parts = std::min<long long>(4LL * dev.sm_count, (n + 16383) / 16384);
+    // one resident wave: as many CTAs as the kernel's registers allow per SM
+    int per_sm = 1;
+    PB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, sum_max_fused, 512, 0));
+    long long parts = std::min<long long>((long long)std::max(per_sm, 1) * dev.sm_count, (n + 16383) / 16384);
     parts = std::max<long long>(parts, 1);
     void *ws = nullptr;
     rc = pb::zeroed_workspace(256, (size_t)parts * 2 * sizeof(float), &ws, stream);
