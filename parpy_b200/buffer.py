@@ -74,13 +74,20 @@ def _host_view(t):
 
 
 class Buffer:
-    def __init__(self, buf, shape, dtype, src=None):
+    def __init__(self, buf, shape, dtype, src=None, refcount=None):
         if type(self) is Buffer:
             raise RuntimeError("Cannot construct instance of base Buffer class")
         self.buf = buf
         self.shape = tuple(shape)
         self.dtype = _resolve_dtype(dtype)
         self.src = src
+        # views made by reshape / same-width with_type share one count; the host array
+        # is written back when the last of them goes (python/parpy/buffer.py:117-144)
+        if refcount is None:
+            self.refcount = [1]
+        else:
+            self.refcount = refcount
+            self.refcount[0] += 1
 
     def __float__(self):
         if len(self.shape) == 0:
@@ -112,13 +119,15 @@ class CudaBuffer(Buffer):
 
     backend = CompileBackend.Cuda
 
-    def __init__(self, buf, shape, dtype, src=None):
-        super().__init__(buf, shape, dtype, src)
+    def __init__(self, buf, shape, dtype, src=None, refcount=None):
+        super().__init__(buf, shape, dtype, src, refcount)
         self.__cuda_array_interface__ = buf.__cuda_array_interface__
 
     def __del__(self):
         try:
-            self.release()
+            self.refcount[0] -= 1
+            if self.refcount[0] == 0:
+                self.release()
         except Exception:
             pass
 
@@ -168,16 +177,43 @@ class CudaBuffer(Buffer):
         new_shape = tuple(dims)
         if math.prod(self.shape) != math.prod(new_shape):
             raise ValueError(f"Cannot reshape buffer of shape {self.shape} to {new_shape}")
-        return CudaBuffer(self.buf.reshape(new_shape), new_shape, self.dtype, self.src)
+        return CudaBuffer(self.buf.reshape(new_shape), new_shape, self.dtype, self.src, self.refcount)
 
     def with_type(self, new_dtype):
         new_dtype = _resolve_dtype(new_dtype)
         if not isinstance(new_dtype, DataType):
             raise ValueError(f"Found unsupported data type: {type(new_dtype)}")
         if self.dtype.size() == new_dtype.size():
-            return CudaBuffer(self.buf.view(new_dtype.to_torch()), self.shape, new_dtype, self.src)
+            return CudaBuffer(self.buf.view(new_dtype.to_torch()), self.shape, new_dtype, self.src, self.refcount)
         t = self.buf.detach().clone().to(new_dtype.to_torch())
         return CudaBuffer(t, self.shape, new_dtype)
+
+
+class DummyBuffer(Buffer):
+    """Describes a host array without touching a device: what `from_array(t, None)`
+    returns, used to inspect arguments where no GPU is available
+    (python/parpy/buffer.py:206-228)."""
+
+    backend = None
+
+    def __init__(self, buf, shape, dtype, src=None, refcount=None):
+        super().__init__(buf, shape, dtype, src, refcount)
+        self.__array_interface__ = {"data": (buf, False), "strides": None, "typestr": str(self.dtype),
+                                    "shape": self.shape, "version": 3}
+
+    @staticmethod
+    def _from_array(t):
+        try:
+            shape, dtype, ptr = _extract_array_interface(t, allow_cuda=True)
+        except ValueError:
+            raise RuntimeError(f"Cannot convert argument {t} to CPU buffer")
+        return DummyBuffer(ptr, shape, dtype)
+
+    def _get_ptr(self):
+        return self.buf
+
+    def numpy(self):
+        return np.asarray(self)
 
 
 def empty(shape, dtype, backend=CompileBackend.Cuda):
@@ -204,7 +240,9 @@ def zeros_like(b):
 
 def from_array(t, backend=CompileBackend.Cuda):
     """Wraps (CUDA array) or stages (host array) ``t`` as a device buffer."""
-    if backend is None or backend in (CompileBackend.Cuda, CompileBackend.Auto):
+    if backend is None:
+        return DummyBuffer._from_array(t)
+    if backend in (CompileBackend.Cuda, CompileBackend.Auto):
         return CudaBuffer._from_array(t)
     if backend == CompileBackend.Metal:
         raise RuntimeError("The Metal backend is not available in parpy_b200")

@@ -191,3 +191,15 @@ def test_hdf5_reader_reproduces_the_committed_fixtures():
     sig = make_golden.build_signals(os.path.join(ref, "test", "data", "signals.hdf5"))
     stored = np.load(os.path.join(GOLDEN, "signals.npz"))
     assert np.array_equal(sig["data"], stored["data"]) and np.array_equal(sig["lens"], stored["lens"])
+
+
+def test_buffer_module_without_a_device():
+    # test/test_buffer.py:59-73
+    a = np.ndarray((20, 10, 32), dtype=np.float32)
+    b = parpy.buffer.from_array(a, None)
+    assert b.shape == (20, 10, 32)
+    assert b.dtype == parpy.buffer.DataType.from_elem_size(parpy.types.F32)
+    with pytest.raises(ValueError, match="Cannot convert to buffer of unknown backend 5"):
+        parpy.buffer.from_array(np.ndarray((10,), dtype=np.float32), 5)
+    with pytest.raises(RuntimeError, match="Metal"):
+        parpy.buffer.from_array(a, parpy.CompileBackend.Metal)
