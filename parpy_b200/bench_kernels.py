@@ -67,9 +67,12 @@ def main():
     ap.add_argument("--ref-cuda", action="store_true",
                     help="also time the reference's CUDA Viterbi (needs oracle/_ref, built where the "
                          "reference checkout is present) on a few sequences")
+    ap.add_argument("--only", default="", help="comma-separated sections to run: softmax, reduce, spmv, "
+                                               "sddmm, forward5, viterbi (default: all)")
     ap.add_argument("--profile", action="store_true",
                     help="one warm-up and one timed launch per kernel (for captures under a profiler)")
     args = ap.parse_args()
+    want = lambda name: not args.only or name in args.only.split(",")
     if args.profile:
         global timed
         plain = timed
@@ -80,7 +83,7 @@ def main():
     g = torch.Generator().manual_seed(1234)
 
     # softmax: the reference test's shape, and a shape large enough to measure bandwidth
-    for shape in ((256, 1024), (32768, 1024), (4096, 16384)):
+    for shape in ((256, 1024), (32768, 1024), (4096, 16384)) if want("softmax") else ():
         x = torch.randn(shape, generator=g, dtype=torch.float32).cuda()
         out = torch.empty_like(x)
         ms = timed(lambda: _native.check(lib.parpy_b200_softmax(P(x.data_ptr()), shape[0], shape[1],
@@ -88,6 +91,19 @@ def main():
         report(f"softmax[{shape[0]},{shape[1]}]", ms, 8 * x.numel())
         del x, out
 
+    if want("reduce"):
+        bench_reductions(args, lib, stream, flush)
+    if want("spmv"):
+        bench_spmv(args, lib, stream, flush, g)
+    if want("sddmm"):
+        bench_sddmm(lib, stream, flush, g)
+    if want("forward5"):
+        bench_forward5(flush)
+    if want("viterbi"):
+        bench_viterbi(args, flush)
+
+
+def bench_reductions(args, lib, stream, flush):
     # fused sum + max over a long vector (2^30 elements = 4 GiB)
     n = 1 << (26 if args.quick else 30)
     v = torch.empty(n, dtype=torch.float32, device="cuda").normal_(generator=torch.Generator(device="cuda").manual_seed(1234))
@@ -104,6 +120,8 @@ def main():
     report("max_rows[8192,8192]", ms, 4 * rows.numel())
     del v, rows
 
+
+def bench_spmv(args, lib, stream, flush, g):
     # CSR SpMV, power-law rows
     nr = 1 << (20 if args.quick else 22)
     A = synthetic.zipf_csr(nr, nr, mean_nnz=32, cap=4096, seed=1234)
@@ -117,6 +135,8 @@ def main():
     report(f"spmv[{nr}x{nr}, nnz={nnz}]", ms, nnz * 12 + nr * 12 + nr * 4 + nr * 4, {"nnz": nnz})
     del d, x, y
 
+
+def bench_sddmm(lib, stream, flush, g):
     # SDDMM, 8192 x 8192 mask at 1 %, K = 64
     N, K = 8192, 64
     C = synthetic.uniform_csr(N, N, 0.01, seed=1234)
@@ -132,6 +152,8 @@ def main():
         nbytes = 4 * (Am.numel() + Bm.numel()) + C["nnz"] * (8 + 8 + 4 + 4) + 8 * (N + 1)
         report(f"sddmm_csr[{N}x{N} 1%, K={K}, alpha={alpha}, beta={beta}]", ms, nbytes, {"nnz": C["nnz"]})
 
+
+def bench_forward5(flush):
     # 5-mer forward: 100 sequences of 2000 steps (latency-bound configuration)
     hmm = synthetic.hmm_model(5)
     seqs = synthetic.hmm_sequences(100, 2000, 2000)
@@ -140,6 +162,8 @@ def main():
     report("hmm_forward_5mer[B=100,T=2000]", ms, synthetic.forward_algorithmic_bytes(hmm, seqs),
            {"state_steps_per_s": synthetic.state_steps(hmm, seqs) / statistics.median(ms) * 1e3})
 
+
+def bench_viterbi(args, flush):
     # windowed Viterbi decoding (windows of 1024 steps, overlap 128), 5-mer and 7-mer models
     for k, nseq, lo, hi in ((5, 100, 2000, 2000), (7, 66, 1000, 4000)):
         hmm = synthetic.hmm_model(k)

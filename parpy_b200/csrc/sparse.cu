@@ -131,81 +131,121 @@ __global__ void sddmm_decompress(const int64_t *__restrict__ crows, int64_t *__r
     for (long long i = a + lane; i < b; i += 32) rows[i] = row;
 }
 
-// Bt[c, k] = B[k, c]
-__global__ void transpose_b(const float *__restrict__ B, float *__restrict__ Bt, long long K, long long ncols) {
-    __shared__ float tile[32][33];
-    const long long c0 = (long long)blockIdx.x * 32, k0 = (long long)blockIdx.y * 32;
-    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
-        const long long k = k0 + j, c = c0 + threadIdx.x;
-        if (k < K && c < ncols) tile[j][threadIdx.x] = B[k * ncols + c];
-    }
-    __syncthreads();
-    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
-        const long long c = c0 + j, k = k0 + threadIdx.x;
-        if (k < K && c < ncols) Bt[c * K + k] = tile[threadIdx.x][j];
+// One launch for both passes that precede the dot products: the first `tblocks` CTAs
+// transpose a 32 x 32 tile of B each, the others expand 8 CSR rows each into per-non-zero
+// row indices (crows == nullptr: rows are given, nothing to expand).
+__global__ void __launch_bounds__(256) sddmm_prepare(const float *__restrict__ B, float *__restrict__ Bt,
+                                                     long long K, long long ncols, unsigned tiles_x,
+                                                     unsigned tblocks, const int64_t *__restrict__ crows,
+                                                     int64_t *__restrict__ rows, long long N) {
+    if (blockIdx.x < tblocks) {
+        __shared__ float tile[32][33];
+        const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+        const long long c0 = (long long)(blockIdx.x % tiles_x) * 32, k0 = (long long)(blockIdx.x / tiles_x) * 32;
+        for (int j = ty; j < 32; j += 8) {
+            const long long k = k0 + j, c = c0 + tx;
+            if (k < K && c < ncols) tile[j][tx] = B[k * ncols + c];
+        }
+        __syncthreads();
+        for (int j = ty; j < 32; j += 8) {
+            const long long c = c0 + j, k = k0 + tx;
+            if (k < K && c < ncols) Bt[c * K + k] = tile[tx][j];
+        }
+    } else {
+        const int lane = threadIdx.x & 31;
+        const long long row = (long long)(blockIdx.x - tblocks) * 8 + (threadIdx.x >> 5);
+        if (row >= N) return;
+        const long long a = __ldg(crows + row), b = __ldg(crows + row + 1);
+        for (long long i = a + lane; i < b; i += 32) rows[i] = row;
     }
 }
 
-// Half a warp per group of kSddmmUnroll consecutive non-zeros: all index loads,
-// then all operand loads, then the math, so that several L2 round trips overlap.
-// VEC: 128-bit loads (K % 4 == 0, 16-byte aligned rows).
-constexpr int kSddmmUnroll = 4;
-
-template <bool VEC>
+// A warp takes W = (32 / LPN) * U consecutive non-zeros per trip: lane l loads row and column
+// index l (one coalesced request each, the next trip's while this trip's operands travel),
+// groups of LPN lanes then work on U non-zeros each, every lane holding K / LPN elements of the
+// two operand rows, H 128-bit pieces per operand and non-zero in flight (all loads of a trip
+// are issued before the math, so their L2 round trips overlap), a log2(LPN)-step shuffle sum
+// per non-zero, and lane l stores non-zero l of the trip (coalesced). The grid is one resident
+// wave. VEC: 128-bit loads (K % 4 == 0, 16-byte aligned rows).
+template <bool VEC, int LPN, int U, int H>
 __global__ void __launch_bounds__(256) sddmm_nnz(const float *__restrict__ A, const float *__restrict__ Bt,
                                                  const int64_t *__restrict__ rows,
                                                  const int64_t *__restrict__ cols,
                                                  const float *__restrict__ cvalues, float *__restrict__ D,
                                                  long long nnz, int K, float alpha, float beta) {
-    // Both halves of a warp run the same number of iterations (the shuffles
-    // below name all 32 lanes); a half without work idles through them.
-    const int sub = threadIdx.x & 15;
-    const int half = (threadIdx.x >> 4) & 1;
-    const long long warp_first = (((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5) * 2;
-    const long long ngroups = ((long long)gridDim.x * blockDim.x) >> 4;
-    for (long long base = warp_first * kSddmmUnroll; base < nnz; base += ngroups * kSddmmUnroll) {
-        const long long i0 = base + (long long)half * kSddmmUnroll;
-        const float *a[kSddmmUnroll], *b[kSddmmUnroll];
-        float acc[kSddmmUnroll];
+    constexpr int G = 32 / LPN;   // non-zeros a warp works on at once
+    constexpr int W = G * U;      // non-zeros per warp and trip
+    static_assert(W <= 32, "one index per lane");
+    const int lane = threadIdx.x & 31;
+    const int sub = lane % LPN, grp = lane / LPN;
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    auto load_index = [&](long long base, long long &r, long long &c) {
+        r = 0;
+        c = 0;
+        if (lane < W && base < nnz) {
+            const long long i = base + lane < nnz ? base + lane : nnz - 1;   // clamp: harmless duplicate work
+            r = __ldg(rows + i);
+            c = __ldg(cols + i);
+        }
+    };
+    long long my_row, my_col;
+    load_index(warp * W, my_row, my_col);
+    // the trip count depends on the warp only, so the full-mask shuffles below are safe
+    for (long long base = warp * W; base < nnz; base += nwarps * W) {
+        long long next_row, next_col;
+        load_index(base + nwarps * W, next_row, next_col);
+        const float *a[U], *b[U];
+        float acc[U];
 #pragma unroll
-        for (int u = 0; u < kSddmmUnroll; ++u) {
-            const long long i = i0 + u < nnz ? i0 + u : nnz - 1;   // clamp: harmless duplicate work
-            a[u] = A + __ldg(rows + i) * K;
-            b[u] = Bt + __ldg(cols + i) * K;
+        for (int u = 0; u < U; ++u) {
+            const int src = u * G + grp;
+            a[u] = A + __shfl_sync(0xffffffffu, my_row, src) * K;
+            b[u] = Bt + __shfl_sync(0xffffffffu, my_col, src) * K;
             acc[u] = 0.0f;
         }
         if (VEC) {
-            for (int k = 4 * sub; k < K; k += 64) {
-                float4 p[kSddmmUnroll], q[kSddmmUnroll];
+            for (int k = 4 * sub; k < K; k += 4 * LPN * H) {
+                float4 p[U][H], q[U][H];
 #pragma unroll
-                for (int u = 0; u < kSddmmUnroll; ++u) {
-                    p[u] = __ldg(reinterpret_cast<const float4 *>(a[u] + k));
-                    q[u] = __ldg(reinterpret_cast<const float4 *>(b[u] + k));
+                for (int u = 0; u < U; ++u) {
+#pragma unroll
+                    for (int h = 0; h < H; ++h) {
+                        const int kk = k + 4 * LPN * h;
+                        const bool in = h == 0 || kk < K;
+                        q[u][h] = in ? __ldg(reinterpret_cast<const float4 *>(b[u] + kk)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        p[u][h] = in ? __ldg(reinterpret_cast<const float4 *>(a[u] + kk)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
                 }
 #pragma unroll
-                for (int u = 0; u < kSddmmUnroll; ++u) {
-                    acc[u] = fmaf(p[u].x, q[u].x, acc[u]);
-                    acc[u] = fmaf(p[u].y, q[u].y, acc[u]);
-                    acc[u] = fmaf(p[u].z, q[u].z, acc[u]);
-                    acc[u] = fmaf(p[u].w, q[u].w, acc[u]);
+                for (int u = 0; u < U; ++u) {
+#pragma unroll
+                    for (int h = 0; h < H; ++h) {
+                        acc[u] = fmaf(p[u][h].x, q[u][h].x, acc[u]);
+                        acc[u] = fmaf(p[u][h].y, q[u][h].y, acc[u]);
+                        acc[u] = fmaf(p[u][h].z, q[u][h].z, acc[u]);
+                        acc[u] = fmaf(p[u][h].w, q[u][h].w, acc[u]);
+                    }
                 }
             }
         } else {
-            for (int k = sub; k < K; k += 16) {
+            for (int k = sub; k < K; k += LPN) {
 #pragma unroll
-                for (int u = 0; u < kSddmmUnroll; ++u) acc[u] = fmaf(__ldg(a[u] + k), __ldg(b[u] + k), acc[u]);
+                for (int u = 0; u < U; ++u) acc[u] = fmaf(__ldg(a[u] + k), __ldg(b[u] + k), acc[u]);
             }
         }
+        float mine = 0.0f;
 #pragma unroll
-        for (int u = 0; u < kSddmmUnroll; ++u) {
+        for (int u = 0; u < U; ++u) {
 #pragma unroll
-            for (int o = 8; o > 0; o >>= 1) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], o, 16);
+            for (int o = LPN / 2; o > 0; o >>= 1) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], o);
+            // non-zero u * G + g of the trip sits in group g: hand it to lane u * G + g
+            const float v = __shfl_sync(0xffffffffu, acc[u], (lane % G) * LPN);
+            if (lane / G == u) mine = v;
         }
-        // lane u of the half stores non-zero i0 + u
-#pragma unroll
-        for (int u = 0; u < kSddmmUnroll; ++u) {
-            if (sub == u && i0 + u < nnz) D[i0 + u] = alpha * acc[u] + beta * __ldg(cvalues + i0 + u);
-        }
+        if (lane < W && base + lane < nnz) D[base + lane] = alpha * mine + beta * __ldg(cvalues + base + lane);
+        my_row = next_row;
+        my_col = next_col;
     }
 }
 
@@ -248,9 +288,9 @@ __global__ void __launch_bounds__(128) spmm_rows(const float *__restrict__ value
     }
 }
 
-int32_t sddmm_common(const float *A, const float *B, const int64_t *rows, const int64_t *cols,
-                     const float *cvalues, float *D, int64_t K, int64_t ncols, int64_t nnz,
-                     double alpha, double beta, cudaStream_t stream) {
+int32_t sddmm_common(const float *A, const float *B, const int64_t *crows, int64_t N, const int64_t *rows,
+                     const int64_t *cols, const float *cvalues, float *D, int64_t K, int64_t ncols,
+                     int64_t nnz, double alpha, double beta, cudaStream_t stream) {
     PB_REQUIRE(K >= 1 && K <= 0x7fffffffLL && ncols >= 1, "sddmm: bad inner size K=%lld or ncols=%lld",
                (long long)K, (long long)ncols);
     if (nnz == 0) return PB_OK;
@@ -262,16 +302,31 @@ int32_t sddmm_common(const float *A, const float *B, const int64_t *rows, const 
     rc = pb::workspace((size_t)K * (size_t)ncols * sizeof(float), &ws, stream, 2);
     if (rc) return rc;
     float *Bt = static_cast<float *>(ws);
-    dim3 tgrid((unsigned)((ncols + 31) / 32), (unsigned)((K + 31) / 32), 1);
-    PB_REQUIRE(tgrid.y <= 65535, "sddmm: K=%lld too large", (long long)K);
-    transpose_b<<<tgrid, dim3(32, 8, 1), 0, stream>>>(B, Bt, K, ncols);
+    const long long tiles_x = (ncols + 31) / 32, tiles = tiles_x * ((K + 31) / 32);
+    const long long expand = crows ? (N + 7) / 8 : 0;
+    PB_REQUIRE(tiles + expand <= 0x7fffffffLL, "sddmm: K=%lld x ncols=%lld too large", (long long)K, (long long)ncols);
+    sddmm_prepare<<<(unsigned)(tiles + expand), 256, 0, stream>>>(B, Bt, K, ncols, (unsigned)tiles_x, (unsigned)tiles,
+                                                                 crows, const_cast<int64_t *>(rows), N);
     PB_CUDA(cudaGetLastError());
-    const long long nnz_per_block = (256 / 16) * kSddmmUnroll;
-    long long blocks = std::min<long long>((nnz + nnz_per_block - 1) / nnz_per_block, 16LL * dev.sm_count);
-    blocks = std::max<long long>(blocks, 1);
     const bool vec = (K % 4 == 0) && pb::aligned16(A) && pb::aligned16(Bt);
-    if (vec) sddmm_nnz<true><<<(unsigned)blocks, 256, 0, stream>>>(A, Bt, rows, cols, cvalues, D, nnz, (int)K, (float)alpha, (float)beta);
-    else sddmm_nnz<false><<<(unsigned)blocks, 256, 0, stream>>>(A, Bt, rows, cols, cvalues, D, nnz, (int)K, (float)alpha, (float)beta);
+    static const int cfg_env = [] { const char *e = getenv("PARPY_B200_SDDMM_CFG"); return e ? atoi(e) : -1; }();
+    const int cfg = cfg_env >= 0 ? cfg_env : 0;
+#define PB_SDDMM(V, L, U, H)                                                                                  \
+    do {                                                                                                      \
+        int per_sm = 0;                                                                                       \
+        PB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, sddmm_nnz<V, L, U, H>, 256, 0));       \
+        const long long per_block = (256 / 32) * (32 / L) * U;                                                \
+        const long long blocks = std::max<long long>(                                                         \
+            1, std::min<long long>((nnz + per_block - 1) / per_block, (long long)std::max(per_sm, 1) * dev.sm_count)); \
+        sddmm_nnz<V, L, U, H><<<(unsigned)blocks, 256, 0, stream>>>(A, Bt, rows, cols, cvalues, D, nnz,       \
+                                                                    (int)K, (float)alpha, (float)beta);       \
+    } while (0)
+    // measured at 8192 x 8192, 1 %, K = 64: <4,2,2> 38.9 us for the whole call, <8,4,2> 40.0,
+    // <8,8,1> 46, <16,8,1> 73 (the old half-warp-per-non-zero kernel: 64)
+    if (!vec) PB_SDDMM(false, 8, 4, 1);
+    else if (cfg == 1) PB_SDDMM(true, 8, 4, 2);
+    else PB_SDDMM(true, 4, 2, 2);
+#undef PB_SDDMM
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }
@@ -362,7 +417,7 @@ int32_t parpy_b200_sddmm_coo(const float *A, const float *B, const int64_t *rows
                              const float *cvalues, float *D, int64_t K, int64_t ncols, int64_t nnz,
                              double alpha, double beta, void *stream_) {
     PB_REQUIRE(nnz >= 0, "sddmm: negative nnz");
-    return sddmm_common(A, B, rows, cols, cvalues, D, K, ncols, nnz, alpha, beta,
+    return sddmm_common(A, B, nullptr, 0, rows, cols, cvalues, D, K, ncols, nnz, alpha, beta,
                         static_cast<cudaStream_t>(stream_));
 }
 
@@ -370,9 +425,9 @@ int32_t parpy_b200_sddmm_csr(const float *A, const float *B, const int64_t *crow
                              const int64_t *cols, const float *cvalues, float *D, int64_t N, int64_t K,
                              int64_t ncols, int64_t nnz, double alpha, double beta, void *stream_) {
     PB_REQUIRE(nnz >= 0 && N >= 0, "sddmm: negative size");
-    int32_t rc = parpy_b200_sddmm_decompress_csr(crows, rows_out, N, stream_);
-    if (rc) return rc;
-    return sddmm_common(A, B, rows_out, cols, cvalues, D, K, ncols, nnz, alpha, beta,
+    if (nnz == 0) return parpy_b200_sddmm_decompress_csr(crows, rows_out, N, stream_);
+    PB_REQUIRE(N == 0 || (crows && rows_out), "sddmm: null pointer");
+    return sddmm_common(A, B, N > 0 ? crows : nullptr, N, rows_out, cols, cvalues, D, K, ncols, nnz, alpha, beta,
                         static_cast<cudaStream_t>(stream_));
 }
 
