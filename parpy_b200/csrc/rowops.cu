@@ -230,10 +230,18 @@ int32_t launch_rowmap(const float *x, float *out, float *rowsum, int64_t N, int6
         const int nvec = (int)(M / 4);
         const int threads = nvec <= 2048 ? 256 : nvec <= 4096 ? 512 : 1024;
         const int per = (nvec + threads - 1) / threads;
-        const long long g = std::min<long long>(N, (long long)dev.sm_count * (2048 / threads) * 2);
-        if (per <= 2) rowmap_block_regs<MODE, 2><<<(unsigned)g, threads, 0, stream>>>(x, out, rowsum, N, (int)M);
-        else if (per <= 4) rowmap_block_regs<MODE, 4><<<(unsigned)g, threads, 0, stream>>>(x, out, rowsum, N, (int)M);
-        else rowmap_block_regs<MODE, 8><<<(unsigned)g, threads, 0, stream>>>(x, out, rowsum, N, (int)M);
+        // one resident wave: CTA b takes rows b, b + grid, ..., so the rows in flight are neighbours
+#define PB_ROWMAP_REGS(V)                                                                                   \
+    do {                                                                                                    \
+        int per_sm = 0;                                                                                     \
+        PB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, rowmap_block_regs<MODE, V>, threads, 0)); \
+        const long long g = std::min<long long>(N, (long long)dev.sm_count * std::max(per_sm, 1));          \
+        rowmap_block_regs<MODE, V><<<(unsigned)g, threads, 0, stream>>>(x, out, rowsum, N, (int)M);         \
+    } while (0)
+        if (per <= 2) PB_ROWMAP_REGS(2);
+        else if (per <= 4) PB_ROWMAP_REGS(4);
+        else PB_ROWMAP_REGS(8);
+#undef PB_ROWMAP_REGS
         PB_CUDA(cudaGetLastError());
         return PB_OK;
     }
