@@ -611,6 +611,283 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_split(const FwdParams p) 
 }
 
 
+// ---- resident kernel, register/shared split, packed arithmetic ---------------------
+// hmm_forward_split with two changes that cut issue slots per state-step:
+//  * all log-probabilities are kept in base-2 units (tables are multiplied by log2(e) when
+//    they are loaded, the result by ln 2 when it is stored), so ex2 / lg2 take their
+//    operands directly and the two scale multiplications per log-sum-exp disappear;
+//  * the additions and multiply-adds run as packed pairs (add/sub/fma .f32x2: one issue
+//    slot for the same operation on two k-mers of the thread, each half rounded exactly
+//    like the scalar instruction).
+// The freed issue slots let more layers take the polynomial exponential (POLY_MASK), which
+// in turn unloads the MUFU pipe.
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 sub2(float2 a, float2 b) {
+    float2 r;
+    asm("{\n\t.reg .b64 ra, rb, rr;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "sub.rn.f32x2 rr, ra, rb;\n\tmov.b64 {%0, %1}, rr;\n\t}"
+        : "=f"(r.x), "=f"(r.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return r;
+}
+__device__ __forceinline__ float2 dup2(float x) { return make_float2(x, x); }
+__device__ __forceinline__ float2 max2(float2 a, float2 b) { return make_float2(fmaxf(a.x, b.x), fmaxf(a.y, b.y)); }
+
+// 2^-|d| for both halves on the FMA pipe; same split and polynomial as ex2_poly.
+__device__ __forceinline__ float2 ex2_poly2_negabs(float2 d) {
+    const float2 t = make_float2(fmaxf(-fabsf(d.x), -126.0f), fmaxf(-fabsf(d.y), -126.0f));  // NaN -> -126
+    const float2 magic = dup2(12582912.0f);
+    const float2 r = add2(t, magic);
+    const float2 n = sub2(r, magic);
+    const float2 f = sub2(t, n);
+    float2 p = dup2(0.001327647129073739f);
+    p = fma2(p, f, dup2(0.009675540961325169f));
+    p = fma2(p, f, dup2(0.05550713092088699f));
+    p = fma2(p, f, dup2(0.24022120237350464f));
+    p = fma2(p, f, dup2(0.6931469440460205f));
+    p = fma2(p, f, dup2(1.0000001192092896f));
+    return make_float2(__int_as_float(__float_as_int(p.x) + (__float_as_int(r.x) << 23)),
+                       __int_as_float(__float_as_int(p.y) + (__float_as_int(r.y) << 23)));
+}
+
+// log2(2^u + 2^v) for two states; (-inf, -inf) gives -inf.
+__device__ __forceinline__ float2 lse2_pair(bool poly, float2 u, float2 v) {
+    const float2 mx = max2(u, v);
+    const float2 d = sub2(u, v);
+    float2 ex;
+    if (poly) ex = ex2_poly2_negabs(d);
+    else ex = make_float2(pb::ex2_approx(-fabsf(d.x)), pb::ex2_approx(-fabsf(d.y)));
+    const float2 s = add2(ex, dup2(1.0f));
+    const float2 l = make_float2(pb::lg2_approx(s.x), pb::lg2_approx(s.y));
+    const float2 r = add2(mx, l);
+    // the polynomial path maps the NaN of (-inf) - (-inf) to a zero term by itself
+    return poly ? r : make_float2(fmaxf(r.x, -INFINITY), fmaxf(r.y, -INFINITY));
+}
+
+// log2 of the sum of four powers of two, terms added in the order j = 0..3.
+__device__ __forceinline__ float2 lse4_pair(float2 p0, float2 p1, float2 p2, float2 p3) {
+    const float2 m = max2(max2(p0, p1), max2(p2, p3));
+    const float2 d0 = sub2(p0, m), d1 = sub2(p1, m), d2 = sub2(p2, m), d3 = sub2(p3, m);
+    float2 sum = add2(make_float2(pb::ex2_approx(d0.x), pb::ex2_approx(d0.y)),
+                      make_float2(pb::ex2_approx(d1.x), pb::ex2_approx(d1.y)));
+    sum = add2(sum, make_float2(pb::ex2_approx(d2.x), pb::ex2_approx(d2.y)));
+    sum = add2(sum, make_float2(pb::ex2_approx(d3.x), pb::ex2_approx(d3.y)));
+    const float2 r = add2(m, make_float2(pb::lg2_approx(sum.x), pb::lg2_approx(sum.y)));
+    return make_float2(fmaxf(r.x, -INFINITY), fmaxf(r.y, -INFINITY));
+}
+
+template <unsigned POLY_MASK>   // bit d set: layer d evaluates its exponential on the FMA pipe
+__global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p) {
+    extern __shared__ __align__(16) float smem_dyn[];
+    __shared__ int s_seq;
+    __shared__ float s_warp[32];
+    __shared__ float s_cl[16];
+    __shared__ float2 s_t2[kLayers];   // (trans2[d], trans2[d]) in base-2 units
+
+    const int tid = threadIdx.x;
+    const int NT = blockDim.x;
+    const unsigned rank = cluster_ctarank();
+    const unsigned CS = cluster_nctarank();
+    const int K = p.K;
+    const int Kq = K >> 2;
+    const int M = NT;                         // predecessor groups per CTA (4 k-mers per thread)
+    const int g = (rank * NT + tid) * 4;      // first global k-mer
+    const int lane = tid & 31, warp = tid >> 5, nwarps = (NT + 31) >> 5;
+    const float2 l2e = dup2(kLog2e);
+
+    float *a0s = smem_dyn;                                             // [2][4][M]
+    float4 *Ts = reinterpret_cast<float4 *>(smem_dyn + 8 * M);         // [4][NT] transition columns
+    float4 *As = Ts + 4 * NT;                                          // [8][NT] layers 8..15
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float4 v = __ldg(reinterpret_cast<const float4 *>(p.trans1) + (j * Kq + (g >> 2)));
+        v.x *= kLog2e; v.y *= kLog2e; v.z *= kLog2e; v.w *= kLog2e;
+        Ts[j * NT + tid] = v;
+    }
+    if (tid < kLayers) s_t2[tid] = dup2(c_model[p.slot].trans2[tid] * kLog2e);
+    const float gamma2 = p.gamma * kLog2e, syn2 = p.synthetic * kLog2e;
+
+    const unsigned a0_base = smem_u32(a0s);
+    unsigned dst0;
+    {
+        const int dj = g / Kq, rem = g % Kq;
+        const int dr = rem / M, di = rem % M;
+        dst0 = map_to_rank(a0_base + 4u * (dj * M + di), dr);
+    }
+    const unsigned buf_bytes = 16u * M;
+    const unsigned seq_addr = smem_u32(&s_seq);
+    const unsigned cl_addr = smem_u32(s_cl);
+    __syncthreads();
+
+    for (;;) {
+        if (rank == 0 && tid == 0) {
+            const int i = atomicAdd(p.counter, 1);
+            const int seq = i < p.B ? p.order[i] : -1;
+            for (unsigned r = 0; r < CS; ++r) st_cluster_s32(map_to_rank(seq_addr, r), seq);
+        }
+        cluster_arrive();
+        cluster_wait();
+        const int seq = s_seq;
+        if (seq < 0) break;
+
+        long long len = p.lens[seq];
+        if (len < 1 || len > p.maxlen) {
+            if (tid == 0 && rank == 0) atomicOr(&g_status, 1u);
+            len = len < 1 ? 1 : p.maxlen;
+        }
+        const uint8_t *obs = p.data + static_cast<long long>(seq) * p.maxlen;
+        const int T_len = static_cast<int>(len);
+
+        // t = 0
+        float2 a[kRegLayers][2];
+        float4 e;
+        int o_next;
+        {
+            const int o0 = obs[0];
+            o_next = obs[T_len > 1 ? 1 : 0];
+            e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o0 * K + g));
+#pragma unroll
+            for (int d = 0; d < kLayers; ++d) {
+                const float4 v = __ldg(reinterpret_cast<const float4 *>(p.initial_prob + d * K + g));
+                // the reference's sum first, then the change of units
+                const float2 lo = mul2(make_float2(v.x + e.x, v.y + e.y), l2e);
+                const float2 hi = mul2(make_float2(v.z + e.z, v.w + e.w), l2e);
+                if (d < kRegLayers) { a[d][0] = lo; a[d][1] = hi; }
+                else As[(d - kRegLayers) * NT + tid] = make_float4(lo.x, lo.y, hi.x, hi.y);
+            }
+        }
+        unsigned buf = 0;
+        st_cluster_v4(dst0, a[0][0].x, a[0][0].y, a[0][1].x, a[0][1].y);
+        cluster_arrive();
+
+        for (int t = 1; t < T_len; ++t) {
+            // this step's emission slice; the observation after it
+            e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o_next * K + g));
+            o_next = obs[t + 1 < T_len ? t + 1 : T_len - 1];
+            const float2 ev[2] = {mul2(make_float2(e.x, e.y), l2e), mul2(make_float2(e.z, e.w), l2e)};
+
+            cluster_wait();
+            const float *seg = a0s + (buf ? 4 * M : 0) + tid;
+            const float2 a0 = dup2(seg[0]), a1 = dup2(seg[M]), a2 = dup2(seg[2 * M]), a3 = dup2(seg[3 * M]);
+            const unsigned dst = dst0 + (buf ? 0u : buf_bytes);
+
+            float2 q[2];
+            {
+                const float4 t0 = Ts[tid], t1 = Ts[NT + tid], t2 = Ts[2 * NT + tid], t3 = Ts[3 * NT + tid];
+                q[0] = lse4_pair(add2(make_float2(t0.x, t0.y), a0), add2(make_float2(t1.x, t1.y), a1),
+                                 add2(make_float2(t2.x, t2.y), a2), add2(make_float2(t3.x, t3.y), a3));
+                q[1] = lse4_pair(add2(make_float2(t0.z, t0.w), a0), add2(make_float2(t1.z, t1.w), a1),
+                                 add2(make_float2(t2.z, t2.w), a2), add2(make_float2(t3.z, t3.w), a3));
+            }
+            {
+                const float2 w = s_t2[0];
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    a[0][h] = add2(lse2_pair((POLY_MASK & 1u) != 0, add2(w, q[h]), a[1][h]), ev[h]);
+            }
+            st_cluster_v4(dst, a[0][0].x, a[0][0].y, a[0][1].x, a[0][1].y);
+            cluster_arrive();
+#pragma unroll
+            for (int d = 1; d < kRegLayers - 1; ++d) {
+                const float2 w = s_t2[d];
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    a[d][h] = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[h]), a[d + 1][h]), ev[h]);
+            }
+            // layers 7..15: the "next layer" operand comes from shared memory
+            float4 nxt = As[tid];  // layer 8 (old)
+            {
+                const float2 w = s_t2[kRegLayers - 1];
+                a[kRegLayers - 1][0] = add2(lse2_pair(((POLY_MASK >> (kRegLayers - 1)) & 1u) != 0, add2(w, q[0]),
+                                                      make_float2(nxt.x, nxt.y)), ev[0]);
+                a[kRegLayers - 1][1] = add2(lse2_pair(((POLY_MASK >> (kRegLayers - 1)) & 1u) != 0, add2(w, q[1]),
+                                                      make_float2(nxt.z, nxt.w)), ev[1]);
+            }
+#pragma unroll
+            for (int d = kRegLayers; d < kLayers; ++d) {
+                // old alpha[min(d+1,15)]; layers 14 and 15 both read old layer 15
+                if (d < kLayers - 1) nxt = As[(d + 1 - kRegLayers) * NT + tid];
+                float2 v0 = make_float2(nxt.x, nxt.y), v1 = make_float2(nxt.z, nxt.w);
+                if (d >= 14) {
+                    const float c = d == 15 ? gamma2 : syn2;
+                    v0.x += c; v0.y += c; v1.x += c; v1.y += c;
+                }
+                const float2 w = s_t2[d];
+                const float2 r0 = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[0]), v0), ev[0]);
+                const float2 r1 = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[1]), v1), ev[1]);
+                As[(d - kRegLayers) * NT + tid] = make_float4(r0.x, r0.y, r1.x, r1.y);
+            }
+            buf ^= 1u;
+        }
+        cluster_wait();
+
+        // final log-sum-exp over all states (base-2 units until the last line)
+        float tmax = -INFINITY;
+#pragma unroll
+        for (int d = 0; d < kRegLayers; ++d)
+            tmax = fmaxf(tmax, fmaxf(fmaxf(a[d][0].x, a[d][0].y), fmaxf(a[d][1].x, a[d][1].y)));
+#pragma unroll
+        for (int d = 0; d < kLayers - kRegLayers; ++d) {
+            const float4 v = As[d * NT + tid];
+            tmax = fmaxf(tmax, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
+        }
+        tmax = pb::warp_max(tmax);
+        if (lane == 0) s_warp[warp] = tmax;
+        __syncthreads();
+        if (tid < (int)CS) {
+            float m = -INFINITY;
+            for (int w = 0; w < nwarps; ++w) m = fmaxf(m, s_warp[w]);
+            st_cluster_f32(map_to_rank(cl_addr + 4u * rank, tid), m);
+        }
+        cluster_arrive();
+        cluster_wait();
+        float gmax = -INFINITY;
+        for (unsigned r = 0; r < CS; ++r) gmax = fmaxf(gmax, s_cl[r]);
+        float tsum = 0.0f;
+#pragma unroll
+        for (int d = 0; d < kRegLayers; ++d)
+            tsum += pb::ex2_approx(a[d][0].x - gmax) + pb::ex2_approx(a[d][0].y - gmax) +
+                    pb::ex2_approx(a[d][1].x - gmax) + pb::ex2_approx(a[d][1].y - gmax);
+#pragma unroll
+        for (int d = 0; d < kLayers - kRegLayers; ++d) {
+            const float4 v = As[d * NT + tid];
+            tsum += pb::ex2_approx(v.x - gmax) + pb::ex2_approx(v.y - gmax) + pb::ex2_approx(v.z - gmax) +
+                    pb::ex2_approx(v.w - gmax);
+        }
+        tsum = pb::warp_sum(tsum);
+        cluster_arrive();
+        cluster_wait();
+        if (lane == 0) s_warp[warp] = tsum;
+        __syncthreads();
+        if (tid < (int)CS) {
+            float sacc = 0.0f;
+            for (int w = 0; w < nwarps; ++w) sacc += s_warp[w];
+            st_cluster_f32(map_to_rank(cl_addr + 4u * rank, tid), sacc);
+        }
+        cluster_arrive();
+        cluster_wait();
+        if (rank == 0 && tid == 0) {
+            float sacc = 0.0f;
+            for (unsigned r = 0; r < CS; ++r) sacc += s_cl[r];
+            p.result[seq] = (gmax + pb::lg2_approx(sacc)) * kLn2;
+        }
+        if (p.write_alpha) {
+            float *dst_alpha = ((len & 1) ? p.alpha1 : p.alpha2) + (long long)seq * (kLayers * (long long)K);
+#pragma unroll
+            for (int d = 0; d < kLayers; ++d) {
+                float4 v = d < kRegLayers ? make_float4(a[d % kRegLayers][0].x, a[d % kRegLayers][0].y,
+                                                        a[d % kRegLayers][1].x, a[d % kRegLayers][1].y)
+                                          : As[(d - kRegLayers) * NT + tid];
+                v.x *= kLn2; v.y *= kLn2; v.z *= kLn2; v.w *= kLn2;
+                *reinterpret_cast<float4 *>(dst_alpha + (long long)d * K + g) = v;
+            }
+        }
+    }
+}
+
+
 // ---- scaled (extended-range linear) kernel ------------------------------------------
 // The same recurrence evaluated on probabilities instead of log-probabilities:
 //   alpha'[d,s] = (A[d] * Q[s] + C[d] * alpha[d+1,s]) * E[s],   Q[s] = sum_j T[j,s] * alpha[0,p_j]
@@ -983,6 +1260,21 @@ ResidentKernel pick_kernel(const Plan &pl, bool five) {
         // how many of the 16 layers take the polynomial exponential
         int npoly = 5;
         if (const char *env = getenv("PARPY_B200_FWD_POLY")) npoly = atoi(env);
+        int packed = 1;
+        if (const char *env = getenv("PARPY_B200_FWD_PACKED")) packed = atoi(env);
+        if (packed) {
+            // layer 0 stays on the MUFU pipe in every mask: it is on the path to the exchange
+            if (!getenv("PARPY_B200_FWD_POLY")) npoly = 10;
+            switch (npoly) {
+                case 0: return hmm_forward_packed<0x0000u>;
+                case 5: return hmm_forward_packed<0x2492u>;   // layers 1,4,7,10,13
+                case 8: return hmm_forward_packed<0xAAAAu>;   // odd layers
+                case 9: return hmm_forward_packed<0xAD5Au>;   // all but 0,2,5,7,9,12,14
+                case 11: return hmm_forward_packed<0xDB6Eu>;  // all but 0,4,7,10,13
+                case 12: return hmm_forward_packed<0xEEEEu>;  // all but 0,4,8,12
+                default: return hmm_forward_packed<0x6DB6u>;  // 10: all but 0,3,6,9,12,15
+            }
+        }
         switch (npoly) {
             case 0: return hmm_forward_split<0x0000u>;
             case 4: return hmm_forward_split<0x2222u>;   // layers 1,5,9,13

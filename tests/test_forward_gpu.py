@@ -151,16 +151,19 @@ def test_other_state_spaces_against_oracle(native, oracle_mod, k):
 
 
 def test_kernel_layout_variants_agree_with_oracle(native, oracle_mod, monkeypatch):
-    # 7mer: register/shared split layout with 0..8 layers on the polynomial exponential, and
-    # the all-register 8-CTA layout; every variant against the CPU oracle on the same inputs.
+    # 7mer: the packed base-2 split kernel (default) and the scalar natural-log split kernel, each
+    # with several sets of layers on the polynomial exponential, and the all-register 8-CTA layout;
+    # every variant against the CPU oracle on the same inputs.
     from parpy_b200 import synthetic
     hmm = synthetic.hmm_model(7, seed=5)
     seqs = synthetic.hmm_sequences(6, 2, 90, seed=6)
     exp, exp_alpha = oracle_mod.forward(hmm, seqs, want_alpha=True)
     dh, ds = to_dev(hmm), to_dev(seqs)
-    settings = [{"PARPY_B200_FWD_SPLIT": "0"}] + [{"PARPY_B200_FWD_POLY": str(n)} for n in (0, 4, 5, 6, 8)]
+    settings = ([{"PARPY_B200_FWD_SPLIT": "0"}]
+                + [{"PARPY_B200_FWD_PACKED": "0", "PARPY_B200_FWD_POLY": str(n)} for n in (0, 4, 5, 6, 8)]
+                + [{"PARPY_B200_FWD_POLY": str(n)} for n in (0, 5, 8, 9, 10, 11, 12)])
     for env in settings:
-        for k in ("PARPY_B200_FWD_SPLIT", "PARPY_B200_FWD_POLY"):
+        for k in ("PARPY_B200_FWD_SPLIT", "PARPY_B200_FWD_POLY", "PARPY_B200_FWD_PACKED"):
             monkeypatch.delenv(k, raising=False)
         for k, v in env.items():
             monkeypatch.setenv(k, v)
