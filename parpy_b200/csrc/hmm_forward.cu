@@ -612,15 +612,15 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_split(const FwdParams p) 
 
 
 // ---- resident kernel, register/shared split, packed arithmetic ---------------------
-// hmm_forward_split with two changes that cut issue slots per state-step:
-//  * all log-probabilities are kept in base-2 units (tables are multiplied by log2(e) when
-//    they are loaded, the result by ln 2 when it is stored), so ex2 / lg2 take their
-//    operands directly and the two scale multiplications per log-sum-exp disappear;
-//  * the additions and multiply-adds run as packed pairs (add/sub/fma .f32x2: one issue
-//    slot for the same operation on two k-mers of the thread, each half rounded exactly
-//    like the scalar instruction).
-// The freed issue slots let more layers take the polynomial exponential (POLY_MASK), which
-// in turn unloads the MUFU pipe.
+// hmm_forward_split with its additions, multiplications and multiply-adds issued as packed
+// pairs (add/sub/mul/fma .f32x2: one issue slot for the same operation on two k-mers of the
+// thread, each half rounded exactly like the scalar instruction, so the results are those
+// of hmm_forward_split with the same POLY_MASK, bit for bit). The freed issue slots let
+// more layers take the polynomial exponential, which in turn unloads the MUFU pipe.
+// Values stay in natural-log units like the reference's: keeping them in base-2 units
+// would save one multiplication per log-sum-exp, but then alpha is rounded on a different
+// grid at every step and the result drifts away from the reference's own fp32 rounding
+// (2e-5 relative on the 5-mer golden vectors instead of 2e-6).
 __device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
 __device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
@@ -635,9 +635,9 @@ __device__ __forceinline__ float2 sub2(float2 a, float2 b) {
 __device__ __forceinline__ float2 dup2(float x) { return make_float2(x, x); }
 __device__ __forceinline__ float2 max2(float2 a, float2 b) { return make_float2(fmaxf(a.x, b.x), fmaxf(a.y, b.y)); }
 
-// 2^-|d| for both halves on the FMA pipe; same split and polynomial as ex2_poly.
-__device__ __forceinline__ float2 ex2_poly2_negabs(float2 d) {
-    const float2 t = make_float2(fmaxf(-fabsf(d.x), -126.0f), fmaxf(-fabsf(d.y), -126.0f));  // NaN -> -126
+// 2^-|t| for both halves on the FMA pipe; same split and polynomial as ex2_poly.
+__device__ __forceinline__ float2 ex2_poly2_negabs(float2 t2) {
+    const float2 t = make_float2(fmaxf(-fabsf(t2.x), -126.0f), fmaxf(-fabsf(t2.y), -126.0f));  // NaN -> -126
     const float2 magic = dup2(12582912.0f);
     const float2 r = add2(t, magic);
     const float2 n = sub2(r, magic);
@@ -652,29 +652,31 @@ __device__ __forceinline__ float2 ex2_poly2_negabs(float2 d) {
                        __int_as_float(__float_as_int(p.y) + (__float_as_int(r.y) << 23)));
 }
 
-// log2(2^u + 2^v) for two states; (-inf, -inf) gives -inf.
+// log(exp(u) + exp(v)) for two states, every half rounded exactly like lse2_sel;
+// (-inf, -inf) gives -inf.
 __device__ __forceinline__ float2 lse2_pair(bool poly, float2 u, float2 v) {
     const float2 mx = max2(u, v);
-    const float2 d = sub2(u, v);
+    const float2 t = mul2(sub2(u, v), dup2(kLog2e));   // |t| = |u - v| * log2(e)
     float2 ex;
-    if (poly) ex = ex2_poly2_negabs(d);
-    else ex = make_float2(pb::ex2_approx(-fabsf(d.x)), pb::ex2_approx(-fabsf(d.y)));
+    if (poly) ex = ex2_poly2_negabs(t);
+    else ex = make_float2(pb::ex2_approx(-fabsf(t.x)), pb::ex2_approx(-fabsf(t.y)));
     const float2 s = add2(ex, dup2(1.0f));
-    const float2 l = make_float2(pb::lg2_approx(s.x), pb::lg2_approx(s.y));
-    const float2 r = add2(mx, l);
+    const float2 r = fma2(make_float2(pb::lg2_approx(s.x), pb::lg2_approx(s.y)), dup2(kLn2), mx);
     // the polynomial path maps the NaN of (-inf) - (-inf) to a zero term by itself
     return poly ? r : make_float2(fmaxf(r.x, -INFINITY), fmaxf(r.y, -INFINITY));
 }
 
-// log2 of the sum of four powers of two, terms added in the order j = 0..3.
+// log of the sum of four exponentials, terms added in the order j = 0..3 (lse4 on pairs).
 __device__ __forceinline__ float2 lse4_pair(float2 p0, float2 p1, float2 p2, float2 p3) {
     const float2 m = max2(max2(p0, p1), max2(p2, p3));
-    const float2 d0 = sub2(p0, m), d1 = sub2(p1, m), d2 = sub2(p2, m), d3 = sub2(p3, m);
+    const float2 l2e = dup2(kLog2e);
+    const float2 d0 = mul2(sub2(p0, m), l2e), d1 = mul2(sub2(p1, m), l2e);
+    const float2 d2 = mul2(sub2(p2, m), l2e), d3 = mul2(sub2(p3, m), l2e);
     float2 sum = add2(make_float2(pb::ex2_approx(d0.x), pb::ex2_approx(d0.y)),
                       make_float2(pb::ex2_approx(d1.x), pb::ex2_approx(d1.y)));
     sum = add2(sum, make_float2(pb::ex2_approx(d2.x), pb::ex2_approx(d2.y)));
     sum = add2(sum, make_float2(pb::ex2_approx(d3.x), pb::ex2_approx(d3.y)));
-    const float2 r = add2(m, make_float2(pb::lg2_approx(sum.x), pb::lg2_approx(sum.y)));
+    const float2 r = fma2(make_float2(pb::lg2_approx(sum.x), pb::lg2_approx(sum.y)), dup2(kLn2), m);
     return make_float2(fmaxf(r.x, -INFINITY), fmaxf(r.y, -INFINITY));
 }
 
@@ -684,7 +686,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
     __shared__ int s_seq;
     __shared__ float s_warp[32];
     __shared__ float s_cl[16];
-    __shared__ float2 s_t2[kLayers];   // (trans2[d], trans2[d]) in base-2 units
+    __shared__ float2 s_t2[kLayers];   // (trans2[d], trans2[d])
 
     const int tid = threadIdx.x;
     const int NT = blockDim.x;
@@ -695,19 +697,16 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
     const int M = NT;                         // predecessor groups per CTA (4 k-mers per thread)
     const int g = (rank * NT + tid) * 4;      // first global k-mer
     const int lane = tid & 31, warp = tid >> 5, nwarps = (NT + 31) >> 5;
-    const float2 l2e = dup2(kLog2e);
 
     float *a0s = smem_dyn;                                             // [2][4][M]
     float4 *Ts = reinterpret_cast<float4 *>(smem_dyn + 8 * M);         // [4][NT] transition columns
     float4 *As = Ts + 4 * NT;                                          // [8][NT] layers 8..15
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-        float4 v = __ldg(reinterpret_cast<const float4 *>(p.trans1) + (j * Kq + (g >> 2)));
-        v.x *= kLog2e; v.y *= kLog2e; v.z *= kLog2e; v.w *= kLog2e;
-        Ts[j * NT + tid] = v;
+        Ts[j * NT + tid] = __ldg(reinterpret_cast<const float4 *>(p.trans1) + (j * Kq + (g >> 2)));
     }
-    if (tid < kLayers) s_t2[tid] = dup2(c_model[p.slot].trans2[tid] * kLog2e);
-    const float gamma2 = p.gamma * kLog2e, syn2 = p.synthetic * kLog2e;
+    if (tid < kLayers) s_t2[tid] = dup2(c_model[p.slot].trans2[tid]);
+    const float gamma2 = p.gamma, syn2 = p.synthetic;
 
     const unsigned a0_base = smem_u32(a0s);
     unsigned dst0;
@@ -751,9 +750,8 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
 #pragma unroll
             for (int d = 0; d < kLayers; ++d) {
                 const float4 v = __ldg(reinterpret_cast<const float4 *>(p.initial_prob + d * K + g));
-                // the reference's sum first, then the change of units
-                const float2 lo = mul2(make_float2(v.x + e.x, v.y + e.y), l2e);
-                const float2 hi = mul2(make_float2(v.z + e.z, v.w + e.w), l2e);
+                const float2 lo = make_float2(v.x + e.x, v.y + e.y);
+                const float2 hi = make_float2(v.z + e.z, v.w + e.w);
                 if (d < kRegLayers) { a[d][0] = lo; a[d][1] = hi; }
                 else As[(d - kRegLayers) * NT + tid] = make_float4(lo.x, lo.y, hi.x, hi.y);
             }
@@ -766,7 +764,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
             // this step's emission slice; the observation after it
             e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o_next * K + g));
             o_next = obs[t + 1 < T_len ? t + 1 : T_len - 1];
-            const float2 ev[2] = {mul2(make_float2(e.x, e.y), l2e), mul2(make_float2(e.z, e.w), l2e)};
+            const float2 ev[2] = {make_float2(e.x, e.y), make_float2(e.z, e.w)};
 
             cluster_wait();
             const float *seg = a0s + (buf ? 4 * M : 0) + tid;
@@ -823,7 +821,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
         }
         cluster_wait();
 
-        // final log-sum-exp over all states (base-2 units until the last line)
+        // final log-sum-exp over all states
         float tmax = -INFINITY;
 #pragma unroll
         for (int d = 0; d < kRegLayers; ++d)
@@ -848,13 +846,12 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
         float tsum = 0.0f;
 #pragma unroll
         for (int d = 0; d < kRegLayers; ++d)
-            tsum += pb::ex2_approx(a[d][0].x - gmax) + pb::ex2_approx(a[d][0].y - gmax) +
-                    pb::ex2_approx(a[d][1].x - gmax) + pb::ex2_approx(a[d][1].y - gmax);
+            tsum += fast_exp(a[d][0].x - gmax) + fast_exp(a[d][0].y - gmax) +
+                    fast_exp(a[d][1].x - gmax) + fast_exp(a[d][1].y - gmax);
 #pragma unroll
         for (int d = 0; d < kLayers - kRegLayers; ++d) {
             const float4 v = As[d * NT + tid];
-            tsum += pb::ex2_approx(v.x - gmax) + pb::ex2_approx(v.y - gmax) + pb::ex2_approx(v.z - gmax) +
-                    pb::ex2_approx(v.w - gmax);
+            tsum += fast_exp(v.x - gmax) + fast_exp(v.y - gmax) + fast_exp(v.z - gmax) + fast_exp(v.w - gmax);
         }
         tsum = pb::warp_sum(tsum);
         cluster_arrive();
@@ -871,18 +868,149 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
         if (rank == 0 && tid == 0) {
             float sacc = 0.0f;
             for (unsigned r = 0; r < CS; ++r) sacc += s_cl[r];
-            p.result[seq] = (gmax + pb::lg2_approx(sacc)) * kLn2;
+            p.result[seq] = gmax + fast_log(sacc);
         }
         if (p.write_alpha) {
             float *dst_alpha = ((len & 1) ? p.alpha1 : p.alpha2) + (long long)seq * (kLayers * (long long)K);
 #pragma unroll
             for (int d = 0; d < kLayers; ++d) {
-                float4 v = d < kRegLayers ? make_float4(a[d % kRegLayers][0].x, a[d % kRegLayers][0].y,
+                const float4 v = d < kRegLayers ? make_float4(a[d % kRegLayers][0].x, a[d % kRegLayers][0].y,
                                                         a[d % kRegLayers][1].x, a[d % kRegLayers][1].y)
                                           : As[(d - kRegLayers) * NT + tid];
-                v.x *= kLn2; v.y *= kLn2; v.z *= kLn2; v.w *= kLn2;
                 *reinterpret_cast<float4 *>(dst_alpha + (long long)d * K + g) = v;
             }
+        }
+    }
+}
+
+
+// ---- one CTA per sequence, packed arithmetic (K <= 1024) -----------------------------
+// The 5-mer state space (16 x 1024) fits the registers of one 256-thread CTA: 4 k-mers x
+// 16 layers per thread, the arithmetic of hmm_forward_packed (packed pairs, polynomial
+// exponential on the layers of POLY_MASK). Layer 0 is exchanged
+// through the CTA's own shared memory, so a time step costs one __syncthreads instead of
+// a cluster barrier, which is what bounds the step time of small state spaces.
+template <unsigned POLY_MASK>
+__global__ void __launch_bounds__(256, 1) hmm_forward_packed_cta(const FwdParams p) {
+    __shared__ __align__(16) float a0s[2][1024];   // layer 0 of all k-mers, double buffered
+    __shared__ int s_seq;
+    __shared__ float s_warp[32];
+    __shared__ float2 s_t2[kLayers];   // (trans2[d], trans2[d])
+
+    const int tid = threadIdx.x;
+    const int NT = blockDim.x;          // K / 4
+    const int K = p.K;
+    const int Kq = K >> 2;
+    const int g = tid * 4;              // first k-mer
+    const int lane = tid & 31, warp = tid >> 5, nwarps = (NT + 31) >> 5;
+
+    float2 T[4][2];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float4 v = __ldg(reinterpret_cast<const float4 *>(p.trans1) + (j * Kq + tid));
+        T[j][0] = make_float2(v.x, v.y);
+        T[j][1] = make_float2(v.z, v.w);
+    }
+    if (tid < kLayers) s_t2[tid] = dup2(c_model[p.slot].trans2[tid]);
+    const float gamma2 = p.gamma, syn2 = p.synthetic;
+
+    for (;;) {
+        __syncthreads();   // s_seq, s_warp and a0s of the previous sequence are no longer read
+        if (tid == 0) {
+            const int i = atomicAdd(p.counter, 1);
+            s_seq = i < p.B ? p.order[i] : -1;
+        }
+        __syncthreads();
+        const int seq = s_seq;
+        if (seq < 0) break;
+
+        long long len = p.lens[seq];
+        if (len < 1 || len > p.maxlen) {
+            if (tid == 0) atomicOr(&g_status, 1u);
+            len = len < 1 ? 1 : p.maxlen;
+        }
+        const uint8_t *obs = p.data + static_cast<long long>(seq) * p.maxlen;
+        const int T_len = static_cast<int>(len);
+
+        float2 a[kLayers][2];
+        float4 e;
+        int o_next;
+        {
+            const int o0 = obs[0];
+            o_next = obs[T_len > 1 ? 1 : 0];
+            e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o0 * K + g));
+#pragma unroll
+            for (int d = 0; d < kLayers; ++d) {
+                const float4 v = __ldg(reinterpret_cast<const float4 *>(p.initial_prob + d * K + g));
+                a[d][0] = make_float2(v.x + e.x, v.y + e.y);
+                a[d][1] = make_float2(v.z + e.z, v.w + e.w);
+            }
+        }
+        unsigned buf = 0;
+        *reinterpret_cast<float4 *>(&a0s[0][g]) = make_float4(a[0][0].x, a[0][0].y, a[0][1].x, a[0][1].y);
+
+        for (int t = 1; t < T_len; ++t) {
+            e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o_next * K + g));
+            o_next = obs[t + 1 < T_len ? t + 1 : T_len - 1];
+            const float2 ev[2] = {make_float2(e.x, e.y), make_float2(e.z, e.w)};
+
+            __syncthreads();   // layer 0 of step t-1 is complete; the other buffer is free
+            const float *seg = a0s[buf] + tid;
+            const float2 a0 = dup2(seg[0]), a1 = dup2(seg[Kq]), a2 = dup2(seg[2 * Kq]), a3 = dup2(seg[3 * Kq]);
+            float2 q[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+                q[h] = lse4_pair(add2(T[0][h], a0), add2(T[1][h], a1), add2(T[2][h], a2), add2(T[3][h], a3));
+#pragma unroll
+            for (int d = 0; d < kLayers; ++d) {
+                const float2 w = s_t2[d];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    float2 v = a[d + 1 < kLayers ? d + 1 : kLayers - 1][h];   // old values: layers ascend in place
+                    if (d >= 14) {
+                        const float c = d == 15 ? gamma2 : syn2;
+                        v.x += c;
+                        v.y += c;
+                    }
+                    a[d][h] = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[h]), v), ev[h]);
+                }
+                if (d == 0)
+                    *reinterpret_cast<float4 *>(&a0s[buf ^ 1u][g]) =
+                        make_float4(a[0][0].x, a[0][0].y, a[0][1].x, a[0][1].y);
+            }
+            buf ^= 1u;
+        }
+
+        // final log-sum-exp over all states
+        float tmax = -INFINITY;
+#pragma unroll
+        for (int d = 0; d < kLayers; ++d)
+            tmax = fmaxf(tmax, fmaxf(fmaxf(a[d][0].x, a[d][0].y), fmaxf(a[d][1].x, a[d][1].y)));
+        tmax = pb::warp_max(tmax);
+        if (lane == 0) s_warp[warp] = tmax;
+        __syncthreads();
+        float gmax = -INFINITY;
+        for (int w = 0; w < nwarps; ++w) gmax = fmaxf(gmax, s_warp[w]);
+        float tsum = 0.0f;
+#pragma unroll
+        for (int d = 0; d < kLayers; ++d)
+            tsum += fast_exp(a[d][0].x - gmax) + fast_exp(a[d][0].y - gmax) +
+                    fast_exp(a[d][1].x - gmax) + fast_exp(a[d][1].y - gmax);
+        tsum = pb::warp_sum(tsum);
+        __syncthreads();   // every thread has read the maxima
+        if (lane == 0) s_warp[warp] = tsum;
+        __syncthreads();
+        if (tid == 0) {
+            float sacc = 0.0f;
+            for (int w = 0; w < nwarps; ++w) sacc += s_warp[w];
+            p.result[seq] = gmax + fast_log(sacc);
+        }
+        if (p.write_alpha) {
+            float *dst_alpha = ((len & 1) ? p.alpha1 : p.alpha2) + (long long)seq * (kLayers * (long long)K);
+#pragma unroll
+            for (int d = 0; d < kLayers; ++d)
+                *reinterpret_cast<float4 *>(dst_alpha + (long long)d * K + g) =
+                    make_float4(a[d][0].x, a[d][0].y, a[d][1].x, a[d][1].y);
         }
     }
 }
@@ -1205,6 +1333,7 @@ struct Plan {
     int kpt = 0, nt = 0, cs = 0;
     bool split = false;  // layers 8..15 in shared memory, 1024 threads per CTA
     bool scaled = false; // extended-range linear arithmetic instead of log space
+    bool cta = false;    // one 256-thread CTA per sequence, packed arithmetic (K = 1024)
 };
 
 // Picks (k-mers per thread, threads per CTA, CTAs per cluster) with
@@ -1244,10 +1373,22 @@ bool make_plan(long long K, Plan *pl, bool allow_split, bool need_kpt4 = false) 
         split = true;
     }
     if (cs > 16) return false;
+    bool cta = false;
+    if (allow_split && K == 1024 && !getenv("PARPY_B200_FWD_KPT") && !getenv("PARPY_B200_FWD_NT")) {
+        int packed = 1;
+        if (const char *env = getenv("PARPY_B200_FWD_PACKED")) packed = atoi(env);
+        if (packed) {
+            kpt = 4;
+            nt = 256;
+            cs = 1;
+            cta = true;
+        }
+    }
     pl->kpt = (int)kpt;
     pl->nt = (int)nt;
     pl->cs = (int)cs;
     pl->split = split;
+    pl->cta = cta;
     return true;
 }
 
@@ -1256,6 +1397,20 @@ using ResidentKernel = void (*)(const FwdParams);
 ResidentKernel pick_kernel(const Plan &pl, bool five) {
     const int kpt = pl.kpt;
     if (pl.scaled) return hmm_forward_scaled;
+    if (pl.cta && !five) {
+        int npoly = 8;   // measured on 100 sequences x 2000 steps: 8 -> 2.67 ms, 10 -> 2.69, 12 -> 2.81
+
+        if (const char *env = getenv("PARPY_B200_FWD_POLY")) npoly = atoi(env);
+        switch (npoly) {
+            case 0: return hmm_forward_packed_cta<0x0000u>;
+            case 5: return hmm_forward_packed_cta<0x2492u>;
+            case 12: return hmm_forward_packed_cta<0xEEEEu>;
+            case 14: return hmm_forward_packed_cta<0xFEFEu>;
+            case 16: return hmm_forward_packed_cta<0xFFFFu>;
+            case 10: return hmm_forward_packed_cta<0x6DB6u>;
+            default: return hmm_forward_packed_cta<0xAAAAu>;
+        }
+    }
     if (pl.split && !five) {
         // how many of the 16 layers take the polynomial exponential
         int npoly = 5;
@@ -1264,15 +1419,15 @@ ResidentKernel pick_kernel(const Plan &pl, bool five) {
         if (const char *env = getenv("PARPY_B200_FWD_PACKED")) packed = atoi(env);
         if (packed) {
             // layer 0 stays on the MUFU pipe in every mask: it is on the path to the exchange
-            if (!getenv("PARPY_B200_FWD_POLY")) npoly = 10;
+            if (!getenv("PARPY_B200_FWD_POLY")) npoly = 8;
             switch (npoly) {
                 case 0: return hmm_forward_packed<0x0000u>;
                 case 5: return hmm_forward_packed<0x2492u>;   // layers 1,4,7,10,13
-                case 8: return hmm_forward_packed<0xAAAAu>;   // odd layers
                 case 9: return hmm_forward_packed<0xAD5Au>;   // all but 0,2,5,7,9,12,14
                 case 11: return hmm_forward_packed<0xDB6Eu>;  // all but 0,4,7,10,13
                 case 12: return hmm_forward_packed<0xEEEEu>;  // all but 0,4,8,12
-                default: return hmm_forward_packed<0x6DB6u>;  // 10: all but 0,3,6,9,12,15
+                case 10: return hmm_forward_packed<0x6DB6u>;  // all but 0,3,6,9,12,15
+                default: return hmm_forward_packed<0xAAAAu>;  // 8: odd layers
             }
         }
         switch (npoly) {
@@ -1291,7 +1446,8 @@ int32_t resident_config(const Plan &pl, bool five, cudaLaunchConfig_t *cfg,
                         cudaLaunchAttribute *attr, int *max_clusters, ResidentKernel *kern) {
     ResidentKernel k = pick_kernel(pl, five);
     size_t smem = size_t(2) * 4 * (size_t(pl.nt) * pl.kpt / 4) * sizeof(float);
-    if (pl.scaled) smem *= 2;  // mantissas + exponents
+    if (pl.cta && !five) smem = 0;  // static shared memory only
+    else if (pl.scaled) smem *= 2;  // mantissas + exponents
     else if (pl.split && !five) smem += size_t(4 + 8) * pl.nt * sizeof(float4);  // transition columns + layers 8..15
     if (pl.cs > 8) PB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
     PB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

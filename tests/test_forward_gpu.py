@@ -173,6 +173,44 @@ def test_kernel_layout_variants_agree_with_oracle(native, oracle_mod, monkeypatc
         for i in range(6):
             a = (a1 if int(seqs["lens"][i]) & 1 else a2)[i].cpu().numpy()
             assert max_rel(a, exp_alpha[i]) <= REL_ORACLE, env
+    # 5mer: one CTA per sequence with packed arithmetic (default) against the 4-CTA cluster layout
+    hmm = synthetic.hmm_model(5, seed=7)
+    seqs = synthetic.hmm_sequences(9, 2, 120, seed=8)
+    exp, exp_alpha = oracle_mod.forward(hmm, seqs, want_alpha=True)
+    dh, ds = to_dev(hmm), to_dev(seqs)
+    for env in [{"PARPY_B200_FWD_PACKED": "0"}] + [{"PARPY_B200_FWD_POLY": str(n)} for n in (0, 5, 8, 10, 12, 14, 16)]:
+        for k in ("PARPY_B200_FWD_SPLIT", "PARPY_B200_FWD_POLY", "PARPY_B200_FWD_PACKED"):
+            monkeypatch.delenv(k, raising=False)
+        for k, v in env.items():
+            monkeypatch.setenv(k, v)
+        rc, res, a1, a2 = cabi_forward(native, dh, ds, 2, alpha=True)
+        assert rc == 0, native.error_message()
+        assert max_rel(res.cpu().numpy(), exp) <= REL_ORACLE, env
+        for i in range(9):
+            a = (a1 if int(seqs["lens"][i]) & 1 else a2)[i].cpu().numpy()
+            assert max_rel(a, exp_alpha[i]) <= REL_ORACLE, env
+
+
+def test_packed_arithmetic_is_bit_identical_to_scalar(native, monkeypatch):
+    # The packed kernel issues the scalar kernel's additions and multiply-adds two at a time
+    # (add/sub/mul/fma.f32x2); every half rounds like the scalar instruction, so with the same
+    # set of polynomial layers the two must agree bit for bit, final alpha included.
+    from parpy_b200 import synthetic
+    hmm = synthetic.hmm_model(7, seed=11)
+    seqs = synthetic.hmm_sequences(5, 40, 300, seed=12)
+    dh, ds = to_dev(hmm), to_dev(seqs)
+    for n in (0, 5, 8):
+        out = {}
+        for packed in ("0", "1"):
+            monkeypatch.setenv("PARPY_B200_FWD_POLY", str(n))
+            monkeypatch.setenv("PARPY_B200_FWD_PACKED", packed)
+            rc, res, a1, a2 = cabi_forward(native, dh, ds, 2, alpha=True)
+            assert rc == 0, native.error_message()
+            out[packed] = (res.cpu().numpy().copy(), a1.cpu().numpy().copy(), a2.cpu().numpy().copy())
+        assert np.array_equal(out["0"][0], out["1"][0]), n
+        for i in range(5):
+            which = 1 if int(seqs["lens"][i]) & 1 else 2
+            assert np.array_equal(out["0"][which][i], out["1"][which][i]), (n, i)
 
 
 def test_scaled_variant_against_golden_oracle_and_log_space(native, oracle_mod):
