@@ -26,15 +26,20 @@
 
 #define V_LAYERS 16
 
-/* Best predecessor of `state`; returns the predecessor index (or 0xffffffff when
- * no candidate beats -inf, where the reference leaves the value uninitialised). */
+/* Best predecessor of `state`; returns the predecessor index. When no candidate beats -inf
+ * (the state cannot be reached at this step) the reference stores an uninitialised value
+ * (hmm.cu:404-406: `state_t maxs;` is only assigned inside `if (p > *maxp)`); this
+ * restatement and the CUDA kernel both take the first k-mer candidate there. The backward
+ * pass can meet such a state only where the reference's own output is arbitrary: a sequence
+ * of probability zero, or the step after the arg-max of a window that the reference reads
+ * one step early. */
 static inline uint32_t max_predecessor(const float *chi, int64_t N, int64_t state, float gamma,
                                        float syn, const float *trans1, const float *trans2,
                                        float *best) {
     const int64_t K = N / V_LAYERS;
     const int64_t layer = state / K, kmer = state % K;
     float maxp = -INFINITY;
-    uint32_t maxs = 0xffffffffu;
+    uint32_t maxs = (uint32_t)((state / 4) % (K / 4));
     for (int64_t x = 0; x < 4; ++x) {
         const int64_t pred = x * (K / 4) + (state / 4) % (K / 4);
         float p = trans1[(pred % K) * 4 + state % 4] + trans2[layer];
@@ -107,8 +112,7 @@ int oracle_viterbi(float gamma, const float *initial_prob, int64_t num_states,
             for (int64_t s = 1; s < N; ++s) if (chi1[s] > m) { m = chi1[s]; cur = (uint32_t)s; }
             for (int64_t j = batch_size - 1; j >= 0; --j) {
                 if (j < batch_size - 1) {
-                    const uint32_t z = zeta[(size_t)j * (size_t)N + cur];
-                    cur = z == 0xffffffffu ? cur : z;
+                    cur = zeta[(size_t)j * (size_t)N + cur];
                 }
                 if (t + j < out_stride) res[t + j] = cur;
             }

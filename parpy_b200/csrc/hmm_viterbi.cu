@@ -24,7 +24,6 @@
 namespace {
 
 constexpr int kLayers = 16;
-constexpr unsigned kNoPred = 15u;   // nibble of a state no candidate reached (all -inf)
 
 struct VitParams {
     const float *initial_prob;  // [16*K]
@@ -69,6 +68,37 @@ __global__ void vit_schedule(const int64_t *__restrict__ lens, int B, int *__res
     if (threadIdx.x == 0) *counter = 0;
 }
 
+// Packed fp32 pairs (add.rn.f32x2: one issue slot, each half rounded like a scalar add).
+__device__ __forceinline__ float2 vadd2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 vdup2(float x) { return make_float2(x, x); }
+
+__device__ __forceinline__ float vmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// Winner among the four k-mer candidates c0..c3 and the duration-chain candidate p5, in the
+// reference's order (j = 0..3, then p5, each taken only if strictly greater than the best so
+// far): the first candidate equal to the maximum. The compare-and-select instructions run on
+// the ALU pipe, which bounds this kernel; two 3-input maxima and one equality test per
+// candidate need fewer of them than a running (value, index) pair. The code comes out
+// already shifted to its nibble (SHIFT), so packing eight of them is a few ORs.
+// A state that no candidate reaches (all -inf) gets code 0. The reference leaves its back
+// pointer uninitialised (hmm.cu:404-406); the backward pass only ever visits reachable
+// states unless the whole sequence has probability zero, where the reference's path is
+// arbitrary as well.
+template <int SHIFT>
+__device__ __forceinline__ void pick5(float c0, float c1, float c2, float c3, float p5, float &best,
+                                      unsigned &code) {
+    const float m = vmax3(vmax3(c0, c1, c2), c3, p5);
+    unsigned c = c3 == m ? (3u << SHIFT) : (4u << SHIFT);
+    c = c2 == m ? (2u << SHIFT) : c;
+    c = c1 == m ? (1u << SHIFT) : c;
+    c = c0 == m ? 0u : c;
+    code = c;
+    best = m;
+}
+
 // (value, index) arg-max with the lowest index among equal values.
 __device__ __forceinline__ void argmax_combine(float &v, unsigned &i, float ov, unsigned oi) {
     if (ov > v || (ov == v && oi < i)) {
@@ -79,7 +109,7 @@ __device__ __forceinline__ void argmax_combine(float &v, unsigned &i, float ov, 
 
 __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p) {
     extern __shared__ __align__(16) float a0s[];  // [2][4][M] layer-0 values this CTA consumes
-    __shared__ float s_t2[kLayers];
+    __shared__ float2 s_t2[kLayers];   // (trans2[d], trans2[d])
     __shared__ int s_seq;
     __shared__ unsigned s_last;
     __shared__ float s_warp_v[32];
@@ -100,12 +130,13 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
     const int bos = p.batch - p.overlap;
     uint4 *codes = p.codes + (long long)(blockIdx.x / CS) * p.codes_per_cluster;
 
-    if (tid < kLayers) s_t2[tid] = __ldg(p.trans2 + tid);
-    float T[4][4];
+    if (tid < kLayers) s_t2[tid] = vdup2(__ldg(p.trans2 + tid));
+    float2 T[4][2];   // transition log-probabilities into the thread's two k-mer pairs
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         const float4 v = __ldg(reinterpret_cast<const float4 *>(p.trans1) + (j * Kq + (g >> 2)));
-        T[j][0] = v.x; T[j][1] = v.y; T[j][2] = v.z; T[j][3] = v.w;
+        T[j][0] = make_float2(v.x, v.y);
+        T[j][1] = make_float2(v.z, v.w);
     }
     const unsigned a0_base = smem_u32(a0s);
     unsigned dst0;
@@ -215,30 +246,49 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
                 }
                 cluster_wait();
                 const float *seg = a0s + (buf ? 4 * M : 0) + tid;
-                const float a[4] = {seg[0], seg[M], seg[2 * M], seg[3 * M]};
+                const float2 a[4] = {vdup2(seg[0]), vdup2(seg[M]), vdup2(seg[2 * M]), vdup2(seg[3 * M])};
                 const unsigned dst = dst0 + (buf ? 0u : buf_bytes);
                 unsigned words[8];
 #pragma unroll
                 for (int d = 0; d < kLayers; ++d) {
-                    const float t2 = s_t2[d];
+                    const float2 t2 = s_t2[d];
                     unsigned packed = 0;
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        float best = -INFINITY;
-                        unsigned code = kNoPred;
+                    for (int h = 0; h < 2; ++h) {
+                        // the four k-mer candidates of both halves: (T + t2) + a, as the reference adds them
+                        float2 cand[4];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const float pj = (T[j][c] + t2) + a[j];
-                            if (pj > best) { best = pj; code = j; }
+                        for (int j = 0; j < 4; ++j) cand[j] = vadd2(vadd2(T[j][h], t2), a[j]);
+                        const float2 nx = make_float2(chi[d + 1 < kLayers ? d + 1 : 15][2 * h],
+                                                      chi[d + 1 < kLayers ? d + 1 : 15][2 * h + 1]);
+                        // duration-chain candidate; below layer 14 its log-probability is 0
+                        const float2 p5 = d == 15 ? vadd2(vdup2(p.gamma), nx)
+                                        : d == 14 ? vadd2(vdup2(p.synthetic), nx) : nx;
+                        float bx, by;
+                        unsigned cx, cy;
+                        if (h == 0) {
+                            if (d & 1) {
+                                pick5<16>(cand[0].x, cand[1].x, cand[2].x, cand[3].x, p5.x, bx, cx);
+                                pick5<20>(cand[0].y, cand[1].y, cand[2].y, cand[3].y, p5.y, by, cy);
+                            } else {
+                                pick5<0>(cand[0].x, cand[1].x, cand[2].x, cand[3].x, p5.x, bx, cx);
+                                pick5<4>(cand[0].y, cand[1].y, cand[2].y, cand[3].y, p5.y, by, cy);
+                            }
+                        } else {
+                            if (d & 1) {
+                                pick5<24>(cand[0].x, cand[1].x, cand[2].x, cand[3].x, p5.x, bx, cx);
+                                pick5<28>(cand[0].y, cand[1].y, cand[2].y, cand[3].y, p5.y, by, cy);
+                            } else {
+                                pick5<8>(cand[0].x, cand[1].x, cand[2].x, cand[3].x, p5.x, bx, cx);
+                                pick5<12>(cand[0].y, cand[1].y, cand[2].y, cand[3].y, p5.y, by, cy);
+                            }
                         }
-                        const float p5 = d == 15 ? p.gamma + chi[15][c]
-                                       : d == 14 ? p.synthetic + chi[15][c]
-                                                 : 0.0f + chi[d + 1 < kLayers ? d + 1 : 15][c];
-                        if (p5 > best) { best = p5; code = 4u; }
-                        chi[d][c] = best + e[c];
-                        packed |= code << (4 * c);
+                        const float2 r = vadd2(make_float2(bx, by), make_float2(e[2 * h], e[2 * h + 1]));
+                        chi[d][2 * h] = r.x;
+                        chi[d][2 * h + 1] = r.y;
+                        packed |= cx | cy;
                     }
-                    if (d & 1) words[d >> 1] |= packed << 16;
+                    if (d & 1) words[d >> 1] |= packed;
                     else words[d >> 1] = packed;
                     if (d == 0) {
                         st_cluster_v4(dst, chi[0][0], chi[0][1], chi[0][2], chi[0][3]);
