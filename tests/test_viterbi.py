@@ -74,6 +74,19 @@ def test_oracle_windowing_rules():
             shift = (la == 0) and (kb // 4 == ka % (K // 4))
             restart = pos % (16 - 4) == 0 and a == b
             assert chain or shift or restart, (i, pos, a, b)
+    # Windows of two steps: the arg-max of a full window is read one step before its end
+    # (hmm.cu:414-434 reads the first chi buffer), so the backward pass can start from a state
+    # that nothing reaches at the last step. The reference's back pointer is uninitialised
+    # there; oracle and kernel both use the state's first k-mer candidate.
+    K = 64
+    for path in oracle.viterbi(hmm, seqs, batch_size=2, batch_overlap=0):
+        for w in range(0, len(path) - 1, 2):
+            a, b = int(path[w]), int(path[w + 1])
+            la, ka, lb, kb = a // K, a % K, b // K, b % K
+            chain = (ka == kb) and (la == lb + 1 or (la == 15 and lb == 15))
+            shift = (la == 0) and (kb // 4 == ka % (K // 4))
+            first_candidate = a == (b // 4) % (K // 4)
+            assert chain or shift or first_candidate, (w, a, b)
     # a window at least as long as the sequence is plain Viterbi
     obs = seqs["data"][0, :int(seqs["lens"][0])].numpy().view(np.uint8)
     whole = oracle.viterbi(hmm, {"data": seqs["data"][:1], "lens": seqs["lens"][:1]}, 1024, 128)[0]
