@@ -121,6 +121,10 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
     const int NT = blockDim.x;
     const unsigned rank = cluster_ctarank();
     const unsigned CS = cluster_nctarank();
+    // One CTA per sequence (small state spaces): the hardware cluster barrier is replaced by
+    // the CTA barrier at the points where the split barrier completes.
+    auto arrive = [&]() { if (CS > 1) cluster_arrive(); };
+    auto wait = [&]() { if (CS > 1) cluster_wait(); else __syncthreads(); };
     const int K = p.K;
     const int Kq = K >> 2;
     const int M = NT;
@@ -157,8 +161,8 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
             const int seq = i < p.B ? p.order[i] : -1;
             for (unsigned r = 0; r < CS; ++r) st_cluster_s32(map_to_rank(seq_addr, r), seq);
         }
-        cluster_arrive();
-        cluster_wait();
+        arrive();
+        wait();
         const int seq = s_seq;
         if (seq < 0) break;
         long long len64 = p.lens[seq];
@@ -196,7 +200,7 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
             }
             unsigned buf = 0;
             st_cluster_v4(dst0, chi[0][0], chi[0][1], chi[0][2], chi[0][3]);
-            cluster_arrive();
+            arrive();
 
             float best_v = -INFINITY;
             unsigned best_i = 0;
@@ -224,18 +228,18 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
                     st_cluster_f32(map_to_rank(clv_addr + 4u * rank, tid), bv);
                     st_cluster_s32(map_to_rank(cli_addr + 4u * rank, tid), (int)bi);
                 }
-                cluster_arrive();
-                cluster_wait();
+                arrive();
+                wait();
                 best_v = s_cl_v[0];
                 best_i = s_cl_i[0];
                 for (unsigned r = 1; r < CS; ++r) argmax_combine(best_v, best_i, s_cl_v[r], s_cl_i[r]);
-                cluster_arrive();   // everyone has read s_cl_* before it can be rewritten
-                cluster_wait();
+                arrive();   // everyone has read s_cl_* before it can be rewritten
+                wait();
             };
             if (karg == 0) {
-                cluster_wait();
+                wait();
                 cluster_argmax();
-                cluster_arrive();
+                arrive();
             }
 
             // ---- forward steps with back pointers (hmm.cu:116-176, 378-412) ----------------
@@ -244,7 +248,7 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
                     const float4 v = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)obs[t + k] * K + g));
                     e[0] = v.x; e[1] = v.y; e[2] = v.z; e[3] = v.w;
                 }
-                cluster_wait();
+                wait();
                 const float *seg = a0s + (buf ? 4 * M : 0) + tid;
                 const float2 a[4] = {vdup2(seg[0]), vdup2(seg[M]), vdup2(seg[2 * M]), vdup2(seg[3 * M])};
                 const unsigned dst = dst0 + (buf ? 0u : buf_bytes);
@@ -292,7 +296,7 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
                     else words[d >> 1] = packed;
                     if (d == 0) {
                         st_cluster_v4(dst, chi[0][0], chi[0][1], chi[0][2], chi[0][3]);
-                        cluster_arrive();
+                        arrive();
                     }
                 }
                 uint4 *slot = codes + ((long long)(k - 1) * Kq + gthread) * 2;
@@ -300,18 +304,18 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
                 __stcg(slot + 1, make_uint4(words[4], words[5], words[6], words[7]));
                 buf ^= 1u;
                 if (k == karg && k < L - 1) {   // full window: arg-max one step before the end
-                    cluster_wait();
+                    wait();
                     cluster_argmax();
-                    cluster_arrive();
+                    arrive();
                 }
             }
-            cluster_wait();
+            wait();
             if (karg == L - 1 && karg > 0) cluster_argmax();
 
             // ---- backward pass (hmm.cu:436-508) -----------------------------------------------
             __threadfence();   // the nibbles of every CTA must be visible to the leader
-            cluster_arrive();
-            cluster_wait();
+            arrive();
+            wait();
             if (rank == 0) {
                 // positions L-1 .. batch-1 all hold the arg-max state (identity back pointers)
                 const long long hi = min((long long)t + p.batch, p.out_stride);
@@ -334,8 +338,8 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
                     for (unsigned r = 0; r < CS; ++r) st_cluster_s32(map_to_rank(last_addr, r), (int)anchor);
                 }
             }
-            cluster_arrive();
-            cluster_wait();
+            arrive();
+            wait();
         }
     }
 }
@@ -347,7 +351,13 @@ struct VitPlan {
 bool vit_plan(long long K, VitPlan *pl) {
     if (K < 1024 || (K & (K - 1)) != 0) return false;
     const long long threads = K / 4;
-    long long nt = K <= 1024 ? 64 : 512;
+    // 5-mer: one 256-thread CTA per sequence (CTA barrier per step; 5.4 ms for 100 sequences of 2000
+    // steps against 6.3 ms for clusters of 4 x 64 threads); larger models: clusters of 512-thread CTAs
+    long long nt = K <= 1024 ? K / 4 : 512;
+    if (const char *env = getenv("PARPY_B200_VIT_NT")) {
+        const long long v = atoll(env);
+        if (v >= 32 && v <= 512 && (v & (v - 1)) == 0 && v <= threads) nt = v;
+    }
     long long cs = threads / nt;
     if (cs > 16) return false;
     pl->nt = (int)nt;
