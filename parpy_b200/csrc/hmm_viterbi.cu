@@ -320,22 +320,53 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
                 // positions L-1 .. batch-1 all hold the arg-max state (identity back pointers)
                 const long long hi = min((long long)t + p.batch, p.out_stride);
                 for (long long pos = t + L - 1 + tid; pos < hi; pos += NT) res[pos] = best_i;
-                if (tid == 0) {
+                if (tid < 32) {
+                    // One warp walks the window backwards. A hop is a dependent load, so the warp
+                    // speculates: a k-mer is usually left through its duration chain (back pointer
+                    // 4: same k-mer, one layer up), and then the next 32 hops read words whose
+                    // addresses are known in advance. Lane i fetches the word of hop i under that
+                    // assumption, all 32 loads travel together, and the hops are resolved from
+                    // registers until one of them changes the k-mer (the rest is fetched again).
                     unsigned cur = best_i;
                     unsigned anchor = cur;
-                    for (int j = L - 2; j >= 0; --j) {
-                        const unsigned s = cur % (unsigned)K, d = cur / (unsigned)K;
-                        const unsigned *w = reinterpret_cast<const unsigned *>(codes + ((long long)j * Kq + (s >> 2)) * 2);
-                        const unsigned word = __ldcg(w + (d >> 1));
-                        const unsigned code = (word >> (16 * (d & 1) + 4 * (s & 3))) & 15u;
-                        if (code < 4u) cur = code * (unsigned)Kq + (s >> 2);
-                        else if (code == 4u) cur = d == 15u ? cur : cur + (unsigned)K;
-                        res[t + j] = cur;
-                        if (j == bos - 1) anchor = cur;
+                    int j = L - 2;
+                    while (j >= 0) {
+                        const unsigned s = cur % (unsigned)K, d0 = cur / (unsigned)K;
+                        const int jj = j - tid;                       // my hop's step
+                        const unsigned dd = min(d0 + (unsigned)tid, 15u);   // its layer if the chain holds
+                        unsigned word = 0;
+                        if (jj >= 0)
+                            word = __ldcg(reinterpret_cast<const unsigned *>(codes + ((long long)jj * Kq + (s >> 2)) * 2) +
+                                          (dd >> 1));
+                        const unsigned mine = (word >> (16 * (dd & 1) + 4 * (s & 3))) & 15u;
+                        // hops that follow the chain, up to the first that does not (or the window start)
+                        const unsigned off_chain = __ballot_sync(0xffffffffu, mine != 4u || jj < 0);
+                        const int n_chain = off_chain ? __ffs(off_chain) - 1 : 32;
+                        // lane i < n_chain writes the state after i + 1 chain hops
+                        if (tid < n_chain) {
+                            const unsigned st = min(d0 + (unsigned)tid + 1u, 15u) * (unsigned)K + s;
+                            res[t + jj] = st;
+                            if (jj == bos - 1) anchor = st;
+                        }
+                        const unsigned d_end = min(d0 + (unsigned)n_chain, 15u);
+                        cur = d_end * (unsigned)K + s;
+                        j -= n_chain;
+                        if (n_chain < 32 && j >= 0) {
+                            // the hop that left the chain: a k-mer predecessor (codes 0..3)
+                            const unsigned code = __shfl_sync(0xffffffffu, mine, n_chain);
+                            cur = code * (unsigned)Kq + (s >> 2);
+                            if (tid == 0) res[t + j] = cur;
+                            if (j == bos - 1) anchor = cur;
+                            --j;
+                        }
                     }
+                    // whichever lane met position bos-1 holds the anchor
+                    const unsigned has = __ballot_sync(0xffffffffu, anchor != best_i);
+                    if (has) anchor = __shfl_sync(0xffffffffu, anchor, __ffs(has) - 1);
                     if (L - 1 == bos - 1) anchor = best_i;
                     // the next window restarts from the state decoded at its t-1
-                    for (unsigned r = 0; r < CS; ++r) st_cluster_s32(map_to_rank(last_addr, r), (int)anchor);
+                    if (tid == 0)
+                        for (unsigned r = 0; r < CS; ++r) st_cluster_s32(map_to_rank(last_addr, r), (int)anchor);
                 }
             }
             arrive();
