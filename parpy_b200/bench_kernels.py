@@ -88,7 +88,10 @@ def main():
         out = torch.empty_like(x)
         ms = timed(lambda: _native.check(lib.parpy_b200_softmax(P(x.data_ptr()), shape[0], shape[1],
                                                                 P(out.data_ptr()), stream())), flush=flush)
-        report(f"softmax[{shape[0]},{shape[1]}]", ms, 8 * x.numel())
+        # a plain device copy of the same shape under the same timing: what this size allows
+        copy_ms = timed(lambda: out.copy_(x), flush=flush)
+        report(f"softmax[{shape[0]},{shape[1]}]", ms, 8 * x.numel(),
+               {"copy_same_shape_ms_median": statistics.median(copy_ms)})
         del x, out
 
     if want("reduce"):

@@ -55,6 +55,36 @@ def test_softmax_shapes_against_oracle(native, oracle_mod, shape):
     assert np.allclose(got.sum(axis=1), 1.0, atol=1e-5)
 
 
+@pytest.mark.parametrize("shape", [(9000, 1024), (33007, 512), (40003, 260), (2100, 4096), (601, 16384), (1003, 9000)])
+def test_large_row_maps(native, oracle_mod, shape):
+    # Inputs of 32 MiB and more (several waves of CTAs): short rows, one per warp, with a last
+    # CTA that is not full; long rows, one per CTA, with the last float4 slots of a thread
+    # unused; softmax, in-place normalisation, exp + row sums.
+    g = torch.Generator().manual_seed(77)
+    x = torch.randn(shape, generator=g, dtype=torch.float32)
+    xd = x.cuda()
+    out = torch.empty_like(xd)
+    stream = P(torch.cuda.current_stream().cuda_stream)
+    rc = native.lib().parpy_b200_softmax(P(xd.data_ptr()), shape[0], shape[1], P(out.data_ptr()), stream)
+    assert rc == 0, native.error_message()
+    got = out.cpu().numpy()
+    assert max_rel(got, oracle_mod.softmax(x)) <= 1e-4
+    assert np.allclose(got.sum(axis=1), 1.0, atol=1e-5)
+    pos = (torch.rand(shape, generator=g) + 0.05)
+    pd = pos.cuda()
+    rc = native.lib().parpy_b200_normalize_rows(P(pd.data_ptr()), shape[0], shape[1], stream)
+    assert rc == 0, native.error_message()
+    assert max_rel(pd.cpu().numpy(), oracle_mod.normalize_rows(pos)) <= 1e-5
+    small = (x * 0.25).contiguous()
+    sd = small.cuda()
+    sums = torch.empty(shape[0], device="cuda")
+    rc = native.lib().parpy_b200_sum_exp_rows(P(sd.data_ptr()), shape[0], shape[1], P(sums.data_ptr()), stream)
+    assert rc == 0, native.error_message()
+    ref_x, ref_sums = oracle_mod.sum_exp_rows(small.numpy().copy())
+    assert max_rel(sd.cpu().numpy(), ref_x) <= 1e-5
+    assert np.allclose(sums.cpu().numpy(), ref_sums, rtol=1e-5)
+
+
 def test_softmax_reference_shaped_entry_and_extremes(native):
     x = torch.tensor([[1e4, 1e4 - 1, -1e4, 0.0], [-3e38, -3e38, -3e38, -3e38]], device="cuda")
     out = torch.empty_like(x)
