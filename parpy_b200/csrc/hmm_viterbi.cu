@@ -99,6 +99,43 @@ __device__ __forceinline__ void pick5(float c0, float c1, float c2, float c3, fl
     best = m;
 }
 
+// The four k-mer candidates of a state differ between duration layers only by the additive
+// trans2[d], so in exact arithmetic their winner does not depend on the layer. With fp32
+// rounding it can, but only when the two best are closer than the rounding errors. `decide4`
+// evaluates s_j = T_j + a_j once per k-mer and reports the winner j* together with `safe`:
+// true when s_best - s_second exceeds a bound on every rounding error involved, in which case
+// fl(fl(T_j + trans2[d]) + a_j) has the same strict winner j* at every layer and only that one
+// candidate needs to be evaluated per layer (bit-identical to evaluating all four).
+//   error of one layer's candidate:  <= 1.0001 u (|T_j| + 2 t2max + |s_j|),  u = 2^-24
+//   error of s_j itself:             <= 1.0001 u |s_j|
+// so  s_b - s_k > 2^-22 (|s_b| + |s_k| + Tmax + 2 t2max)  leaves a factor two in hand; the
+// left side grows faster than the right as s_k falls, so testing the second best covers the
+// rest. -inf among the candidates, NaN or an infinite bound make `safe` false (except a lone
+// finite candidate), and the caller then evaluates all candidates at every layer as before.
+struct Decide4 {
+    unsigned j;    // winner (first index among equal maxima of s)
+    bool safe;
+};
+__device__ __forceinline__ Decide4 decide4(float s0, float s1, float s2, float s3, float slack) {
+    const float hi01 = fmaxf(s0, s1), lo01 = fminf(s0, s1);
+    const float hi23 = fmaxf(s2, s3), lo23 = fminf(s2, s3);
+    const float best = fmaxf(hi01, hi23);
+    const float second = fmaxf(fminf(hi01, hi23), hi01 >= hi23 ? lo01 : lo23);
+    unsigned j = s2 == best ? 2u : 3u;
+    j = s1 == best ? 1u : j;
+    j = s0 == best ? 0u : j;
+    const float bound = 0x1p-22f * (fabsf(best) + fabsf(second) + slack);
+    Decide4 r;
+    r.j = j;
+    r.safe = (best - second > bound) || (second == -INFINITY && best > -INFINITY && slack < INFINITY);
+    return r;
+}
+__device__ __forceinline__ float sel4(unsigned j, float v0, float v1, float v2, float v3) {
+    float r = j == 2u ? v2 : v3;
+    r = j == 1u ? v1 : r;
+    return j == 0u ? v0 : r;
+}
+
 // (value, index) arg-max with the lowest index among equal values.
 __device__ __forceinline__ void argmax_combine(float &v, unsigned &i, float ov, unsigned oi) {
     if (ov > v || (ov == v && oi < i)) {
@@ -141,6 +178,24 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
         const float4 v = __ldg(reinterpret_cast<const float4 *>(p.trans1) + (j * Kq + (g >> 2)));
         T[j][0] = make_float2(v.x, v.y);
         T[j][1] = make_float2(v.z, v.w);
+    }
+    // Tmax + 2 t2max per k-mer of the thread (see decide4); infinite when a table holds -inf
+    float slack[4];
+    {
+        float t2max = 0.0f;
+        for (int d = 0; d < kLayers; ++d) t2max = fmaxf(t2max, fabsf(__ldg(p.trans2 + d)));
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float mx = 0.0f, my = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                // a transition of probability zero makes its candidate -inf at every layer: no error to bound
+                mx = fmaxf(mx, T[j][h].x == -INFINITY ? 0.0f : fabsf(T[j][h].x));
+                my = fmaxf(my, T[j][h].y == -INFINITY ? 0.0f : fabsf(T[j][h].y));
+            }
+            slack[2 * h] = mx + 2.0f * t2max;
+            slack[2 * h + 1] = my + 2.0f * t2max;
+        }
     }
     const unsigned a0_base = smem_u32(a0s);
     unsigned dst0;
@@ -254,51 +309,92 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
                 const unsigned dst = dst0 + (buf ? 0u : buf_bytes);
                 unsigned words[8];
 #pragma unroll
-                for (int d = 0; d < kLayers; ++d) {
-                    const float2 t2 = s_t2[d];
-                    unsigned packed = 0;
+                for (int i = 0; i < 8; ++i) words[i] = 0u;
+                // winner of the k-mer candidates, once per k-mer (decide4); a pair of k-mers takes
+                // the short path when it is safe for both in every lane of the warp
+                Decide4 dec[4];
+                bool fast[2];
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        // the four k-mer candidates of both halves: (T + t2) + a, as the reference adds them
-                        float2 cand[4];
+                for (int h = 0; h < 2; ++h) {
+                    float2 sj[4];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) cand[j] = vadd2(vadd2(T[j][h], t2), a[j]);
-                        const float2 nx = make_float2(chi[d + 1 < kLayers ? d + 1 : 15][2 * h],
-                                                      chi[d + 1 < kLayers ? d + 1 : 15][2 * h + 1]);
-                        // duration-chain candidate; below layer 14 its log-probability is 0
-                        const float2 p5 = d == 15 ? vadd2(vdup2(p.gamma), nx)
-                                        : d == 14 ? vadd2(vdup2(p.synthetic), nx) : nx;
-                        float bx, by;
-                        unsigned cx, cy;
-                        if (h == 0) {
-                            if (d & 1) {
-                                pick5<16>(cand[0].x, cand[1].x, cand[2].x, cand[3].x, p5.x, bx, cx);
-                                pick5<20>(cand[0].y, cand[1].y, cand[2].y, cand[3].y, p5.y, by, cy);
-                            } else {
-                                pick5<0>(cand[0].x, cand[1].x, cand[2].x, cand[3].x, p5.x, bx, cx);
-                                pick5<4>(cand[0].y, cand[1].y, cand[2].y, cand[3].y, p5.y, by, cy);
-                            }
-                        } else {
-                            if (d & 1) {
-                                pick5<24>(cand[0].x, cand[1].x, cand[2].x, cand[3].x, p5.x, bx, cx);
-                                pick5<28>(cand[0].y, cand[1].y, cand[2].y, cand[3].y, p5.y, by, cy);
-                            } else {
-                                pick5<8>(cand[0].x, cand[1].x, cand[2].x, cand[3].x, p5.x, bx, cx);
-                                pick5<12>(cand[0].y, cand[1].y, cand[2].y, cand[3].y, p5.y, by, cy);
-                            }
-                        }
-                        const float2 r = vadd2(make_float2(bx, by), make_float2(e[2 * h], e[2 * h + 1]));
-                        chi[d][2 * h] = r.x;
-                        chi[d][2 * h + 1] = r.y;
-                        packed |= cx | cy;
-                    }
-                    if (d & 1) words[d >> 1] |= packed;
-                    else words[d >> 1] = packed;
-                    if (d == 0) {
-                        st_cluster_v4(dst, chi[0][0], chi[0][1], chi[0][2], chi[0][3]);
-                        arrive();
-                    }
+                    for (int j = 0; j < 4; ++j) sj[j] = vadd2(T[j][h], a[j]);
+                    dec[2 * h] = decide4(sj[0].x, sj[1].x, sj[2].x, sj[3].x, slack[2 * h]);
+                    dec[2 * h + 1] = decide4(sj[0].y, sj[1].y, sj[2].y, sj[3].y, slack[2 * h + 1]);
+                    fast[h] = __all_sync(0xffffffffu, dec[2 * h].safe && dec[2 * h + 1].safe);
                 }
+                // layers [d_lo, d_hi) of pair h, ascending (a layer reads the old value of the next)
+                auto layers = [&](const int h, const int d_lo, const int d_hi) {
+                    if (fast[h]) {
+                        const unsigned jx = dec[2 * h].j, jy = dec[2 * h + 1].j;
+                        const float2 Tw = make_float2(sel4(jx, T[0][h].x, T[1][h].x, T[2][h].x, T[3][h].x),
+                                                      sel4(jy, T[0][h].y, T[1][h].y, T[2][h].y, T[3][h].y));
+                        const float2 aw = make_float2(sel4(jx, a[0].x, a[1].x, a[2].x, a[3].x),
+                                                      sel4(jy, a[0].x, a[1].x, a[2].x, a[3].x));
+                        const unsigned ex = jx << (8 * h), ey = jy << (8 * h + 4);     // even layers
+                        const unsigned ox = ex << 16, oy = ey << 16;                     // odd layers
+#pragma unroll
+                        for (int d = d_lo; d < d_hi; ++d) {
+                            const float2 val = vadd2(vadd2(Tw, s_t2[d]), aw);
+                            const float2 nx = make_float2(chi[d + 1 < kLayers ? d + 1 : 15][2 * h],
+                                                          chi[d + 1 < kLayers ? d + 1 : 15][2 * h + 1]);
+                            const float2 p5 = d == 15 ? vadd2(vdup2(p.gamma), nx)
+                                            : d == 14 ? vadd2(vdup2(p.synthetic), nx) : nx;
+                            const unsigned sh = 8 * h + 16 * (d & 1);
+                            const unsigned cx = p5.x > val.x ? (4u << sh) : ((d & 1) ? ox : ex);
+                            const unsigned cy = p5.y > val.y ? (4u << (sh + 4)) : ((d & 1) ? oy : ey);
+                            const float2 r = vadd2(make_float2(fmaxf(val.x, p5.x), fmaxf(val.y, p5.y)),
+                                                   make_float2(e[2 * h], e[2 * h + 1]));
+                            chi[d][2 * h] = r.x;
+                            chi[d][2 * h + 1] = r.y;
+                            words[d >> 1] |= cx | cy;
+                        }
+                    } else {
+#pragma unroll
+                        for (int d = d_lo; d < d_hi; ++d) {
+                            const float2 t2 = s_t2[d];
+                            // all four k-mer candidates: (T + t2) + a, as the reference adds them
+                            float2 cand[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) cand[j] = vadd2(vadd2(T[j][h], t2), a[j]);
+                            const float2 nx = make_float2(chi[d + 1 < kLayers ? d + 1 : 15][2 * h],
+                                                          chi[d + 1 < kLayers ? d + 1 : 15][2 * h + 1]);
+                            // duration-chain candidate; below layer 14 its log-probability is 0
+                            const float2 p5 = d == 15 ? vadd2(vdup2(p.gamma), nx)
+                                            : d == 14 ? vadd2(vdup2(p.synthetic), nx) : nx;
+                            float bx, by;
+                            unsigned cx, cy;
+                            if (h == 0) {
+                                if (d & 1) {
+                                    pick5<16>(cand[0].x, cand[1].x, cand[2].x, cand[3].x, p5.x, bx, cx);
+                                    pick5<20>(cand[0].y, cand[1].y, cand[2].y, cand[3].y, p5.y, by, cy);
+                                } else {
+                                    pick5<0>(cand[0].x, cand[1].x, cand[2].x, cand[3].x, p5.x, bx, cx);
+                                    pick5<4>(cand[0].y, cand[1].y, cand[2].y, cand[3].y, p5.y, by, cy);
+                                }
+                            } else {
+                                if (d & 1) {
+                                    pick5<24>(cand[0].x, cand[1].x, cand[2].x, cand[3].x, p5.x, bx, cx);
+                                    pick5<28>(cand[0].y, cand[1].y, cand[2].y, cand[3].y, p5.y, by, cy);
+                                } else {
+                                    pick5<8>(cand[0].x, cand[1].x, cand[2].x, cand[3].x, p5.x, bx, cx);
+                                    pick5<12>(cand[0].y, cand[1].y, cand[2].y, cand[3].y, p5.y, by, cy);
+                                }
+                            }
+                            const float2 r = vadd2(make_float2(bx, by), make_float2(e[2 * h], e[2 * h + 1]));
+                            chi[d][2 * h] = r.x;
+                            chi[d][2 * h + 1] = r.y;
+                            words[d >> 1] |= cx | cy;
+                        }
+                    }
+                };
+                // layer 0 of both pairs first: it is what the other CTAs wait for
+                layers(0, 0, 1);
+                layers(1, 0, 1);
+                st_cluster_v4(dst, chi[0][0], chi[0][1], chi[0][2], chi[0][3]);
+                arrive();
+                layers(0, 1, kLayers);
+                layers(1, 1, kLayers);
                 uint4 *slot = codes + ((long long)(k - 1) * Kq + gthread) * 2;
                 __stcg(slot, make_uint4(words[0], words[1], words[2], words[3]));
                 __stcg(slot + 1, make_uint4(words[4], words[5], words[6], words[7]));

@@ -142,6 +142,29 @@ def test_kernel_matches_oracle_small_windows_and_ragged_lengths(k, batch, overla
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("noise", [0.0, 3e-7, 1e-5, 1e-3])
+def test_kernel_matches_oracle_when_candidates_nearly_tie(noise):
+    # The kernel decides the winner among the four k-mer candidates once per k-mer when their
+    # margin provably exceeds the rounding errors, and evaluates every candidate at every layer
+    # otherwise. Models built to sit on that boundary: transition log-probabilities that are
+    # equal up to a relative noise of 0 (exact ties), about one ulp, and a few hundred ulps, and
+    # emissions quantised to a handful of values so that scores collide; sequences long enough
+    # for scores of magnitude 1e4.
+    from parpy_b200 import hmm as hmm_mod
+    hmm = synthetic.hmm_model(5, seed=41)
+    g = torch.Generator().manual_seed(42)
+    base = torch.full((1024, 4), -1.3862944, dtype=torch.float32)
+    hmm["trans1"] = (base * (1.0 + noise * torch.randn(1024, 4, generator=g))).contiguous()
+    hmm["output_prob"] = (torch.round(hmm["output_prob"] * 2.0) / 2.0).contiguous()
+    seqs = synthetic.hmm_sequences(3, 2500, 2500, seed=43)
+    seqs["lens"] = torch.tensor([2500, 1024, 1500])
+    exp = oracle.viterbi(hmm, seqs)
+    got = hmm_mod.viterbi_paths(_dev(hmm), _dev(seqs))
+    for i, (a, b) in enumerate(zip(got, exp)):
+        assert np.array_equal(a, b), (noise, i, int(np.argmax(a != b)))
+
+
+@pytest.mark.gpu
 def test_viterbi_argument_checks(native):
     from parpy_b200 import hmm as hmm_mod
     hmm, seqs = _dev(synthetic.hmm_model(3)), _dev(synthetic.hmm_sequences(2, 5, 9))
