@@ -1407,6 +1407,7 @@ ResidentKernel pick_kernel(const Plan &pl, bool five) {
             case 12: return hmm_forward_packed_cta<0xEEEEu>;
             case 14: return hmm_forward_packed_cta<0xFEFEu>;
             case 16: return hmm_forward_packed_cta<0xFFFFu>;
+            case 7: return hmm_forward_packed_cta<0x5554u>;
             case 10: return hmm_forward_packed_cta<0x6DB6u>;
             default: return hmm_forward_packed_cta<0xAAAAu>;
         }
@@ -1418,16 +1419,20 @@ ResidentKernel pick_kernel(const Plan &pl, bool five) {
         int packed = 1;
         if (const char *env = getenv("PARPY_B200_FWD_PACKED")) packed = atoi(env);
         if (packed) {
-            // layer 0 stays on the MUFU pipe in every mask: it is on the path to the exchange
-            if (!getenv("PARPY_B200_FWD_POLY")) npoly = 8;
+            // layer 0 stays on the MUFU pipe in every mask: it is on the path to the exchange.
+            // Measured on the benchmark workload (state-steps/s): even layers but 0 (7 layers) 1.799e12,
+            // layers 1..8 1.793e12, odd layers 1.764e12, 9 layers 1.747e12, 10 layers 1.751e12,
+            // 11 layers 1.712e12, layers 8..15 1.707e12.
+            if (!getenv("PARPY_B200_FWD_POLY")) npoly = 7;
             switch (npoly) {
                 case 0: return hmm_forward_packed<0x0000u>;
                 case 5: return hmm_forward_packed<0x2492u>;   // layers 1,4,7,10,13
+                case 8: return hmm_forward_packed<0xAAAAu>;   // odd layers
                 case 9: return hmm_forward_packed<0xAD5Au>;   // all but 0,2,5,7,9,12,14
+                case 10: return hmm_forward_packed<0x6DB6u>;  // all but 0,3,6,9,12,15
                 case 11: return hmm_forward_packed<0xDB6Eu>;  // all but 0,4,7,10,13
                 case 12: return hmm_forward_packed<0xEEEEu>;  // all but 0,4,8,12
-                case 10: return hmm_forward_packed<0x6DB6u>;  // all but 0,3,6,9,12,15
-                default: return hmm_forward_packed<0xAAAAu>;  // 8: odd layers
+                default: return hmm_forward_packed<0x5554u>;  // 7: even layers but 0
             }
         }
         switch (npoly) {
