@@ -144,8 +144,47 @@ __device__ __forceinline__ void argmax_combine(float &v, unsigned &i, float ov, 
     }
 }
 
+// ASYNC (clusters of 2 to 8 CTAs): layer 0 travels with st.async and is counted in by an
+// mbarrier of the consuming CTA (complete_tx) instead of st.shared::cluster + barrier.cluster,
+// so the sender runs no release fence. A CTA's phase completes on the bytes of a quarter of
+// each producer's threads (the quarter whose k-mers it consumes), so a CTA can run ahead of a
+// thread elsewhere in the cluster: in a cluster of 8 a writer of round r is only ordered after
+// every thread's read of round r - 4 (three hops through the "feeds" relation reach every
+// CTA), hence four buffers and four mbarriers. Waits are bounded.
+constexpr int kVitWaitLimit = 1 << 22;
+__device__ unsigned g_vit_status;   // bit 0: a wait for layer 0 ran out; the paths of that call are not valid
+
+__device__ __forceinline__ bool vit_mbar_wait(unsigned mbar, unsigned parity) {
+    for (int i = 0; i < kVitWaitLimit; ++i) {
+        unsigned ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                     "selp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(mbar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+// Layer 0 of one thread to the consuming CTA: buffer b of its shared memory.
+template <bool ASYNC>
+__device__ __forceinline__ void vit_send_layer0(unsigned dst, unsigned rmbar, unsigned my_mbar, bool elected,
+                                                unsigned round_bytes, float v0, float v1, float v2, float v3) {
+    if (ASYNC) {
+        // one thread per CTA and round announces the bytes its own CTA will receive in this buffer
+        if (elected)
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(my_mbar), "r"(round_bytes) : "memory");
+        asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];"
+                     ::"r"(dst), "f"(v0), "f"(v1), "f"(v2), "f"(v3), "r"(rmbar) : "memory");
+    } else {
+        st_cluster_v4(dst, v0, v1, v2, v3);
+    }
+}
+
+template <bool ASYNC>
 __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p) {
-    extern __shared__ __align__(16) float a0s[];  // [2][4][M] layer-0 values this CTA consumes
+    constexpr unsigned NB = ASYNC ? 4u : 2u;      // layer-0 buffers
+    extern __shared__ __align__(16) float a0s[];  // [NB][4][M] layer-0 values this CTA consumes
+    __shared__ __align__(8) unsigned long long s_mbar[4];
     __shared__ float2 s_t2[kLayers];   // (trans2[d], trans2[d])
     __shared__ int s_seq;
     __shared__ unsigned s_last;
@@ -204,6 +243,18 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
         dst0 = map_to_rank(a0_base + 4u * (dj * M + rem % M), rem / M);
     }
     const unsigned buf_bytes = 16u * M;
+    const unsigned mbar0 = smem_u32(&s_mbar[0]);
+    unsigned rmbar0 = 0;            // mbarrier 0 of the CTA that consumes my layer 0
+    unsigned phase = 0;             // bit b: parity to wait for on mbarrier b
+    bool dead = false;
+    if (ASYNC) {
+        rmbar0 = map_to_rank(smem_u32(&s_mbar[0]), (unsigned)((g % Kq) / M));
+        if (tid == 0) {
+            for (int b = 0; b < 4; ++b)
+                asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&s_mbar[b])));
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+    }
     const unsigned seq_addr = smem_u32(&s_seq);
     const unsigned last_addr = smem_u32(&s_last);
     const unsigned clv_addr = smem_u32(s_cl_v);
@@ -253,9 +304,9 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
                     for (int c = 0; c < 4; ++c)
                         chi[d][c] = (unsigned)(d * K + g + c) == last ? e[c] : -INFINITY;
             }
-            unsigned buf = 0;
-            st_cluster_v4(dst0, chi[0][0], chi[0][1], chi[0][2], chi[0][3]);
-            arrive();
+            unsigned buf = 0;   // buffer that holds the previous step's layer 0
+            vit_send_layer0<ASYNC>(dst0, rmbar0, mbar0, tid == 0, 16u * M, chi[0][0], chi[0][1], chi[0][2], chi[0][3]);
+            if (!ASYNC) arrive();
 
             float best_v = -INFINITY;
             unsigned best_i = 0;
@@ -292,9 +343,13 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
                 wait();
             };
             if (karg == 0) {
-                wait();
-                cluster_argmax();
-                arrive();
+                if (ASYNC) {
+                    cluster_argmax();
+                } else {
+                    wait();
+                    cluster_argmax();
+                    arrive();
+                }
             }
 
             // ---- forward steps with back pointers (hmm.cu:116-176, 378-412) ----------------
@@ -303,10 +358,18 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
                     const float4 v = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)obs[t + k] * K + g));
                     e[0] = v.x; e[1] = v.y; e[2] = v.z; e[3] = v.w;
                 }
-                wait();
-                const float *seg = a0s + (buf ? 4 * M : 0) + tid;
+                if (ASYNC) {
+                    if (!dead && !vit_mbar_wait(mbar0 + 8u * buf, (phase >> buf) & 1u)) {
+                        dead = true;
+                        atomicOr(&g_vit_status, 1u);
+                    }
+                    phase ^= 1u << buf;
+                } else {
+                    wait();
+                }
+                const float *seg = a0s + buf * 4 * M + tid;
                 const float2 a[4] = {vdup2(seg[0]), vdup2(seg[M]), vdup2(seg[2 * M]), vdup2(seg[3 * M])};
-                const unsigned dst = dst0 + (buf ? 0u : buf_bytes);
+                const unsigned nbuf = (buf + 1u) % NB;   // where this step's layer 0 goes
                 unsigned words[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) words[i] = 0u;
@@ -391,21 +454,34 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
                 // layer 0 of both pairs first: it is what the other CTAs wait for
                 layers(0, 0, 1);
                 layers(1, 0, 1);
-                st_cluster_v4(dst, chi[0][0], chi[0][1], chi[0][2], chi[0][3]);
-                arrive();
+                vit_send_layer0<ASYNC>(dst0 + nbuf * buf_bytes, rmbar0 + 8u * nbuf, mbar0 + 8u * nbuf, tid == 0, 16u * M,
+                                       chi[0][0], chi[0][1], chi[0][2], chi[0][3]);
+                if (!ASYNC) arrive();
                 layers(0, 1, kLayers);
                 layers(1, 1, kLayers);
                 uint4 *slot = codes + ((long long)(k - 1) * Kq + gthread) * 2;
                 __stcg(slot, make_uint4(words[0], words[1], words[2], words[3]));
                 __stcg(slot + 1, make_uint4(words[4], words[5], words[6], words[7]));
-                buf ^= 1u;
+                buf = nbuf;
                 if (k == karg && k < L - 1) {   // full window: arg-max one step before the end
-                    wait();
-                    cluster_argmax();
-                    arrive();
+                    if (ASYNC) {
+                        cluster_argmax();
+                    } else {
+                        wait();
+                        cluster_argmax();
+                        arrive();
+                    }
                 }
             }
-            wait();
+            if (ASYNC) {   // the last round is not used, but it must have landed
+                if (!dead && !vit_mbar_wait(mbar0 + 8u * buf, (phase >> buf) & 1u)) {
+                    dead = true;
+                    atomicOr(&g_vit_status, 1u);
+                }
+                phase ^= 1u << buf;
+            } else {
+                wait();
+            }
             if (karg == L - 1 && karg > 0) cluster_argmax();
 
             // ---- backward pass (hmm.cu:436-508) -----------------------------------------------
@@ -522,9 +598,14 @@ extern "C" int32_t parpy_b200_viterbi(float gamma, const float *initial_prob, in
     if (rc) return rc;
     PB_REQUIRE(dev.cc_major >= 10, "viterbi: needs compute capability 10.x, found %d.%d", dev.cc_major, dev.cc_minor);
 
-    const size_t smem = size_t(2) * 4 * pl.nt * sizeof(float);
-    if (pl.cs > 8) PB_CUDA(cudaFuncSetAttribute(hmm_viterbi_resident, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
-    PB_CUDA(cudaFuncSetAttribute(hmm_viterbi_resident, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    // layer 0 by st.async + mbarriers in clusters of 2 to 8 CTAs (7mer: 30.0 against 36.4 ms)
+    bool async_x = true;
+    if (const char *env = getenv("PARPY_B200_VIT_ASYNC")) async_x = atoi(env) != 0;
+    async_x = async_x && pl.cs >= 2 && pl.cs <= 8;
+    void (*kernel)(const VitParams) = async_x ? hmm_viterbi_resident<true> : hmm_viterbi_resident<false>;
+    const size_t smem = size_t(async_x ? 4 : 2) * 4 * pl.nt * sizeof(float);
+    if (pl.cs > 8) PB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    PB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cudaLaunchAttribute attr[1];
@@ -539,7 +620,7 @@ extern "C" int32_t parpy_b200_viterbi(float gamma, const float *initial_prob, in
     cfg.numAttrs = 1;
     cfg.stream = stream;
     int max_clusters = 0;
-    PB_CUDA(cudaOccupancyMaxActiveClusters(&max_clusters, hmm_viterbi_resident, &cfg));
+    PB_CUDA(cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg));
     PB_REQUIRE(max_clusters >= 1, "viterbi: no cluster of %d CTAs x %d threads fits this device", pl.cs, pl.nt);
 
     // back-pointer nibbles: (batch - 1) steps x K/4 threads x 32 bytes per resident cluster,
@@ -578,6 +659,6 @@ extern "C" int32_t parpy_b200_viterbi(float gamma, const float *initial_prob, in
     vit_schedule<<<1, 1024, sched_smem, stream>>>(lens, p.B, const_cast<int *>(p.order), p.counter);
     PB_CUDA(cudaGetLastError());
     cfg.gridDim = dim3(pl.cs * (unsigned)clusters, 1, 1);
-    PB_CUDA(cudaLaunchKernelEx(&cfg, hmm_viterbi_resident, p));
+    PB_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
     return PB_OK;
 }

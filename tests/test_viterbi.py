@@ -165,6 +165,25 @@ def test_kernel_matches_oracle_when_candidates_nearly_tie(noise):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("k,nseq,lo,hi", [(7, 40, 600, 2600), (6, 150, 300, 1500)])
+def test_layer0_exchange_variants_agree_at_scale(monkeypatch, k, nseq, lo, hi):
+    # Clusters of 2 to 8 CTAs pass layer 0 either with st.shared::cluster + barrier.cluster or with
+    # st.async + mbarriers over four buffers. More sequences than resident clusters, ragged lengths,
+    # several windows each; the decoded paths of the two must be identical, run after run.
+    from parpy_b200 import hmm as hmm_mod
+    hmm = synthetic.hmm_model(k, seed=50 + k)
+    seqs = synthetic.hmm_sequences(nseq, lo, hi, seed=60 + k)
+    dh, ds = _dev(hmm), _dev(seqs)
+    monkeypatch.setenv("PARPY_B200_VIT_ASYNC", "0")
+    ref = hmm_mod.viterbi_paths(dh, ds)
+    monkeypatch.setenv("PARPY_B200_VIT_ASYNC", "1")
+    for rep in range(3):
+        got = hmm_mod.viterbi_paths(dh, ds)
+        for i, (a, b) in enumerate(zip(got, ref)):
+            assert np.array_equal(a, b), (rep, i, int(np.argmax(a != b)))
+
+
+@pytest.mark.gpu
 def test_viterbi_argument_checks(native):
     from parpy_b200 import hmm as hmm_mod
     hmm, seqs = _dev(synthetic.hmm_model(3)), _dev(synthetic.hmm_sequences(2, 5, 9))
