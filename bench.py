@@ -1,12 +1,15 @@
 #!/usr/bin/env python
-"""Benchmark of the hot path: 7-mer HMM forward, 500 ragged sequences per GPU.
+"""Benchmark of the hot path: 7-mer HMM forward over a batch of 500 ragged
+sequences (lengths uniform in [1000, 4000]).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
 One "step" is one forward pass over the whole batch (all sequences, all time
-steps). Prints ONE JSON line on rank 0. Under torchrun every rank drives its own
-GPU on its own shard; the only collective is the final all-gather of the
-per-sequence log-likelihoods, inside the timed step.
+steps). Prints ONE JSON line on rank 0. Under torchrun the batch is sharded by
+sequence over the ranks (strong scaling, the default; `weak` in the line is the
+same kernel with a full batch per GPU); every rank drives its own GPU and the
+only collective is the final all-gather of the per-sequence log-likelihoods,
+inside the timed step.
 
   value     state-steps/s, whole job, inputs resident in HBM (device-timed)
   e2e       the same metric through the Python call surface with pinned HOST
@@ -18,6 +21,11 @@ per-sequence log-likelihoods, inside the timed step.
   cpu_baseline / --impl reference
             the CPU restatement of the reference algorithm (oracle/) on the
             host cores, on a bounded sample of the same workload
+  schedule  how evenly rank 0's sequences pack onto its resident clusters
+  variants  the opt-in scaled kernel on the same batch (N = 1)
+  surrounding
+            softmax, sum+max, CSR SpMV and SDDMM on their benchmark shapes, once
+            each after the timed region (N = 1; see bench_kernels.py)
 """
 import argparse
 import json
@@ -48,12 +56,16 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak",
-                    help="weak: 500 sequences per GPU; strong: 500 sequences sharded over the GPUs")
+    ap.add_argument("--scaling", choices=["weak", "strong"], default="strong",
+                    help="strong (default): the 500-sequence batch sharded over the GPUs; "
+                         "weak: 500 sequences per GPU")
     ap.add_argument("--variant", choices=["auto", "five_term", "scaled", "streaming"], default="auto")
     ap.add_argument("--ref-cuda", action="store_true",
                     help="also time the reference's own CUDA implementation (oracle/_ref), once")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-surrounding", action="store_true",
+                    help="skip the surrounding kernels (softmax, sum+max, SpMV, SDDMM) after the timed region")
+    ap.add_argument("--no-variants", action="store_true", help="skip the opt-in scaled kernel")
     ap.add_argument("--batch", type=int, default=BATCH, help=argparse.SUPPRESS)
     ap.add_argument("--kmer", type=int, default=KMER, help=argparse.SUPPRESS)
     ap.add_argument("--min-len", type=int, default=MIN_LEN, help=argparse.SUPPRESS)
@@ -76,6 +88,7 @@ def workload_config(args, world):
         "num_states": 16 * 4 ** args.kmer,
         "batch_per_gpu": args.batch if args.scaling == "weak" else None,
         "global_batch": args.batch * (world if args.scaling == "weak" else 1),
+        "seed": SEED,
         "seq_len": f"uniform[{args.min_len},{args.max_len}]",
         "obs_levels": 101,
         "parallelism": f"sequence-sharded x{world}",
@@ -99,6 +112,15 @@ def cpu_sample(hmm, seqs, cores):
     return sub, desc
 
 
+def host_cores():
+    """Host threads this process may use: the CPU affinity mask, not OMP_NUM_THREADS
+    (launchers such as torchrun set that to 1 for every rank)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def time_cpu_once(hmm, sub, cores):
     from oracle import oracle
     t0 = time.perf_counter()
@@ -113,7 +135,7 @@ def run_reference_arm(args, rank, world):
         return
     from oracle import oracle
     from parpy_b200 import synthetic
-    cores = oracle.max_threads()
+    cores = host_cores()
     hmm = synthetic.hmm_model(args.kmer, seed=SEED)
     seqs = synthetic.hmm_sequences(args.batch, args.min_len, args.max_len, seed=SEED)
     sub, desc = cpu_sample(hmm, seqs, cores)
@@ -125,13 +147,12 @@ def run_reference_arm(args, rank, world):
         times.append(dt)
     total = sum(times)
     value = work * args.steps / total
-    cfg = workload_config(args, 1)
-    cfg["cache"] = "n/a (CPU)"
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": cfg,
+        "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": workload_config(args, max(world, args.gpus)),
+        "ran_on": "host CPU cores of rank 0 (no GPU, no L2 flush); each step scores the sample below",
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -214,6 +235,7 @@ def main():
         run_reference_arm(args, rank, world)
         return
 
+    import ctypes
     import torch
     import torch.distributed as td
     import parpy_b200 as parpy
@@ -224,155 +246,207 @@ def main():
     if args.gpus > 1 and world == 1:
         raise SystemExit("launch multi-GPU runs with torchrun (one process per GPU)")
     torch.cuda.set_device(local_rank)
-    _native.lib()  # fail loudly if the CUDA library is missing
+    lib = _native.lib()  # fail loudly if the CUDA library is missing
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         td.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
-    # ---- inputs: identical tables on every rank, per-rank sequences -------------------
+    # ---- inputs: identical tables on every rank ----------------------------------------
     hmm = synthetic.hmm_model(args.kmer, seed=SEED)
-    if args.scaling == "weak":
-        # same lengths on every rank (equal work per GPU), rank-specific observations
-        seqs = synthetic.hmm_sequences(args.batch, args.min_len, args.max_len, seed=SEED,
-                                       data_seed=None if rank == 0 else SEED + 17 * rank)
-        global_lens = None
-    else:
-        all_seqs = synthetic.hmm_sequences(args.batch, args.min_len, args.max_len, seed=SEED)
-        global_lens = all_seqs["lens"].numpy()
-        seqs, _ = dist.shard_sequences(all_seqs, rank, world)
-    local_work = synthetic.state_steps(hmm, seqs)
-    local_bytes = synthetic.forward_algorithmic_bytes(hmm, seqs)
-    batch = int(seqs["num_instances"])
+    n_states = int(hmm["num_states"])
+    # resident clusters of the forward kernel on this GPU (its persistent work queue has that many takers)
+    clusters = ctypes.c_int32(0)
+    _native.check(lib.parpy_b200_forward_plan(n_states, args.batch, None, None, None, ctypes.byref(clusters)),
+                  "forward_plan")
+    clusters = int(clusters.value)
+    all_seqs = synthetic.hmm_sequences(args.batch, args.min_len, args.max_len, seed=SEED)
+    global_lens = all_seqs["lens"].numpy()
+
+    def inputs_for(scaling):
+        """(local sequences, partition or None): strong = the one batch sharded over the ranks;
+        weak = a batch of that size per rank (same lengths, rank-specific observations)."""
+        if scaling == "strong":
+            if world == 1:
+                return all_seqs, None
+            parts = dist.partition(global_lens, world, clusters)
+            local, _ = dist.shard_sequences(all_seqs, rank, world, clusters)
+            return local, parts
+        local = synthetic.hmm_sequences(args.batch, args.min_len, args.max_len, seed=SEED,
+                                        data_seed=None if rank == 0 else SEED + 17 * rank)
+        return local, None
 
     dev_hmm = hmm_mod.to_device(hmm)
-    dev_seqs = hmm_mod.to_device(seqs)
-    opts = parpy.par({"inst": parpy.threads(batch)})
-    if args.variant != "auto":
-        opts.b200 = {"forward": args.variant}
-    alpha = None
-    if args.variant == "streaming":
-        n = int(hmm["num_states"])
-        alpha = (torch.zeros(batch, n, device="cuda"), torch.zeros(batch, n, device="cuda"))
-    result = torch.zeros(batch, dtype=torch.float32, device="cuda")
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device="cuda")
-    gather_buf = [torch.empty_like(result) for _ in range(world)] if world > 1 and args.scaling == "weak" else None
-
-    def step_device():
-        a1, a2 = alpha if alpha is not None else (None, None)
-        hmm_mod.forward_kernel(dev_hmm, dev_seqs, result, a1, a2, opts=opts)
-        if world > 1:
-            if args.scaling == "weak":
-                td.all_gather(gather_buf, result)
-            else:
-                dist.gather_results(result, global_lens)
 
     def barrier():
         if world > 1:
             td.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 0)):
-        step_device()
-    barrier()
+    def measure(scaling, variant, with_e2e):
+        """Times `steps` forward passes of this rank's share (device-resident inputs, then host
+        inputs through the Python call). Returns a dict of this rank's figures."""
+        seqs, parts = inputs_for(scaling)
+        batch = int(seqs["num_instances"])
+        dev_seqs = hmm_mod.to_device(seqs)
+        opts = parpy.par({"inst": parpy.threads(max(batch, 1))})
+        if variant != "auto":
+            opts.b200 = {"forward": variant}
+        alpha = None
+        if variant == "streaming":
+            alpha = (torch.zeros(batch, n_states, device="cuda"), torch.zeros(batch, n_states, device="cuda"))
+        a1, a2 = alpha if alpha is not None else (None, None)
+        result = torch.zeros(batch, dtype=torch.float32, device="cuda")
+        gather_buf = [torch.empty_like(result) for _ in range(world)] if world > 1 and scaling == "weak" else None
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    events = []
-    barrier()
-    for _ in range(args.steps):
-        flush.fill_(1)                      # evict L2 between timed steps (untimed)
-        e0 = torch.cuda.Event(enable_timing=True)
-        e1 = torch.cuda.Event(enable_timing=True)
-        e0.record()
-        step_device()
-        e1.record()
-        events.append((e0, e1))
-    barrier()
-    step_ms = [a.elapsed_time(b) for a, b in events]
-    total_ms = sum(step_ms)
-    clocks = sampler.stop() if rank == 0 else None
+        def gather(local_result):
+            if world == 1:
+                return
+            if scaling == "weak":
+                td.all_gather(gather_buf, local_result)
+            else:
+                dist.gather_results(local_result, global_lens, parts=parts)
 
-    # ---- end to end: pinned host arrays through the public call ----------------------
-    pin_hmm = {k: (v.pin_memory() if isinstance(v, torch.Tensor) and v.dim() > 0 else v) for k, v in hmm.items()}
-    pin_seqs = {k: (v.pin_memory() if isinstance(v, torch.Tensor) and v.dim() > 0 else v) for k, v in seqs.items()}
-    host_result = torch.zeros(batch, dtype=torch.float32).pin_memory()
-    h2d = sum(v.numel() * v.element_size() for d in (pin_hmm, pin_seqs) for v in d.values()
-              if isinstance(v, torch.Tensor) and v.dim() > 0)
-    d2h = host_result.numel() * 4
+        def step_device():
+            hmm_mod.forward_kernel(dev_hmm, dev_seqs, result, a1, a2, opts=opts)
+            gather(result)
 
-    def step_e2e():
-        a1, a2 = alpha if alpha is not None else (None, None)   # streaming variant: device scratch
-        hmm_mod.forward_kernel(pin_hmm, pin_seqs, host_result, a1, a2, opts=opts)
-        if world > 1 and args.scaling == "weak":
-            td.all_gather(gather_buf, host_result.cuda(non_blocking=True))
+        for _ in range(max(args.warmup, 0)):
+            step_device()
+        barrier()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        events = []
+        barrier()
+        for _ in range(args.steps):
+            flush.fill_(1)                      # evict L2 between timed steps (untimed)
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+            step_device()
+            e1.record()
+            events.append((e0, e1))
+        barrier()
+        step_ms = [a.elapsed_time(b) for a, b in events]
+        out = {"step_ms": step_ms, "total_ms": sum(step_ms), "clocks": sampler.stop() if rank == 0 else None,
+               "work": synthetic.state_steps(hmm, seqs), "bytes": synthetic.forward_algorithmic_bytes(hmm, seqs),
+               "batch": batch, "result": result, "seqs": seqs, "e2e_s": 0.0, "h2d": 0, "d2h": 0}
+        if not with_e2e:
+            return out
 
-    for _ in range(min(args.warmup, 2)):
-        step_e2e()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        step_e2e()
-    barrier()
-    e2e_s = time.perf_counter() - t0
-    assert torch.equal(host_result.cuda(), result), "end-to-end result differs from the device-resident run"
+        # ---- end to end: pinned host arrays through the public call ----------------------
+        pin = lambda d: {k: (v.pin_memory() if isinstance(v, torch.Tensor) and v.dim() > 0 else v) for k, v in d.items()}
+        pin_hmm, pin_seqs = pin(hmm), pin(seqs)
+        host_result = torch.zeros(batch, dtype=torch.float32).pin_memory()
+        out["h2d"] = sum(v.numel() * v.element_size() for d in (pin_hmm, pin_seqs) for v in d.values()
+                         if isinstance(v, torch.Tensor) and v.dim() > 0)
+        out["d2h"] = host_result.numel() * 4
 
-    # ---- reduce over ranks: max time, summed work ---------------------------------------
-    stats = torch.tensor([total_ms, e2e_s, float(local_work), float(local_bytes)], dtype=torch.float64, device="cuda")
-    if world > 1:
-        mx = stats.clone()
-        td.all_reduce(mx, op=td.ReduceOp.MAX)
-        sm = stats.clone()
-        td.all_reduce(sm, op=td.ReduceOp.SUM)
-        total_ms, e2e_s = float(mx[0]), float(mx[1])
-        work, nbytes = float(sm[2]), float(sm[3])
-    else:
-        work, nbytes = float(local_work), float(local_bytes)
+        def step_e2e():
+            hmm_mod.forward_kernel(pin_hmm, pin_seqs, host_result, a1, a2, opts=opts)
+            if world > 1:
+                gather(host_result.cuda(non_blocking=True))
+
+        for _ in range(min(args.warmup, 2)):
+            step_e2e()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            step_e2e()
+        barrier()
+        out["e2e_s"] = time.perf_counter() - t0
+        assert torch.equal(host_result.cuda(), result), "end-to-end result differs from the device-resident run"
+        return out
+
+    def reduce_ranks(m):
+        """Max time over ranks, work summed over ranks."""
+        stats = torch.tensor([m["total_ms"], m["e2e_s"], float(m["work"]), float(m["bytes"])],
+                             dtype=torch.float64, device="cuda")
+        if world > 1:
+            mx, sm = stats.clone(), stats.clone()
+            td.all_reduce(mx, op=td.ReduceOp.MAX)
+            td.all_reduce(sm, op=td.ReduceOp.SUM)
+            return float(mx[0]), float(mx[1]), float(sm[2]), float(sm[3])
+        return m["total_ms"], m["e2e_s"], float(m["work"]), float(m["bytes"])
+
+    head = measure(args.scaling, args.variant, with_e2e=True)
+    total_ms, e2e_s, work, nbytes = reduce_ranks(head)
+    weak = None
+    if world > 1 and args.scaling == "strong":
+        # the same kernel with a full batch on every GPU, as an extra figure
+        wm = measure("weak", args.variant, with_e2e=False)
+        w_ms, _, w_work, _ = reduce_ranks(wm)
+        weak = {"value": w_work * args.steps / (w_ms * 1e-3), "ms_per_step": w_ms / args.steps,
+                "global_batch": args.batch * world}
 
     if rank == 0:
         peak, peak_kind = measured_peak()
         value = work * args.steps / (total_ms * 1e-3)
         # dominant kernel: the resident forward kernel, one launch per step per rank;
         # the step also holds a one-CTA scheduling prologue of a few microseconds
-        launch_s = statistics.mean(step_ms) * 1e-3
-        achieved = local_bytes / launch_s / 1e9
+        launch_s = statistics.mean(head["step_ms"]) * 1e-3
+        achieved = head["bytes"] / launch_s / 1e9
+        lens_local = head["seqs"]["lens"].numpy()
+        mx, mean = dist.cluster_balance(lens_local, clusters)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
             "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": workload_config(args, world),
             "e2e": {"value": work * args.steps / e2e_s, "unit": UNIT,
-                    "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
+                    "h2d_bytes_per_step": int(head["h2d"]), "d2h_bytes_per_step": int(head["d2h"])},
             "gpu_launches": 2 * args.steps * world,
-            "clocks": clocks,
+            "clocks": head["clocks"],
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": ncu_traffic_bytes(args, h2d),
+                         "frac": achieved / peak, "traffic": ncu_traffic_bytes(args, head["h2d"]),
                          "peak_source": peak_kind,
                          "note": "algorithmic bytes (8.25 B/state-step) per launch over the measured "
                                  "launch duration; alpha stays on chip, so DRAM traffic is far lower"},
-            "step_ms": step_ms,
+            "step_ms": head["step_ms"],
+            # rank 0's share on its persistent clusters: the launch lasts as long as the busiest
+            # cluster's step total, the work done is the mean
+            "schedule": {"resident_clusters": clusters, "sequences_rank0": head["batch"],
+                         "busiest_cluster_steps": mx, "mean_cluster_steps": mean,
+                         "balance": mean / mx if mx else None},
         }
+        if weak is not None:
+            line["weak"] = weak
+        if world == 1 and args.variant == "auto" and not args.no_variants:
+            sc = measure("strong", "scaled", with_e2e=False)
+            a, b = sc["result"].cpu().numpy(), head["result"].cpu().numpy()
+            line["variants"] = {"scaled": {
+                "value": sc["work"] * args.steps / (sc["total_ms"] * 1e-3), "ms_per_step": sc["total_ms"] / args.steps,
+                "max_rel_vs_default": float(abs((a - b) / b).max()),
+                "what": "opt-in linear-domain kernel (opts.b200['forward'] = 'scaled'), same batch"}}
         if world == 1 and not args.no_cpu_baseline:
-            from oracle import oracle
-            cores = oracle.max_threads()
-            sub, desc = cpu_sample(hmm, seqs, cores)
+            cores = host_cores()
+            sub, desc = cpu_sample(hmm, all_seqs, cores)
             w, dt = time_cpu_once(hmm, sub, cores)
             line["cpu_baseline"] = {"value": w / dt, "unit": UNIT, "cores": cores, "kind": "port",
                                     "sample": desc}
         if args.ref_cuda and world == 1:
-            line["reference_cuda"] = time_reference_cuda(args, hmm, seqs, result, local_work)
+            line["reference_cuda"] = time_reference_cuda(args, hmm, all_seqs, head["result"], head["work"])
+        if world == 1 and not args.no_surrounding:
+            del head, flush
+            torch.cuda.empty_cache()
+            try:
+                import bench_kernels
+                line["surrounding"] = bench_kernels.surrounding()
+            except Exception as exc:            # the headline figures above stand on their own
+                line["surrounding"] = {"unavailable": str(exc)[:200]}
         print(json.dumps(line), flush=True)
     if world > 1:
         td.barrier()
         td.destroy_process_group()
 
 
-# One ncu capture of hmm_forward_resident<4,false> (60 sequences of 200-400 steps,
-# profiles/hmm_forward_resident_7mer_ncu.md) measured dram__bytes_read.sum =
-# 7,988,480 B and dram__bytes_write.sum = 0 B for 7,954,340 B of inputs (tables +
-# observations + lengths): the kernel reads its inputs from DRAM once and keeps
-# alpha on chip, so DRAM traffic follows the input size, not the step count.
-NCU_DRAM_BYTES_PER_INPUT_BYTE = 7988480.0 / 7954340.0
+# One ncu capture of hmm_forward_packed<0x5554> (66 sequences of 200-400 steps, --set full,
+# summary under profiles/) measured dram__bytes_read.sum = 7,994,000 B and
+# dram__bytes_write.sum = 0 B for 7,956,782 B of inputs (tables + observations + lengths): the
+# kernel reads its inputs from DRAM once and keeps alpha on chip, so DRAM traffic follows the
+# input size, not the step count.
+NCU_DRAM_BYTES_PER_INPUT_BYTE = 7994000.0 / 7956782.0
 
 
 def ncu_traffic_bytes(args, input_bytes):

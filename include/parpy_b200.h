@@ -19,10 +19,8 @@
  *      NULL = legacy default stream) and option flags.
  *
  * Concurrency: entry points may be called from several host threads and on
- * several streams. Library-owned scratch is kept per (device, stream). The
- * forward kernels read 16 per-call constants from one of 16 constant-memory
- * slots handed out round-robin: more than 16 forward calls in flight at once on
- * different streams of one device would share a slot.
+ * several streams. Library-owned scratch is kept per (device, stream); calls on
+ * one stream use it one after another in stream order.
  */
 #ifndef PARPY_B200_H
 #define PARPY_B200_H
@@ -113,6 +111,20 @@ int32_t parpy_b200_forward(float gamma, const float *initial_prob, int64_t num_s
                            int64_t num_instances, float *result, float *alpha1,
                            float *alpha2, uint32_t flags, void *stream);
 
+/* parpy_b200_forward with the number of rows of output_prob (n_obs, 1..256) given,
+ * so that observation bytes can be checked: a byte >= n_obs inside a sequence is
+ * read as n_obs - 1 instead of indexing past the table, and bit 1 of the status
+ * word (parpy_b200_forward_status) is raised. The reference's generated entry has
+ * no such check and no n_obs parameter (an out-of-range byte reads out of bounds
+ * there); forward_kernel and parpy_b200_forward keep that signature and accept
+ * any byte value the caller guarantees to be valid. n_obs = 0: no check. */
+int32_t parpy_b200_forward_ex(float gamma, const float *initial_prob, int64_t num_states,
+                              const float *output_prob, int64_t n_obs, float synthetic_248,
+                              const float *trans1, const float *trans2, const void *data,
+                              const int64_t *lens, int64_t maxlen, int64_t num_instances,
+                              float *result, float *alpha1, float *alpha2, uint32_t flags,
+                              void *stream);
+
 /* Describes the launch parpy_b200_forward would use for a state space on the
  * current device (host pointers; any may be NULL): kmers per thread, threads
  * per CTA, CTAs per cluster and resident clusters. Returns non-zero when only
@@ -121,9 +133,19 @@ int32_t parpy_b200_forward_plan(int64_t num_states, int64_t num_instances, int32
                                 int32_t *threads_per_cta, int32_t *ctas_per_cluster,
                                 int32_t *clusters);
 
+/* The static schedule parpy_b200_forward builds for a batch of up to 4096
+ * sequences on `clusters` (1..512) resident clusters: cluster_of[i] (device,
+ * int32 [num_instances]) receives the cluster that scores sequence i. lens is
+ * the device array the forward entry takes. Sequences are packed longest first
+ * into the least loaded cluster, then the fullest cluster is repaired by single
+ * exchanges, so the per-cluster sums of lengths (what a launch's duration
+ * follows) differ by far less than one sequence. For inspection and tests. */
+int32_t parpy_b200_forward_schedule(const int64_t *lens, int64_t num_instances, int64_t clusters,
+                                    int32_t *cluster_of, void *stream);
+
 /* Reads and clears the device status word of the current device (host call,
  * synchronises the device). Bit 0: a sequence length outside [1, maxlen] was
- * clamped. */
+ * clamped. Bit 1: an observation byte >= n_obs was clamped (parpy_b200_forward_ex). */
 int32_t parpy_b200_forward_status(uint32_t *status);
 
 /* Forward pass for callers that must not trigger a device allocation.
@@ -140,7 +162,7 @@ int32_t parpy_b200_forward_status(uint32_t *status);
  * the same result[] (resident kernel, factored log-sum-exp, alpha kept on chip)
  * with its scheduling scratch — the length-sorted sequence order and the work-
  * queue head — in a fixed device array compiled into the library, of
- * 4 * PARPY_B200_NOALLOC_MAX_SEQUENCES + 256 bytes on every GPU that loads the
+ * 4 * PARPY_B200_NOALLOC_MAX_SEQUENCES + 2560 bytes on every GPU that loads the
  * library, held until the process exits.
  *
  * Limits and rules:
@@ -152,6 +174,8 @@ int32_t parpy_b200_forward_status(uint32_t *status);
  *  - The first call on each device looks up the array's device address (one
  *    cudaGetSymbolAddress, with that device current). Make that first call
  *    before any stream capture is begun on the device.
+ *  - (The array also holds a 2.5 KB table with each resident cluster's part of
+ *    the schedule.)
  *  - All calls on a device share the one array, and it keeps the previous
  *    call's contents; each call rewrites the part it uses before reading it.
  *    Two calls whose kernels overlap on the GPU (different streams) race on it:
@@ -260,6 +284,27 @@ int32_t parpy_b200_viterbi(float gamma, const float *initial_prob, int64_t num_s
                            const float *trans2, const void *data, const int64_t *lens, int64_t maxlen,
                            int64_t num_instances, int64_t batch_size, int64_t batch_overlap,
                            uint32_t *out, int64_t out_stride, void *stream);
+/* Same, with the number of rows of output_prob given (1..256; 0: no check): an
+ * observation byte >= n_obs inside a sequence is read as n_obs - 1 and bit 1 of
+ * the Viterbi status word is raised (the reference's CUDA indexes past the table). */
+int32_t parpy_b200_viterbi_ex(float gamma, const float *initial_prob, int64_t num_states,
+                              const float *output_prob, int64_t n_obs, float synthetic_248,
+                              const float *trans1, const float *trans2, const void *data,
+                              const int64_t *lens, int64_t maxlen, int64_t num_instances,
+                              int64_t batch_size, int64_t batch_overlap, uint32_t *out, int64_t out_stride,
+                              void *stream);
+/* Reads and clears the Viterbi status word of the current device (host call,
+ * synchronises the device). Bit 0: a bounded wait for another CTA's layer-0
+ * values ran out, so the paths written by the calls since the last read are not
+ * valid. Bit 1: an observation byte >= n_obs was clamped. No counterpart in the
+ * reference, whose kernels cannot time out (one launch per step). */
+int32_t parpy_b200_viterbi_status(uint32_t *status);
+/* Launches one 32-thread CTA that waits, with the decoding kernel's bounded
+ * wait, on a barrier nothing completes; after `polls` (0..2^20) polls it gives up
+ * and raises bit 0 of the Viterbi status word. Touches no caller data. Lets a
+ * caller (or a test) see the give-up path reach parpy_b200_viterbi_status
+ * without any kernel being starved. */
+int32_t parpy_b200_viterbi_wait_probe(int32_t polls, void *stream);
 
 #ifdef __cplusplus
 }

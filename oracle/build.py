@@ -23,6 +23,16 @@ REF_DIR = os.path.join(HERE, "_ref")
 C_SOURCES = ["hmm_oracle.c", "kernels_oracle.c", "viterbi_oracle.c"]
 
 
+def reference_root():
+    """Where the reference checkout lies: ``$PARPY_REFERENCE_ROOT``, else a
+    directory named ``reference`` beside this repository. None when absent."""
+    env = os.environ.get("PARPY_REFERENCE_ROOT")
+    if env:
+        return env if os.path.isdir(env) else None
+    sibling = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    return sibling if os.path.isdir(os.path.join(sibling, "benchmarks")) else None
+
+
 def _run(cmd):
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
@@ -63,5 +73,5 @@ def build_reference(ref_root, force=False):
 
 if __name__ == "__main__":
     print(build_oracle(force=True))
-    for f in build_reference(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", force=True):
+    for f in build_reference(sys.argv[1] if len(sys.argv) > 1 else reference_root(), force=True):
         print(f)

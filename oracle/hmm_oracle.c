@@ -36,12 +36,17 @@ static inline float f32_max(float a, float b) {
     return fmaxf(a, b);
 }
 
-/* One time step for one sequence; forward.py:112-158 for every state. */
+/* One time step for one sequence; forward.py:112-158 for every state. States
+ * of a step do not depend on one another, so `split_states` may hand them to
+ * several threads (used when a batch has fewer sequences than threads); the
+ * values do not depend on the split. */
 static void step_states(float gamma, int64_t N, const float *output_row,
                         float synthetic_248, const float *trans1,
-                        const float *trans2, const float *src, float *dst) {
+                        const float *trans2, const float *src, float *dst,
+                        int split_states) {
     const int64_t K = N / ORACLE_LAYERS;  /* num_kmers, forward.py:115 */
     const int64_t Q = N / 64;             /* num_states // 64, forward.py:117 */
+#pragma omp parallel for schedule(static) if (split_states)
     for (int64_t state = 0; state < N; ++state) {
         const int64_t kmer = state % K;
         const int64_t layer = state / K;
@@ -108,7 +113,13 @@ int oracle_forward(float gamma, const float *initial_prob, int64_t num_states,
 #else
     (void)num_threads;
 #endif
-#pragma omp parallel for schedule(dynamic, 1)
+    /* Sequences are independent: one thread each. A batch with fewer sequences
+     * than threads splits the states of every step over the threads instead. */
+    int split_states = 0;
+#ifdef _OPENMP
+    split_states = num_instances < omp_get_max_threads() && N >= 4096;
+#endif
+#pragma omp parallel for schedule(dynamic, 1) if (!split_states)
     for (int64_t inst = 0; inst < num_instances; ++inst) {
         float *a1 = (float *)malloc(sizeof(float) * (size_t)N);
         float *a2 = (float *)malloc(sizeof(float) * (size_t)N);
@@ -130,7 +141,7 @@ int oracle_forward(float gamma, const float *initial_prob, int64_t num_states,
             const float *src = (t & 1) ? a1 : a2; /* forward.py:105-109 */
             float *dst = (t & 1) ? a2 : a1;
             step_states(gamma, N, output_prob + (int64_t)obs[t] * K,
-                        synthetic_248, trans1, trans2, src, dst);
+                        synthetic_248, trans1, trans2, src, dst, split_states);
         }
         /* forward.py:163-173 */
         const float *alpha = (len & 1) ? a1 : a2;

@@ -38,6 +38,9 @@ SIGNATURES = {
                                              c_ptr, c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_ptr]),
     "parpy_b200_forward": (c_i32, [c_f32, c_ptr, c_i64, c_ptr, c_f32, c_ptr, c_ptr, c_ptr, c_ptr,
                                    c_i64, c_i64, c_ptr, c_ptr, c_ptr, c_u32, c_ptr]),
+    "parpy_b200_forward_ex": (c_i32, [c_f32, c_ptr, c_i64, c_ptr, c_i64, c_f32, c_ptr, c_ptr, c_ptr, c_ptr,
+                                      c_i64, c_i64, c_ptr, c_ptr, c_ptr, c_u32, c_ptr]),
+    "parpy_b200_forward_schedule": (c_i32, [c_ptr, c_i64, c_i64, c_ptr, c_ptr]),
     "parpy_b200_forward_noalloc": (c_i32, [c_f32, c_ptr, c_i64, c_ptr, c_f32, c_ptr, c_ptr, c_ptr, c_ptr,
                                            c_i64, c_i64, c_ptr, c_ptr]),
     "parpy_b200_forward_plan": (c_i32, [c_i64, c_i64, c_ptr, c_ptr, c_ptr, c_ptr]),
@@ -64,6 +67,10 @@ SIGNATURES = {
     "parpy_b200_hmm_pad_signals": (c_i32, [c_ptr, c_ptr, c_i64, c_i64, c_ptr, c_ptr, c_ptr]),
     "parpy_b200_viterbi": (c_i32, [c_f32, c_ptr, c_i64, c_ptr, c_f32, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_i64,
                                    c_i64, c_i64, c_ptr, c_i64, c_ptr]),
+    "parpy_b200_viterbi_ex": (c_i32, [c_f32, c_ptr, c_i64, c_ptr, c_i64, c_f32, c_ptr, c_ptr, c_ptr, c_ptr, c_i64,
+                                      c_i64, c_i64, c_i64, c_ptr, c_i64, c_ptr]),
+    "parpy_b200_viterbi_status": (c_i32, [c_ptr]),
+    "parpy_b200_viterbi_wait_probe": (c_i32, [c_i32, c_ptr]),
 }
 
 REDUCE_SUM, REDUCE_PROD, REDUCE_MAX, REDUCE_MIN = 0, 1, 2, 3

@@ -21,7 +21,6 @@
 #include <cooperative_groups.h>
 
 #include <algorithm>
-#include <atomic>
 #include <mutex>
 
 #include "../../include/parpy_b200.h"
@@ -33,51 +32,61 @@ namespace {
 constexpr int kLayers = 16;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
-constexpr int kModelSlots = 16;
-constexpr int kSortLimit = 4096;  // sequences sorted by length up to this batch size
-
-// Per-call model scalars, read through the constant bank so that they cost no
-// registers: trans2[0..15], gamma, synthetic_248.
-struct ModelConsts {
-    float trans2[kLayers];
-};
-__constant__ ModelConsts c_model[kModelSlots];
-// exp(trans2[d]) for the scaled (linear-domain) kernel, same slot discipline.
-__constant__ ModelConsts c_model_lin[kModelSlots];
+constexpr int kSortLimit = 4096;  // batches up to this size get a static, balanced schedule
+constexpr int kMaxBins = 512;     // resident clusters a static schedule is built for
+constexpr int kSegInts = kMaxBins + 64;   // ints reserved for the per-cluster segment table
 
 // Device status word. Bit 0: a sequence length outside [1, maxlen] was clamped.
+// Bit 1: an observation >= n_obs inside a sequence was clamped to n_obs - 1.
 __device__ unsigned g_status;
 
 // Fixed scheduling scratch of parpy_b200_forward_noalloc: the sequence order
-// (one int per sequence) followed by the work-queue head. It is part of the
-// loaded module, so every GPU that loads the library holds these bytes until the
-// process exits. In host code this name is only a handle for the symbol, not a
-// device address; host code obtains the address with cudaGetSymbolAddress.
+// (one int per sequence), the work-queue head and the per-cluster segment table.
+// It is part of the loaded module, so every GPU that loads the library holds
+// these bytes until the process exits. In host code this name is only a handle
+// for the symbol, not a device address; host code obtains the address with
+// cudaGetSymbolAddress.
 constexpr int kNoAllocMaxSequences = PARPY_B200_NOALLOC_MAX_SEQUENCES;
 constexpr size_t kNoAllocOrderBytes = size_t(kNoAllocMaxSequences) * sizeof(int);
-static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocOrderBytes + 256];
+constexpr size_t kSchedTailBytes = 256 + size_t(kSegInts) * sizeof(int);   // queue head + segment table
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocOrderBytes + kSchedTailBytes];
 
 struct FwdParams {
     const float *initial_prob;  // [16*K]
     const float *output_prob;   // [n_obs, K]
     const float *trans1;        // [K, 4]
+    const float *trans2;        // [16]
     const uint8_t *data;        // [B, maxlen]
     const int64_t *lens;        // [B]
     float *result;              // [B]
     float *alpha1;              // optional [B, 16*K]
     float *alpha2;              // optional [B, 16*K]
-    const int *order;           // [B] sequence ids, longest first
-    int *counter;               // work-queue head
+    const int *order;           // [B] sequence ids: grouped by cluster (static schedule) or longest first
+    const int *seg;             // [clusters + 1] bounds of each cluster's part of `order`; NULL: work queue
+    int *counter;               // work-queue head (dynamic schedule only)
     long long maxlen;
     int B;
     int K;
-    int slot;                   // index into c_model
+    int obs_max;                // n_obs - 1: observations above it are clamped and flagged (255: unknown)
     int write_alpha;
     float gamma;
     float synthetic;
     float gamma_lin;            // exp(gamma), exp(synthetic_248): scaled kernel only
     float synthetic_lin;
 };
+
+// Observation byte t of a sequence, kept inside the emission table: a value past the
+// last row is clamped and flagged (by one thread per cluster).
+__device__ __forceinline__ int obs_at(const FwdParams &p, const uint8_t *obs, int t) {
+    int o = obs[t];
+    if (o > p.obs_max) {
+        unsigned r;
+        asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+        if (threadIdx.x == 0 && r == 0) atomicOr(&g_status, 2u);
+        o = p.obs_max;
+    }
+    return o;
+}
 
 // ---- log-sum-exp building blocks -------------------------------------------
 // exp and log are the fast intrinsics the reference's CUDA backend prints for
@@ -145,31 +154,252 @@ __device__ __forceinline__ float lse5_reference(float p1, float p2, float p3, fl
 }
 
 // ---- scheduling prologue ----------------------------------------------------
-// Orders sequences longest-first (rank by counting) so that the persistent
-// clusters pop long sequences first, and resets the work-queue head.
-__global__ void hmm_schedule(const int64_t *__restrict__ lens, int B, int *__restrict__ order,
-                             int *__restrict__ counter) {
-    extern __shared__ int s_len[];
-    const bool sort = B <= kSortLimit;
-    if (sort) {
-        for (int i = threadIdx.x; i < B; i += blockDim.x) {
-            long long l = lens[i];
-            s_len[i] = l > 0x7fffffffLL ? 0x7fffffff : (l < 0 ? 0 : static_cast<int>(l));
-        }
-        __syncthreads();
-        for (int i = threadIdx.x; i < B; i += blockDim.x) {
+// One CTA decides, before the forward kernel starts, which resident cluster scores
+// which sequences. A cluster's time is the sum of the lengths it is given and the
+// launch lasts as long as the busiest cluster, so the lengths are packed into C bins
+// of nearly equal sums: longest-first greedy packing (each sequence to the least
+// loaded bin), then repeated repair of the fullest bin by the best single exchange
+// (or move) of one of its sequences with another bin. Greedy packing alone, which is
+// also what a longest-first work queue produces, leaves the bins up to one shortest
+// sequence apart: 2 % of the run for 500 sequences of 1000..4000 steps on 33 clusters;
+// the repair brings that below 0.1 %. Output: `order` holds the sequence ids grouped
+// by bin (longest first inside a bin) and seg[c] .. seg[c+1] delimit bin c.
+// Batches above kSortLimit fall back to a work queue in input order (seg unused).
+__device__ __forceinline__ unsigned long long warp_min_u64(unsigned long long v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long w = __shfl_xor_sync(0xffffffffu, v, o);
+        v = w < v ? w : v;
+    }
+    return v;
+}
+
+__global__ void __launch_bounds__(1024, 1)
+hmm_schedule(const int64_t *__restrict__ lens, int B, int C, int *__restrict__ order,
+             int *__restrict__ counter, int *__restrict__ seg, int *__restrict__ cluster_of) {
+    extern __shared__ int s_dyn[];                       // [B] lengths by rank, then two u16 arrays
+    __shared__ long long s_load[kMaxBins];
+    __shared__ int s_cnt[kMaxBins + 1];
+    __shared__ unsigned short s_alist[256];
+    __shared__ unsigned long long s_red[32];
+    __shared__ int s_a, s_na, s_done;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) *counter = 0;
+    if (C <= 0) {   // no static schedule asked for: work queue in input order
+        for (int i = tid; i < B; i += blockDim.x) order[i] = i;
+        return;
+    }
+    int *s_len = s_dyn;                                                          // length of the item of rank r
+    unsigned short *s_id = reinterpret_cast<unsigned short *>(s_dyn + B);        // its sequence id
+    unsigned short *s_bin = s_id + B;                                            // its bin
+    constexpr int kLenCap = 1 << 26;    // keeps every sum below 2^38 (64-bit keys below)
+    constexpr int kPerThread = kSortLimit / 1024;
+
+    // rank by counting: longest first, lower id first among equal lengths
+    for (int i = tid; i < B; i += blockDim.x) {
+        const long long l = lens[i];
+        s_len[i] = l > kLenCap ? kLenCap : (l < 1 ? 1 : static_cast<int>(l));
+    }
+    __syncthreads();
+    int my_len[kPerThread], my_rank[kPerThread];
+#pragma unroll
+    for (int k = 0; k < kPerThread; ++k) {
+        const int i = tid + k * 1024;
+        my_len[k] = 0;
+        my_rank[k] = -1;
+        if (i < B) {
             const int li = s_len[i];
             int rank = 0;
             for (int j = 0; j < B; ++j) {
                 const int lj = s_len[j];
                 rank += (lj > li) || (lj == li && j < i);
             }
-            order[rank] = i;
+            my_len[k] = li;
+            my_rank[k] = rank;
         }
-    } else {
-        for (int i = threadIdx.x; i < B; i += blockDim.x) order[i] = i;
     }
-    if (threadIdx.x == 0) *counter = 0;
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < kPerThread; ++k) {
+        if (my_rank[k] >= 0) {
+            s_len[my_rank[k]] = my_len[k];
+            s_id[my_rank[k]] = static_cast<unsigned short>(tid + k * 1024);
+        }
+    }
+    for (int c = tid; c < C; c += blockDim.x) s_load[c] = 0;
+    __syncthreads();
+
+    // greedy packing, one warp: item r to the least loaded bin (lowest bin among equals)
+    if (warp == 0) {
+        for (int r = 0; r < B; ++r) {
+            int bin;
+            if (r < C) {
+                bin = r;
+            } else {
+                unsigned long long key = ~0ull;
+                for (int c = lane; c < C; c += 32) {
+                    const unsigned long long k = (static_cast<unsigned long long>(s_load[c]) << 10) | unsigned(c);
+                    key = k < key ? k : key;
+                }
+                bin = static_cast<int>(warp_min_u64(key) & 1023u);
+            }
+            if (lane == 0) {
+                s_load[bin] += s_len[r];
+                s_bin[r] = static_cast<unsigned short>(bin);
+            }
+            __syncwarp();
+        }
+    }
+    __syncthreads();
+
+    // repair of the fullest bin; the number of rounds is bounded by half the steps it could save
+    long long total = 0;
+    if (C > 1 && B > C) {
+        for (int c = 0; c < C; ++c) total += s_load[c];
+    }
+    int budget = 0;
+    if (C > 1 && B > C) {
+        long long top = 0;
+        for (int c = 0; c < C; ++c) top = s_load[c] > top ? s_load[c] : top;
+        const long long gap = top - total / C;
+        budget = static_cast<int>(gap / 2 < 4096 ? gap / 2 : 4096);
+    }
+    for (int it = 0; it < budget; ++it) {
+        if (warp == 0) {
+            // fullest bin (lowest index among equals) and its longest members, in rank order
+            unsigned long long key = ~0ull;
+            for (int c = lane; c < C; c += 32) {
+                const unsigned long long k = ((~static_cast<unsigned long long>(s_load[c]) & ((1ull << 40) - 1)) << 10) | unsigned(c);
+                key = k < key ? k : key;
+            }
+            const int a = static_cast<int>(warp_min_u64(key) & 1023u);
+            int n = 0;
+            for (int r0 = 0; r0 < B && n < 256; r0 += 32) {
+                const int r = r0 + lane;
+                const bool in = r < B && s_bin[r] == a;
+                const unsigned m = __ballot_sync(0xffffffffu, in);
+                const int pos = n + __popc(m & ((1u << lane) - 1u));
+                if (in && pos < 256) s_alist[pos] = static_cast<unsigned short>(r);
+                n += __popc(m);
+            }
+            if (lane == 0) {
+                s_a = a;
+                s_na = n < 256 ? n : 256;
+                s_done = 0;
+            }
+        }
+        __syncthreads();
+        const int a = s_a, na = s_na;
+        const long long La = s_load[a];
+        // candidates: exchange x (fullest bin) with a shorter y of bin b, or move x to bin b;
+        // key = new larger sum of the two bins, then a deterministic tie-break
+        unsigned long long best = ~0ull;
+        for (int y = tid; y < B; y += blockDim.x) {
+            const int b = s_bin[y];
+            const long long d = La - s_load[b];
+            if (b == a || d < 2) continue;
+            const int ly = s_len[y];
+            const long long Lb = s_load[b];
+            for (int i = 0; i < na; ++i) {
+                const int x = s_alist[i];
+                const long long dd = s_len[x] - ly;
+                if (dd > 0 && dd < d) {
+                    const long long m = La - dd > Lb + dd ? La - dd : Lb + dd;
+                    const unsigned long long k = (static_cast<unsigned long long>(m) << 25) | (unsigned(y) << 12) | unsigned(x);
+                    best = k < best ? k : best;
+                }
+            }
+        }
+        for (int b = tid; b < C; b += blockDim.x) {
+            const long long Lb = s_load[b];
+            const long long d = La - Lb;
+            if (b == a || d < 2) continue;
+            for (int i = 0; i < na; ++i) {
+                const int x = s_alist[i];
+                const long long lx = s_len[x];
+                if (lx < d) {
+                    const long long m = La - lx > Lb + lx ? La - lx : Lb + lx;
+                    const unsigned long long k = (static_cast<unsigned long long>(m) << 25) | (1ull << 24) |
+                                                 (static_cast<unsigned long long>(b) << 12) | unsigned(x);
+                    best = k < best ? k : best;
+                }
+            }
+        }
+        best = warp_min_u64(best);
+        if (lane == 0) s_red[warp] = best;
+        __syncthreads();
+        if (warp == 0) {
+            best = warp_min_u64(s_red[lane]);
+            if (lane == 0) {
+                if (best == ~0ull || static_cast<long long>(best >> 25) >= La) {
+                    s_done = 1;
+                } else {
+                    const int x = static_cast<int>(best & 4095u);
+                    if (best & (1ull << 24)) {
+                        const int b = static_cast<int>((best >> 12) & 1023u);
+                        s_load[a] -= s_len[x];
+                        s_load[b] += s_len[x];
+                        s_bin[x] = static_cast<unsigned short>(b);
+                    } else {
+                        const int y = static_cast<int>((best >> 12) & 4095u);
+                        const int b = s_bin[y];
+                        const int dd = s_len[x] - s_len[y];
+                        s_load[a] -= dd;
+                        s_load[b] += dd;
+                        s_bin[x] = static_cast<unsigned short>(b);
+                        s_bin[y] = static_cast<unsigned short>(a);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        if (s_done) break;
+    }
+
+    // group by bin: counts, prefix, then every bin lists its members in rank order
+    for (int c = tid; c <= C; c += blockDim.x) s_cnt[c] = 0;
+    __syncthreads();
+    for (int r = tid; r < B; r += blockDim.x) atomicAdd(&s_cnt[s_bin[r] + 1], 1);
+    __syncthreads();
+    if (tid == 0) {
+        for (int c = 0; c < C; ++c) s_cnt[c + 1] += s_cnt[c];
+    }
+    __syncthreads();
+    for (int c = tid; c <= C; c += blockDim.x) seg[c] = s_cnt[c];
+    for (int c = tid; c < C; c += blockDim.x) {
+        int at = s_cnt[c];
+        for (int r = 0; r < B; ++r)
+            if (s_bin[r] == c) order[at++] = s_id[r];
+    }
+    if (cluster_of != nullptr)
+        for (int r = tid; r < B; r += blockDim.x) cluster_of[s_id[r]] = s_bin[r];
+}
+
+// The next sequence of this cluster (-1: none left). Static schedule: the CTA's shared word
+// `s_seq` holds the position in the cluster's own part of `order` (set up by
+// first_position), so that nothing stays in a register across a sequence. Otherwise the
+// cluster leader pops the shared queue and hands the id to every CTA through distributed
+// shared memory. Either way the cluster barrier here also separates the previous sequence's
+// use of the CTA's scratch words from the next one's.
+__device__ __forceinline__ void first_position(const FwdParams &p, const unsigned CS, const int tid, int *s_seq) {
+    if (p.seg != nullptr && tid == 0) *s_seq = p.seg[blockIdx.x / CS];
+}
+__device__ __forceinline__ int next_sequence(const FwdParams &p, const unsigned rank, const unsigned CS,
+                                             const int tid, int *s_seq) {
+    if (p.seg == nullptr && rank == 0 && tid == 0) {
+        const int i = atomicAdd(p.counter, 1);
+        const int seq = i < p.B ? p.order[i] : -1;
+        const unsigned seq_addr = smem_u32(s_seq);
+        for (unsigned r = 0; r < CS; ++r) st_cluster_s32(map_to_rank(seq_addr, r), seq);
+    }
+    cluster_arrive();
+    cluster_wait();
+    if (p.seg == nullptr) return *s_seq;
+    const int qi = *s_seq;
+    const int seq = qi < p.seg[blockIdx.x / CS + 1] ? p.order[qi] : -1;
+    __syncthreads();   // every thread has read the position
+    if (tid == 0) *s_seq = qi + 1;
+    return seq;
 }
 
 // ---- resident kernel ---------------------------------------------------------
@@ -182,6 +412,7 @@ hmm_forward_resident(const FwdParams p) {
     __shared__ int s_seq;
     __shared__ float s_warp[32];
     __shared__ float s_cl[16];
+    __shared__ float s_tr2[kLayers];              // trans2
 
     const int tid = threadIdx.x;
     const int NT = blockDim.x;
@@ -193,7 +424,8 @@ hmm_forward_resident(const FwdParams p) {
     const int lk = tid * KPT;          // first local k-mer
     const int g = (rank * NT + tid) * KPT;  // first global k-mer
     const int lane = tid & 31, warp = tid >> 5, nwarps = (NT + 31) >> 5;
-    const ModelConsts &mc = c_model[p.slot];
+    if (tid < kLayers) s_tr2[tid] = __ldg(p.trans2 + tid);
+    __syncthreads();
 
     // Transition log-probs into my k-mers: T[j][c] = trans1[p_j, (g+c)%4].
     float T[4][KPT];
@@ -221,19 +453,11 @@ hmm_forward_resident(const FwdParams p) {
         dst0 = map_to_rank(a0_base + 4u * (dj * M + di), dr);
     }
     const unsigned buf_bytes = 16u * M;  // 4 segments * M floats
-    const unsigned seq_addr = smem_u32(&s_seq);
     const unsigned cl_addr = smem_u32(s_cl);
 
+    first_position(p, CS, tid, &s_seq);
     for (;;) {
-        // ---- pop the next sequence (cluster leader) and broadcast it ----------
-        if (rank == 0 && tid == 0) {
-            const int i = atomicAdd(p.counter, 1);
-            const int seq = i < p.B ? p.order[i] : -1;
-            for (unsigned r = 0; r < CS; ++r) st_cluster_s32(map_to_rank(seq_addr, r), seq);
-        }
-        cluster_arrive();
-        cluster_wait();
-        const int seq = s_seq;
+        const int seq = next_sequence(p, rank, CS, tid, &s_seq);
         if (seq < 0) break;
 
         long long len = p.lens[seq];
@@ -249,9 +473,9 @@ hmm_forward_resident(const FwdParams p) {
         float e[KPT], e_next[KPT];
         int o_next;
         {
-            const int o0 = obs[0];
-            const int o1 = obs[T_len > 1 ? 1 : 0];
-            o_next = obs[T_len > 2 ? 2 : T_len - 1];
+            const int o0 = obs_at(p, obs, 0);
+            const int o1 = obs_at(p, obs, T_len > 1 ? 1 : 0);
+            o_next = obs_at(p, obs, T_len > 2 ? 2 : T_len - 1);
             if constexpr (KPT == 4) {
                 const float4 v0 = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o0 * K + g));
                 const float4 v1 = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o1 * K + g));
@@ -293,7 +517,7 @@ hmm_forward_resident(const FwdParams p) {
                     e_next[0] = __ldg(row);
                 }
                 const int tn = t + 2 < T_len ? t + 2 : T_len - 1;
-                o_next = obs[tn];
+                o_next = obs_at(p, obs, tn);
             }
 
             cluster_wait();  // layer 0 of step t-1 from every CTA has landed
@@ -308,7 +532,7 @@ hmm_forward_resident(const FwdParams p) {
                     q[c] = lse4(T[0][c] + a0, T[1][c] + a1, T[2][c] + a2, T[3][c] + a3);
                 // layer 0 first: it is what the other CTAs wait for
 #pragma unroll
-                for (int c = 0; c < KPT; ++c) a[0][c] = lse2(mc.trans2[0] + q[c], a[1][c]) + e[c];
+                for (int c = 0; c < KPT; ++c) a[0][c] = lse2(s_tr2[0] + q[c], a[1][c]) + e[c];
                 if constexpr (KPT == 4) st_cluster_v4(dst, a[0][0], a[0][1], a[0][2], a[0][3]);
                 else st_cluster_f32(dst, a[0][0]);
                 cluster_arrive();
@@ -319,7 +543,7 @@ hmm_forward_resident(const FwdParams p) {
                         const float v = d == 15 ? p.gamma + a[15][c]
                                       : d == 14 ? p.synthetic + a[15][c]
                                                 : a[d + 1 < kLayers ? d + 1 : 15][c];
-                        a[d][c] = lse2(mc.trans2[d] + q[c], v) + e[c];
+                        a[d][c] = lse2(s_tr2[d] + q[c], v) + e[c];
                     }
                 }
             } else {
@@ -327,7 +551,7 @@ hmm_forward_resident(const FwdParams p) {
                 for (int d = 0; d < kLayers; ++d) {
 #pragma unroll
                     for (int c = 0; c < KPT; ++c) {
-                        const float t2 = mc.trans2[d];
+                        const float t2 = s_tr2[d];
                         const float p1 = (T[0][c] + t2) + a0;
                         const float p2 = (T[1][c] + t2) + a1;
                         const float p3 = (T[2][c] + t2) + a2;
@@ -423,6 +647,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_split(const FwdParams p) 
     __shared__ int s_seq;
     __shared__ float s_warp[32];
     __shared__ float s_cl[16];
+    __shared__ float s_tr2[kLayers];          // trans2
 
     const int tid = threadIdx.x;
     const int NT = blockDim.x;
@@ -433,7 +658,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_split(const FwdParams p) 
     const int M = NT;                         // predecessor groups per CTA (4 k-mers per thread)
     const int g = (rank * NT + tid) * 4;      // first global k-mer
     const int lane = tid & 31, warp = tid >> 5, nwarps = (NT + 31) >> 5;
-    const ModelConsts &mc = c_model[p.slot];
+    if (tid < kLayers) s_tr2[tid] = __ldg(p.trans2 + tid);
 
     float *a0s = smem_dyn;                                             // [2][4][M]
     float4 *Ts = reinterpret_cast<float4 *>(smem_dyn + 8 * M);         // [4][NT] transition columns
@@ -450,18 +675,11 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_split(const FwdParams p) 
         dst0 = map_to_rank(a0_base + 4u * (dj * M + di), dr);
     }
     const unsigned buf_bytes = 16u * M;
-    const unsigned seq_addr = smem_u32(&s_seq);
     const unsigned cl_addr = smem_u32(s_cl);
 
+    first_position(p, CS, tid, &s_seq);
     for (;;) {
-        if (rank == 0 && tid == 0) {
-            const int i = atomicAdd(p.counter, 1);
-            const int seq = i < p.B ? p.order[i] : -1;
-            for (unsigned r = 0; r < CS; ++r) st_cluster_s32(map_to_rank(seq_addr, r), seq);
-        }
-        cluster_arrive();
-        cluster_wait();
-        const int seq = s_seq;
+        const int seq = next_sequence(p, rank, CS, tid, &s_seq);
         if (seq < 0) break;
 
         long long len = p.lens[seq];
@@ -477,8 +695,8 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_split(const FwdParams p) 
         float4 e;
         int o_next;
         {
-            const int o0 = obs[0];
-            o_next = obs[T_len > 1 ? 1 : 0];
+            const int o0 = obs_at(p, obs, 0);
+            o_next = obs_at(p, obs, T_len > 1 ? 1 : 0);
             e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o0 * K + g));
 #pragma unroll
             for (int d = 0; d < kLayers; ++d) {
@@ -495,7 +713,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_split(const FwdParams p) 
         for (int t = 1; t < T_len; ++t) {
             // this step's emission slice; the observation after it
             e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o_next * K + g));
-            o_next = obs[t + 1 < T_len ? t + 1 : T_len - 1];
+            o_next = obs_at(p, obs, t + 1 < T_len ? t + 1 : T_len - 1);
             const float ev[4] = {e.x, e.y, e.z, e.w};
 
             cluster_wait();
@@ -513,14 +731,14 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_split(const FwdParams p) 
             }
 #pragma unroll
             for (int c = 0; c < 4; ++c)
-                a[0][c] = lse2_sel((POLY_MASK & 1u) != 0, mc.trans2[0] + q[c], a[1][c]) + ev[c];
+                a[0][c] = lse2_sel((POLY_MASK & 1u) != 0, s_tr2[0] + q[c], a[1][c]) + ev[c];
             st_cluster_v4(dst, a[0][0], a[0][1], a[0][2], a[0][3]);
             cluster_arrive();
 #pragma unroll
             for (int d = 1; d < kRegLayers - 1; ++d)
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
-                    a[d][c] = lse2_sel(((POLY_MASK >> d) & 1u) != 0, mc.trans2[d] + q[c], a[d + 1][c]) + ev[c];
+                    a[d][c] = lse2_sel(((POLY_MASK >> d) & 1u) != 0, s_tr2[d] + q[c], a[d + 1][c]) + ev[c];
             // layers 7..15: the "next layer" operand comes from shared memory
             float4 nxt = As[tid];  // layer 8 (old)
             {
@@ -528,7 +746,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_split(const FwdParams p) 
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
                     a[kRegLayers - 1][c] = lse2_sel(((POLY_MASK >> (kRegLayers - 1)) & 1u) != 0,
-                                               mc.trans2[kRegLayers - 1] + q[c], nv[c]) + ev[c];
+                                               s_tr2[kRegLayers - 1] + q[c], nv[c]) + ev[c];
             }
 #pragma unroll
             for (int d = kRegLayers; d < kLayers; ++d) {
@@ -539,7 +757,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_split(const FwdParams p) 
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     const float v = d == 15 ? p.gamma + nv[c] : d == 14 ? p.synthetic + nv[c] : nv[c];
-                    r[c] = lse2_sel(((POLY_MASK >> d) & 1u) != 0, mc.trans2[d] + q[c], v) + ev[c];
+                    r[c] = lse2_sel(((POLY_MASK >> d) & 1u) != 0, s_tr2[d] + q[c], v) + ev[c];
                 }
                 As[(d - kRegLayers) * NT + tid] = make_float4(r[0], r[1], r[2], r[3]);
             }
@@ -705,7 +923,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
     for (int j = 0; j < 4; ++j) {
         Ts[j * NT + tid] = __ldg(reinterpret_cast<const float4 *>(p.trans1) + (j * Kq + (g >> 2)));
     }
-    if (tid < kLayers) s_t2[tid] = dup2(c_model[p.slot].trans2[tid]);
+    if (tid < kLayers) s_t2[tid] = dup2(__ldg(p.trans2 + tid));
     const float gamma2 = p.gamma, syn2 = p.synthetic;
 
     const unsigned a0_base = smem_u32(a0s);
@@ -716,19 +934,12 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
         dst0 = map_to_rank(a0_base + 4u * (dj * M + di), dr);
     }
     const unsigned buf_bytes = 16u * M;
-    const unsigned seq_addr = smem_u32(&s_seq);
     const unsigned cl_addr = smem_u32(s_cl);
     __syncthreads();
 
+    first_position(p, CS, tid, &s_seq);
     for (;;) {
-        if (rank == 0 && tid == 0) {
-            const int i = atomicAdd(p.counter, 1);
-            const int seq = i < p.B ? p.order[i] : -1;
-            for (unsigned r = 0; r < CS; ++r) st_cluster_s32(map_to_rank(seq_addr, r), seq);
-        }
-        cluster_arrive();
-        cluster_wait();
-        const int seq = s_seq;
+        const int seq = next_sequence(p, rank, CS, tid, &s_seq);
         if (seq < 0) break;
 
         long long len = p.lens[seq];
@@ -744,8 +955,8 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
         float4 e;
         int o_next;
         {
-            const int o0 = obs[0];
-            o_next = obs[T_len > 1 ? 1 : 0];
+            const int o0 = obs_at(p, obs, 0);
+            o_next = obs_at(p, obs, T_len > 1 ? 1 : 0);
             e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o0 * K + g));
 #pragma unroll
             for (int d = 0; d < kLayers; ++d) {
@@ -763,7 +974,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
         for (int t = 1; t < T_len; ++t) {
             // this step's emission slice; the observation after it
             e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o_next * K + g));
-            o_next = obs[t + 1 < T_len ? t + 1 : T_len - 1];
+            o_next = obs_at(p, obs, t + 1 < T_len ? t + 1 : T_len - 1);
             const float2 ev[2] = {make_float2(e.x, e.y), make_float2(e.z, e.w)};
 
             cluster_wait();
@@ -911,17 +1122,26 @@ __global__ void __launch_bounds__(256, 1) hmm_forward_packed_cta(const FwdParams
         T[j][0] = make_float2(v.x, v.y);
         T[j][1] = make_float2(v.z, v.w);
     }
-    if (tid < kLayers) s_t2[tid] = dup2(c_model[p.slot].trans2[tid]);
+    if (tid < kLayers) s_t2[tid] = dup2(__ldg(p.trans2 + tid));
     const float gamma2 = p.gamma, syn2 = p.synthetic;
 
+    if (p.seg != nullptr && tid == 0) s_seq = p.seg[blockIdx.x];   // position in this CTA's part of the schedule
     for (;;) {
         __syncthreads();   // s_seq, s_warp and a0s of the previous sequence are no longer read
-        if (tid == 0) {
-            const int i = atomicAdd(p.counter, 1);
-            s_seq = i < p.B ? p.order[i] : -1;
+        int seq;
+        if (p.seg != nullptr) {
+            const int qi = s_seq;
+            seq = qi < p.seg[blockIdx.x + 1] ? p.order[qi] : -1;
+            __syncthreads();   // every thread has read the position
+            if (tid == 0) s_seq = qi + 1;
+        } else {
+            if (tid == 0) {
+                const int i = atomicAdd(p.counter, 1);
+                s_seq = i < p.B ? p.order[i] : -1;
+            }
+            __syncthreads();
+            seq = s_seq;
         }
-        __syncthreads();
-        const int seq = s_seq;
         if (seq < 0) break;
 
         long long len = p.lens[seq];
@@ -936,8 +1156,8 @@ __global__ void __launch_bounds__(256, 1) hmm_forward_packed_cta(const FwdParams
         float4 e;
         int o_next;
         {
-            const int o0 = obs[0];
-            o_next = obs[T_len > 1 ? 1 : 0];
+            const int o0 = obs_at(p, obs, 0);
+            o_next = obs_at(p, obs, T_len > 1 ? 1 : 0);
             e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o0 * K + g));
 #pragma unroll
             for (int d = 0; d < kLayers; ++d) {
@@ -951,7 +1171,7 @@ __global__ void __launch_bounds__(256, 1) hmm_forward_packed_cta(const FwdParams
 
         for (int t = 1; t < T_len; ++t) {
             e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o_next * K + g));
-            o_next = obs[t + 1 < T_len ? t + 1 : T_len - 1];
+            o_next = obs_at(p, obs, t + 1 < T_len ? t + 1 : T_len - 1);
             const float2 ev[2] = {make_float2(e.x, e.y), make_float2(e.z, e.w)};
 
             __syncthreads();   // layer 0 of step t-1 is complete; the other buffer is free
@@ -1058,6 +1278,7 @@ __global__ void __launch_bounds__(512, 1) hmm_forward_scaled(const FwdParams p) 
     __shared__ int s_warp_i[32];
     __shared__ float s_cl[16];
     __shared__ int s_cl_i[16];
+    __shared__ float s_A[kLayers];      // exp(trans2[d])
 
     const int tid = threadIdx.x;
     const int NT = blockDim.x;
@@ -1068,7 +1289,7 @@ __global__ void __launch_bounds__(512, 1) hmm_forward_scaled(const FwdParams p) 
     const int M = NT;
     const int g = (rank * NT + tid) * 4;
     const int lane = tid & 31, warp = tid >> 5, nwarps = (NT + 31) >> 5;
-    const ModelConsts &A = c_model_lin[p.slot];
+    if (tid < kLayers) s_A[tid] = expf(__ldg(p.trans2 + tid));
 
     float *a0x = smem_dyn;
     int *a0e = reinterpret_cast<int *>(smem_dyn + 8 * M);
@@ -1091,19 +1312,12 @@ __global__ void __launch_bounds__(512, 1) hmm_forward_scaled(const FwdParams p) 
         dste0 = map_to_rank(smem_u32(a0e) + 4u * (dj * M + di), dr);
     }
     const unsigned buf_bytes = 16u * M;
-    const unsigned seq_addr = smem_u32(&s_seq);
     const unsigned cl_addr = smem_u32(s_cl);
     const unsigned cli_addr = smem_u32(s_cl_i);
 
+    first_position(p, CS, tid, &s_seq);
     for (;;) {
-        if (rank == 0 && tid == 0) {
-            const int i = atomicAdd(p.counter, 1);
-            const int seq = i < p.B ? p.order[i] : -1;
-            for (unsigned r = 0; r < CS; ++r) st_cluster_s32(map_to_rank(seq_addr, r), seq);
-        }
-        cluster_arrive();
-        cluster_wait();
-        const int seq = s_seq;
+        const int seq = next_sequence(p, rank, CS, tid, &s_seq);
         if (seq < 0) break;
 
         long long len = p.lens[seq];
@@ -1121,9 +1335,9 @@ __global__ void __launch_bounds__(512, 1) hmm_forward_scaled(const FwdParams p) 
         int W = 0;       // exponent shared by this thread's 64 states
         int kt;          // exponent of the largest mantissa (magnitude hint)
         {
-            const int o0 = obs[0];
-            const int o1 = obs[T_len > 1 ? 1 : 0];
-            o_next = obs[T_len > 2 ? 2 : T_len - 1];
+            const int o0 = obs_at(p, obs, 0);
+            const int o1 = obs_at(p, obs, T_len > 1 ? 1 : 0);
+            o_next = obs_at(p, obs, T_len > 2 ? 2 : T_len - 1);
             const float4 e0 = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o0 * K + g));
             e_next = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o1 * K + g));
             const float el[4] = {fast_exp(e0.x), fast_exp(e0.y), fast_exp(e0.z), fast_exp(e0.w)};
@@ -1149,7 +1363,7 @@ __global__ void __launch_bounds__(512, 1) hmm_forward_scaled(const FwdParams p) 
             // emission probabilities of o_t (log values were fetched a step ago)
             const float el[4] = {fast_exp(e_next.x), fast_exp(e_next.y), fast_exp(e_next.z), fast_exp(e_next.w)};
             e_next = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o_next * K + g));
-            o_next = obs[t + 2 < T_len ? t + 2 : T_len - 1];
+            o_next = obs_at(p, obs, t + 2 < T_len ? t + 2 : T_len - 1);
 
             cluster_wait();
             const int off = (buf ? 4 * M : 0) + tid;
@@ -1180,7 +1394,7 @@ __global__ void __launch_bounds__(512, 1) hmm_forward_scaled(const FwdParams p) 
             }
             // layer 0 first: it is what the other CTAs wait for
 #pragma unroll
-            for (int c = 0; c < 4; ++c) x[0][c] = fmaf(A.trans2[0], QE[c], Eo[c] * x[1][c]);
+            for (int c = 0; c < 4; ++c) x[0][c] = fmaf(s_A[0], QE[c], Eo[c] * x[1][c]);
             st_cluster_v4(dstx, x[0][0], x[0][1], x[0][2], x[0][3]);
             st_cluster_v4i(dste, export_exponent(x[0][0], Wn), export_exponent(x[0][1], Wn),
                            export_exponent(x[0][2], Wn), export_exponent(x[0][3], Wn));
@@ -1193,7 +1407,7 @@ __global__ void __launch_bounds__(512, 1) hmm_forward_scaled(const FwdParams p) 
                     const float nx = d == 15 ? p.gamma_lin * x[15][c]
                                    : d == 14 ? p.synthetic_lin * x[15][c]
                                              : x[d + 1 < kLayers ? d + 1 : 15][c];
-                    x[d][c] = fmaf(A.trans2[d], QE[c], Eo[c] * nx);
+                    x[d][c] = fmaf(s_A[d], QE[c], Eo[c] * nx);
                 }
                 m = max3(m, fmaxf(x[d][0], x[d][1]), fmaxf(x[d][2], x[d][3]));
             }
@@ -1254,17 +1468,13 @@ __global__ void __launch_bounds__(512, 1) hmm_forward_scaled(const FwdParams p) 
     }
 }
 
-__global__ void hmm_linear_consts(const float *__restrict__ trans2, float *__restrict__ out) {
-    if (threadIdx.x < kLayers) out[threadIdx.x] = expf(trans2[threadIdx.x]);
-}
-
 // ---- streaming kernels --------------------------------------------------------
 __global__ void hmm_stream_init(const FwdParams p) {
     const long long N = (long long)kLayers * p.K;
     const long long state = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const int inst = blockIdx.y;
     if (state >= N) return;
-    const int o = p.data[(long long)inst * p.maxlen];
+    const int o = obs_at(p, p.data + (long long)inst * p.maxlen, 0);
     p.alpha1[inst * N + state] = p.initial_prob[state] + p.output_prob[(long long)o * p.K + state % p.K];
 }
 
@@ -1277,13 +1487,12 @@ __global__ void hmm_stream_step(const FwdParams p, int t) {
     if (t >= p.lens[inst]) return;  // benchmarks/forward.py:113: no write past the end
     const float *src = ((t & 1) ? p.alpha1 : p.alpha2) + inst * N;
     float *dst = ((t & 1) ? p.alpha2 : p.alpha1) + inst * N;
-    const ModelConsts &mc = c_model[p.slot];
-    const int o = p.data[(long long)inst * p.maxlen + t];
+    const int o = obs_at(p, p.data + (long long)inst * p.maxlen, t);
     const int s = static_cast<int>(state % K);
     const int d = static_cast<int>(state / K);
     const int Kq = K >> 2;
     const int low = s >> 2;
-    const float t2 = mc.trans2[d];
+    const float t2 = __ldg(p.trans2 + d);
     const float p1 = (p.trans1[(0 * Kq + low) * 4 + (s & 3)] + t2) + src[0 * Kq + low];
     const float p2 = (p.trans1[(1 * Kq + low) * 4 + (s & 3)] + t2) + src[1 * Kq + low];
     const float p3 = (p.trans1[(2 * Kq + low) * 4 + (s & 3)] + t2) + src[2 * Kq + low];
@@ -1477,19 +1686,44 @@ int32_t resident_config(const Plan &pl, bool five, cudaLaunchConfig_t *cfg,
     return PB_OK;
 }
 
-std::atomic<unsigned> g_slot{0};
+// Scheduling scratch of one call: order[B] (256-byte aligned), the queue head, the segment table.
+struct SchedScratch {
+    int *order, *counter, *seg;
+};
+size_t sched_bytes(int B) { return ((size_t(B) * sizeof(int) + 255) & ~size_t(255)) + kSchedTailBytes; }
+SchedScratch sched_layout(void *base, size_t order_bytes) {
+    char *c = static_cast<char *>(base);
+    return {reinterpret_cast<int *>(c), reinterpret_cast<int *>(c + order_bytes),
+            reinterpret_cast<int *>(c + order_bytes + 256)};
+}
+
+// Launches the scheduling prologue for `clusters` resident clusters and fills in the
+// schedule fields of `p`. Batches up to kSortLimit get the static balanced schedule.
+int32_t launch_schedule(FwdParams *p, const SchedScratch &sc, int clusters, int *cluster_of,
+                        cudaStream_t stream) {
+    const bool fixed = p->B <= kSortLimit && clusters <= kMaxBins;
+    p->order = sc.order;
+    p->counter = sc.counter;
+    p->seg = fixed ? sc.seg : nullptr;
+    const size_t smem = fixed ? size_t(p->B) * 8 : 0;
+    hmm_schedule<<<1, 1024, smem, stream>>>(p->lens, p->B, fixed ? clusters : 0, sc.order, sc.counter, sc.seg,
+                                             cluster_of);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
 
 int32_t forward_impl(float gamma, const float *initial_prob, int64_t num_states,
                      const float *output_prob, float synthetic_248, const float *trans1,
                      const float *trans2, const void *data, const int64_t *lens, int64_t maxlen,
                      int64_t num_instances, float *result, float *alpha1, float *alpha2,
-                     uint32_t flags, cudaStream_t stream) {
+                     uint32_t flags, int64_t n_obs, cudaStream_t stream) {
     PB_REQUIRE(num_states >= 64 && num_states % 64 == 0,
                "forward: num_states=%lld must be a positive multiple of 64", (long long)num_states);
     PB_REQUIRE(num_states <= (1LL << 30), "forward: num_states=%lld too large", (long long)num_states);
     PB_REQUIRE(num_instances >= 0 && num_instances <= 0x7fffffffLL,
                "forward: num_instances=%lld out of range", (long long)num_instances);
     PB_REQUIRE(maxlen >= 1 && maxlen <= 0x7fffffffLL, "forward: maxlen=%lld out of range", (long long)maxlen);
+    PB_REQUIRE(n_obs >= 0, "forward: n_obs=%lld is negative", (long long)n_obs);
     if (num_instances == 0) return PB_OK;
     PB_REQUIRE(initial_prob && output_prob && trans1 && trans2 && data && lens && result,
                "forward: null table, observation or result pointer");
@@ -1511,6 +1745,7 @@ int32_t forward_impl(float gamma, const float *initial_prob, int64_t num_states,
     p.initial_prob = initial_prob;
     p.output_prob = output_prob;
     p.trans1 = trans1;
+    p.trans2 = trans2;
     p.data = static_cast<const uint8_t *>(data);
     p.lens = lens;
     p.result = result;
@@ -1519,15 +1754,12 @@ int32_t forward_impl(float gamma, const float *initial_prob, int64_t num_states,
     p.maxlen = maxlen;
     p.B = static_cast<int>(num_instances);
     p.K = static_cast<int>(K);
+    p.obs_max = n_obs >= 1 && n_obs <= 256 ? static_cast<int>(n_obs) - 1 : 255;
     p.gamma = gamma;
     p.synthetic = synthetic_248;
     p.gamma_lin = expf(gamma);
     p.synthetic_lin = expf(synthetic_248);
     p.write_alpha = write_alpha ? 1 : 0;
-    p.slot = static_cast<int>(g_slot.fetch_add(1) % kModelSlots);
-    PB_CUDA(cudaMemcpyToSymbolAsync(c_model, trans2, sizeof(ModelConsts),
-                                    size_t(p.slot) * sizeof(ModelConsts), cudaMemcpyDeviceToDevice,
-                                    stream));
 
     Plan pl;
     const bool resident = !streaming_forced && make_plan(K, &pl, !five && !scaled, scaled);
@@ -1545,31 +1777,17 @@ int32_t forward_impl(float gamma, const float *initial_prob, int64_t num_states,
         ResidentKernel kern = nullptr;
         rc = resident_config(pl, five, &cfg, attr, &max_clusters, &kern);
         if (rc) return rc;
-        // scratch: order[B] + counter, from the library workspace
-        void *ws = nullptr;
-        const size_t order_bytes = (size_t(p.B) * sizeof(int) + 255) & ~size_t(255);
-        rc = pb::workspace(order_bytes + 512, &ws, stream, 0);
-        if (rc) return rc;
-        int *order = static_cast<int *>(ws);
-        int *counter = reinterpret_cast<int *>(static_cast<char *>(ws) + order_bytes);
-        if (scaled) {
-            float *lin = reinterpret_cast<float *>(static_cast<char *>(ws) + order_bytes + 256);
-            hmm_linear_consts<<<1, 32, 0, stream>>>(trans2, lin);
-            PB_CUDA(cudaGetLastError());
-            PB_CUDA(cudaMemcpyToSymbolAsync(c_model_lin, lin, sizeof(ModelConsts),
-                                            size_t(p.slot) * sizeof(ModelConsts),
-                                            cudaMemcpyDeviceToDevice, stream));
-        }
-        p.order = order;
-        p.counter = counter;
-        const size_t sched_smem = p.B <= kSortLimit ? size_t(p.B) * sizeof(int) : 0;
-        hmm_schedule<<<1, 1024, sched_smem, stream>>>(lens, p.B, order, counter);
-        PB_CUDA(cudaGetLastError());
         int clusters = std::min(max_clusters, p.B);
         if (const char *env = getenv("PARPY_B200_FWD_CLUSTERS")) {
             const int v = atoi(env);
             if (v >= 1 && v <= clusters) clusters = v;
         }
+        // scratch from the library workspace: sequence order, queue head, segment table
+        void *ws = nullptr;
+        rc = pb::workspace(sched_bytes(p.B), &ws, stream, 0);
+        if (rc) return rc;
+        rc = launch_schedule(&p, sched_layout(ws, sched_bytes(p.B) - kSchedTailBytes), clusters, nullptr, stream);
+        if (rc) return rc;
         cfg.gridDim = dim3(pl.cs * clusters, 1, 1);
         cfg.stream = stream;
         PB_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
@@ -1603,7 +1821,17 @@ int32_t parpy_b200_forward(float gamma, const float *initial_prob, int64_t num_s
                            int64_t maxlen, int64_t num_instances, float *result, float *alpha1,
                            float *alpha2, uint32_t flags, void *stream) {
     return forward_impl(gamma, initial_prob, num_states, output_prob, synthetic_248, trans1, trans2,
-                        data, lens, maxlen, num_instances, result, alpha1, alpha2, flags,
+                        data, lens, maxlen, num_instances, result, alpha1, alpha2, flags, 0,
+                        static_cast<cudaStream_t>(stream));
+}
+
+int32_t parpy_b200_forward_ex(float gamma, const float *initial_prob, int64_t num_states,
+                              const float *output_prob, int64_t n_obs, float synthetic_248,
+                              const float *trans1, const float *trans2, const void *data,
+                              const int64_t *lens, int64_t maxlen, int64_t num_instances, float *result,
+                              float *alpha1, float *alpha2, uint32_t flags, void *stream) {
+    return forward_impl(gamma, initial_prob, num_states, output_prob, synthetic_248, trans1, trans2,
+                        data, lens, maxlen, num_instances, result, alpha1, alpha2, flags, n_obs,
                         static_cast<cudaStream_t>(stream));
 }
 
@@ -1613,7 +1841,7 @@ int32_t forward_kernel(float gamma, float *initial_prob, int64_t num_states, flo
                        float *alpha1, float *alpha2) {
     return forward_impl(gamma, initial_prob, num_states, output_prob, synthetic_248, trans1, trans2,
                         data, lens, maxlen, num_instances, result, alpha1, alpha2,
-                        PARPY_B200_FWD_AUTO, nullptr);
+                        PARPY_B200_FWD_AUTO, 0, nullptr);
 }
 
 int32_t forward_kernel_scratch_first(float gamma, float *initial_prob, int64_t num_states,
@@ -1623,7 +1851,7 @@ int32_t forward_kernel_scratch_first(float gamma, float *initial_prob, int64_t n
                                      float *result) {
     return forward_impl(gamma, initial_prob, num_states, output_prob, synthetic_248, trans1, trans2,
                         data, lens, maxlen, num_instances, result, alpha1, alpha2,
-                        PARPY_B200_FWD_AUTO, nullptr);
+                        PARPY_B200_FWD_AUTO, 0, nullptr);
 }
 
 int32_t parpy_b200_forward_plan(int64_t num_states, int64_t num_instances, int32_t *kmers_per_thread,
@@ -1645,6 +1873,25 @@ int32_t parpy_b200_forward_plan(int64_t num_states, int64_t num_instances, int32
     if (ctas_per_cluster) *ctas_per_cluster = pl.cs;
     if (clusters) *clusters = (int32_t)std::min<int64_t>(max_clusters, std::max<int64_t>(num_instances, 1));
     return PB_OK;
+}
+
+int32_t parpy_b200_forward_schedule(const int64_t *lens, int64_t num_instances, int64_t clusters,
+                                    int32_t *cluster_of, void *stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    PB_REQUIRE(num_instances >= 1 && num_instances <= kSortLimit,
+               "forward_schedule: the static schedule covers 1..%d sequences (got %lld); larger batches "
+               "use a work queue", kSortLimit, (long long)num_instances);
+    PB_REQUIRE(clusters >= 1 && clusters <= kMaxBins, "forward_schedule: clusters=%lld outside 1..%d",
+               (long long)clusters, kMaxBins);
+    PB_REQUIRE(lens && cluster_of, "forward_schedule: null pointer");
+    FwdParams p{};
+    p.lens = lens;
+    p.B = static_cast<int>(num_instances);
+    void *ws = nullptr;
+    int32_t rc = pb::workspace(sched_bytes(p.B), &ws, stream, 0);
+    if (rc) return rc;
+    const int c = static_cast<int>(std::min<int64_t>(clusters, num_instances));
+    return launch_schedule(&p, sched_layout(ws, sched_bytes(p.B) - kSchedTailBytes), c, cluster_of, stream);
 }
 
 int32_t parpy_b200_forward_status(uint32_t *status) {
@@ -1730,11 +1977,8 @@ extern "C" int32_t parpy_b200_forward_noalloc(float gamma, const float *initial_
     p.gamma = gamma;
     p.synthetic = synthetic_248;
     p.write_alpha = 0;
-    p.slot = static_cast<int>(g_slot.fetch_add(1) % kModelSlots);
-    p.order = static_cast<int *>(scratch);
-    p.counter = reinterpret_cast<int *>(static_cast<char *>(scratch) + kNoAllocOrderBytes);
-    PB_CUDA(cudaMemcpyToSymbolAsync(c_model, trans2, sizeof(ModelConsts),
-                                    size_t(p.slot) * sizeof(ModelConsts), cudaMemcpyDeviceToDevice, stream));
+    p.trans2 = trans2;
+    p.obs_max = 255;
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[1];
     int max_clusters = 0;
@@ -1742,12 +1986,12 @@ extern "C" int32_t parpy_b200_forward_noalloc(float gamma, const float *initial_
     rc = resident_config(pl, false, &cfg, attr, &max_clusters, &kern);
     if (rc) return rc;
     // The array keeps whatever the previous call left in it. hmm_schedule rewrites
-    // all num_instances order entries and sets the queue head to zero before the
-    // forward kernel (same stream) reads either, so nothing stale is ever used.
-    const size_t sched_smem = p.B <= kSortLimit ? size_t(p.B) * sizeof(int) : 0;
-    hmm_schedule<<<1, 1024, sched_smem, stream>>>(lens, p.B, const_cast<int *>(p.order), p.counter);
-    PB_CUDA(cudaGetLastError());
-    cfg.gridDim = dim3(pl.cs * std::min(max_clusters, p.B), 1, 1);
+    // all num_instances order entries, the queue head and the segment table before the
+    // forward kernel (same stream) reads any of them, so nothing stale is ever used.
+    const int clusters = std::min(max_clusters, p.B);
+    rc = launch_schedule(&p, sched_layout(scratch, kNoAllocOrderBytes), clusters, nullptr, stream);
+    if (rc) return rc;
+    cfg.gridDim = dim3(pl.cs * clusters, 1, 1);
     cfg.stream = stream;
     PB_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
     return PB_OK;

@@ -43,6 +43,7 @@ struct VitParams {
     int K;
     int batch;
     int overlap;
+    int obs_max;                // n_obs - 1: observations above it are clamped and flagged
     float gamma;
     float synthetic;
 };
@@ -152,10 +153,12 @@ __device__ __forceinline__ void argmax_combine(float &v, unsigned &i, float ov, 
 // every thread's read of round r - 4 (three hops through the "feeds" relation reach every
 // CTA), hence four buffers and four mbarriers. Waits are bounded.
 constexpr int kVitWaitLimit = 1 << 22;
-__device__ unsigned g_vit_status;   // bit 0: a wait for layer 0 ran out; the paths of that call are not valid
+// Device status word. Bit 0: a wait for layer 0 ran out; the paths of that call are not
+// valid. Bit 1: an observation >= n_obs inside a sequence was clamped to n_obs - 1.
+__device__ unsigned g_vit_status;
 
-__device__ __forceinline__ bool vit_mbar_wait(unsigned mbar, unsigned parity) {
-    for (int i = 0; i < kVitWaitLimit; ++i) {
+__device__ __forceinline__ bool vit_mbar_wait(unsigned mbar, unsigned parity, int limit = kVitWaitLimit) {
+    for (int i = 0; i < limit; ++i) {
         unsigned ok;
         asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
                      "selp.u32 %0, 1, 0, p;\n\t}"
@@ -163,6 +166,33 @@ __device__ __forceinline__ bool vit_mbar_wait(unsigned mbar, unsigned parity) {
         if (ok) return true;
     }
     return false;
+}
+
+// Observation byte t of a sequence, kept inside the emission table.
+__device__ __forceinline__ int vit_obs(const VitParams &p, const uint8_t *obs, int t) {
+    int o = obs[t];
+    if (o > p.obs_max) {
+        if (threadIdx.x == 0) atomicOr(&g_vit_status, 2u);
+        o = p.obs_max;
+    }
+    return o;
+}
+
+// One CTA waits, with the kernel's bounded wait, on an mbarrier that nothing ever completes:
+// the wait runs out after `polls` polls and the status bit is raised exactly as in the
+// decoding kernel. No other CTA, no data in flight; used to check that a wait that gives up
+// reaches the host.
+__global__ void vit_wait_probe(int polls) {
+    __shared__ __align__(8) unsigned long long mbar;
+    const unsigned addr = smem_u32(&mbar);
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(addr));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (!vit_mbar_wait(addr, 0u, polls) && threadIdx.x == 0) atomicOr(&g_vit_status, 1u);
+    __syncthreads();
+    if (threadIdx.x == 0) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(addr) : "memory");
 }
 
 // Layer 0 of one thread to the consuming CTA: buffer b of its shared memory.
@@ -287,7 +317,7 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
             float chi[kLayers][4];
             float e[4];
             {
-                const float4 v = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)obs[t] * K + g));
+                const float4 v = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)vit_obs(p, obs, t) * K + g));
                 e[0] = v.x; e[1] = v.y; e[2] = v.z; e[3] = v.w;
             }
             if (t == 0) {
@@ -355,7 +385,7 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
             // ---- forward steps with back pointers (hmm.cu:116-176, 378-412) ----------------
             for (int k = 1; k < L; ++k) {
                 {
-                    const float4 v = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)obs[t + k] * K + g));
+                    const float4 v = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)vit_obs(p, obs, t + k) * K + g));
                     e[0] = v.x; e[1] = v.y; e[2] = v.z; e[3] = v.w;
                 }
                 if (ASYNC) {
@@ -570,13 +600,14 @@ bool vit_plan(long long K, VitPlan *pl) {
 
 }  // namespace
 
-extern "C" int32_t parpy_b200_viterbi(float gamma, const float *initial_prob, int64_t num_states,
-                                      const float *output_prob, float synthetic_248,
-                                      const float *trans1, const float *trans2, const void *data,
-                                      const int64_t *lens, int64_t maxlen, int64_t num_instances,
-                                      int64_t batch_size, int64_t batch_overlap, uint32_t *out,
-                                      int64_t out_stride, void *stream_) {
+static int32_t viterbi_impl(float gamma, const float *initial_prob, int64_t num_states,
+                            const float *output_prob, int64_t n_obs, float synthetic_248,
+                            const float *trans1, const float *trans2, const void *data,
+                            const int64_t *lens, int64_t maxlen, int64_t num_instances,
+                            int64_t batch_size, int64_t batch_overlap, uint32_t *out,
+                            int64_t out_stride, void *stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    PB_REQUIRE(n_obs >= 0, "viterbi: n_obs=%lld is negative", (long long)n_obs);
     PB_REQUIRE(num_states >= 64 && num_states % 64 == 0, "viterbi: num_states=%lld must be a positive multiple of 64",
                (long long)num_states);
     PB_REQUIRE(num_instances >= 0 && num_instances <= 0x7fffffffLL, "viterbi: num_instances out of range");
@@ -653,6 +684,7 @@ extern "C" int32_t parpy_b200_viterbi(float gamma, const float *initial_prob, in
     p.K = (int)K;
     p.batch = (int)batch_size;
     p.overlap = (int)batch_overlap;
+    p.obs_max = n_obs >= 1 && n_obs <= 256 ? (int)n_obs - 1 : 255;
     p.gamma = gamma;
     p.synthetic = synthetic_248;
     const size_t sched_smem = p.B <= 4096 ? size_t(p.B) * sizeof(int) : 0;
@@ -662,3 +694,43 @@ extern "C" int32_t parpy_b200_viterbi(float gamma, const float *initial_prob, in
     PB_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
     return PB_OK;
 }
+
+extern "C" {
+
+int32_t parpy_b200_viterbi(float gamma, const float *initial_prob, int64_t num_states,
+                           const float *output_prob, float synthetic_248, const float *trans1,
+                           const float *trans2, const void *data, const int64_t *lens, int64_t maxlen,
+                           int64_t num_instances, int64_t batch_size, int64_t batch_overlap,
+                           uint32_t *out, int64_t out_stride, void *stream) {
+    return viterbi_impl(gamma, initial_prob, num_states, output_prob, 0, synthetic_248, trans1, trans2, data, lens,
+                        maxlen, num_instances, batch_size, batch_overlap, out, out_stride, stream);
+}
+
+int32_t parpy_b200_viterbi_ex(float gamma, const float *initial_prob, int64_t num_states,
+                              const float *output_prob, int64_t n_obs, float synthetic_248,
+                              const float *trans1, const float *trans2, const void *data,
+                              const int64_t *lens, int64_t maxlen, int64_t num_instances,
+                              int64_t batch_size, int64_t batch_overlap, uint32_t *out, int64_t out_stride,
+                              void *stream) {
+    return viterbi_impl(gamma, initial_prob, num_states, output_prob, n_obs, synthetic_248, trans1, trans2, data,
+                        lens, maxlen, num_instances, batch_size, batch_overlap, out, out_stride, stream);
+}
+
+int32_t parpy_b200_viterbi_status(uint32_t *status) {
+    PB_REQUIRE(status != nullptr, "viterbi_status: null output pointer");
+    unsigned v = 0, zero = 0;
+    PB_CUDA(cudaDeviceSynchronize());
+    PB_CUDA(cudaMemcpyFromSymbol(&v, g_vit_status, sizeof(v)));
+    PB_CUDA(cudaMemcpyToSymbol(g_vit_status, &zero, sizeof(zero)));
+    *status = v;
+    return PB_OK;
+}
+
+int32_t parpy_b200_viterbi_wait_probe(int32_t polls, void *stream) {
+    PB_REQUIRE(polls >= 0 && polls <= (1 << 20), "viterbi_wait_probe: polls=%d outside 0..2^20", polls);
+    vit_wait_probe<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(polls);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+}  // extern "C"

@@ -1,12 +1,22 @@
 """Multi-GPU sharding for the batched paths: one process per GPU, sequences (or
 row blocks) partitioned across ranks, every rank runs the single-GPU kernel on
-its shard, and one all-gather of the per-sequence results is the only
-collective. The reference has no multi-device code; this module is additive.
+its shard, and one all-gather of the per-sequence (per-row, per-non-zero)
+results is the only collective. The reference has no multi-device code; this
+module is additive.
 
-The partition is a deterministic function of the lengths, so every rank
-computes the same assignment without communicating.
+Every partition is a deterministic function of host-side sizes, so all ranks
+compute the same assignment without communicating. Nothing here hands another
+GPU's memory to a kernel: ranks exchange results through the process group only.
 """
+import heapq
+
 import numpy as np
+
+
+# ---- sequences (HMM forward / Viterbi) ------------------------------------------------
+def _longest_first(lens):
+    lens = np.asarray(lens, dtype=np.int64)
+    return lens, np.lexsort((np.arange(len(lens)), -lens))
 
 
 def lpt_partition(lens, world):
@@ -14,8 +24,7 @@ def lpt_partition(lens, world):
     (descending, index ascending on ties) are assigned one by one to the rank
     with the least total length (lowest rank on ties). Returns ``world`` sorted
     int64 index arrays."""
-    lens = np.asarray(lens, dtype=np.int64)
-    order = np.lexsort((np.arange(len(lens)), -lens))
+    lens, order = _longest_first(lens)
     load = np.zeros(world, dtype=np.int64)
     bins = [[] for _ in range(world)]
     for i in order:
@@ -25,12 +34,69 @@ def lpt_partition(lens, world):
     return [np.array(sorted(b), dtype=np.int64) for b in bins]
 
 
-def shard_sequences(seqs, rank, world):
+def cluster_schedule(lens, clusters):
+    """What the forward kernel's work queue does with one rank's sequences: the
+    resident clusters pop sequences longest first, each taking the next one when
+    it finishes its current one (time = number of steps). Returns the per-cluster
+    step totals."""
+    lens, order = _longest_first(lens)
+    clusters = max(1, min(int(clusters), max(len(lens), 1)))
+    heap = [(0, c) for c in range(clusters)]
+    load = np.zeros(clusters, dtype=np.int64)
+    for i in order:
+        t, c = heapq.heappop(heap)
+        load[c] = t + int(lens[i])
+        heapq.heappush(heap, (int(load[c]), c))
+    return load
+
+
+def cluster_balance(lens, clusters):
+    """(max, mean) of the per-cluster step totals of :func:`cluster_schedule`; a
+    rank's kernel time follows the maximum, its useful work the mean."""
+    load = cluster_schedule(lens, clusters)
+    return int(load.max()) if len(load) else 0, float(load.mean()) if len(load) else 0.0
+
+
+def balanced_partition(lens, world, clusters_per_rank):
+    """Partition for few sequences per resident cluster. A rank runs its shard on
+    ``clusters_per_rank`` persistent clusters, so its time is the largest
+    per-cluster total, not its total length divided by the cluster count. The
+    sequences are therefore packed longest-first into ``world * clusters_per_rank``
+    bins (least loaded bin first) and bin b goes to rank ``b % world``: every
+    rank receives bins of every size class, and its own longest-first queue
+    reproduces a packing of about the same height. Returns ``world`` sorted
+    int64 index arrays."""
+    lens, order = _longest_first(lens)
+    nbins = world * int(clusters_per_rank)
+    heap = [(0, b) for b in range(nbins)]
+    bins = [[] for _ in range(world)]
+    for i in order:
+        t, b = heapq.heappop(heap)
+        bins[b % world].append(int(i))
+        heapq.heappush(heap, (t + int(lens[i]), b))
+    return [np.array(sorted(b), dtype=np.int64) for b in bins]
+
+
+def partition(lens, world, clusters_per_rank=None):
+    """The sequence partition every rank derives: :func:`lpt_partition`, or, when
+    the number of resident clusters per rank is given, whichever of it and
+    :func:`balanced_partition` has the smaller largest per-cluster total over
+    all ranks (ties: LPT)."""
+    parts = lpt_partition(lens, world)
+    if clusters_per_rank is None or world == 1:
+        return parts
+    lens = np.asarray(lens, dtype=np.int64)
+    alt = balanced_partition(lens, world, clusters_per_rank)
+    height = lambda ps: max(cluster_balance(lens[p], clusters_per_rank)[0] for p in ps)
+    return alt if height(alt) < height(parts) else parts
+
+
+def shard_sequences(seqs, rank, world, clusters_per_rank=None):
     """The ``seqs`` dictionary restricted to this rank's sequences (host side;
     call before moving data to the device) and the global indices it holds."""
     import torch
     lens = seqs["lens"].cpu().numpy() if hasattr(seqs["lens"], "cpu") else np.asarray(seqs["lens"])
-    idx = lpt_partition(lens, world)[rank]
+    idx = partition(lens, world, clusters_per_rank)[rank]
     tidx = torch.from_numpy(idx)
     data = seqs["data"].cpu()[tidx] if hasattr(seqs["data"], "cpu") else torch.from_numpy(np.asarray(seqs["data"]))[tidx]
     llens = torch.from_numpy(lens)[tidx]
@@ -44,30 +110,169 @@ def shard_sequences(seqs, rank, world):
     return local, idx
 
 
-def gather_results(local_result, lens, group=None):
-    """All-gathers the per-sequence results of every rank and returns them in
-    the original sequence order. ``lens`` are the global lengths (host), from
-    which every rank re-derives the partition."""
+def _gather_blocks(local, sizes, group=None):
+    """All-gathers one block per rank (``sizes[r]`` leading entries of rank r's
+    block are valid) with a single collective: blocks are padded to the largest
+    size. Returns the list of valid blocks in rank order."""
     import torch
     import torch.distributed as td
     world = td.get_world_size(group)
-    parts = lpt_partition(lens, world)
-    width = max(len(p) for p in parts)
-    padded = torch.zeros(width, dtype=local_result.dtype, device=local_result.device)
-    padded[:local_result.numel()] = local_result
+    width = int(max(sizes)) if len(sizes) else 0
+    shape = (width,) + tuple(local.shape[1:])
+    padded = torch.zeros(shape, dtype=local.dtype, device=local.device)
+    padded[:local.shape[0]] = local
     gathered = [torch.empty_like(padded) for _ in range(world)]
     td.all_gather(gathered, padded, group=group)
+    return [gathered[r][:int(sizes[r])] for r in range(world)]
+
+
+def gather_results(local_result, lens, group=None, clusters_per_rank=None, parts=None):
+    """All-gathers the per-sequence results of every rank and returns them in
+    the original sequence order. ``lens`` are the global lengths (host), from
+    which every rank re-derives the partition (pass the same
+    ``clusters_per_rank`` as to :func:`shard_sequences`); a caller that gathers
+    repeatedly may pass the partition itself as ``parts``."""
+    import torch
+    import torch.distributed as td
+    world = td.get_world_size(group)
+    if parts is None:
+        parts = partition(lens, world, clusters_per_rank)
+    blocks = _gather_blocks(local_result, [len(p) for p in parts], group)
     out = torch.empty(sum(len(p) for p in parts), dtype=local_result.dtype, device=local_result.device)
     for r, p in enumerate(parts):
-        out[torch.from_numpy(p).to(out.device)] = gathered[r][:len(p)]
+        out[torch.from_numpy(p).to(out.device)] = blocks[r]
     return out
 
 
+# ---- row blocks (CSR SpMV, SDDMM) and vector slices (reductions) ------------------------
 def row_block_partition(row_ptr, world):
     """Contiguous row blocks with balanced non-zero counts for CSR operators:
-    returns ``world + 1`` row boundaries."""
-    row_ptr = np.asarray(row_ptr, dtype=np.int64)
-    nnz = int(row_ptr[-1])
-    targets = (np.arange(1, world, dtype=np.int64) * nnz) // world
-    cuts = np.searchsorted(row_ptr, targets, side="left")
-    return np.concatenate(([0], cuts, [len(row_ptr) - 1])).astype(np.int64)
+    returns ``world + 1`` row boundaries (NumPy int64). ``row_ptr`` may be a
+    NumPy array or a torch tensor on any device (only ``world - 1`` boundary
+    searches leave the device)."""
+    nrows = len(row_ptr) - 1
+    if hasattr(row_ptr, "is_cuda"):      # a torch tensor
+        import torch
+        nnz = int(row_ptr[-1])
+        targets = (torch.arange(1, world, dtype=torch.int64) * nnz) // world
+        cuts = torch.searchsorted(row_ptr.contiguous(), targets.to(row_ptr.device)).cpu().numpy()
+    else:
+        row_ptr = np.asarray(row_ptr, dtype=np.int64)
+        nnz = int(row_ptr[-1])
+        targets = (np.arange(1, world, dtype=np.int64) * nnz) // world
+        cuts = np.searchsorted(row_ptr, targets, side="left")
+    return np.concatenate(([0], cuts, [nrows])).astype(np.int64)
+
+
+def shard_csr(A, rank, world, rows_key="rows"):
+    """This rank's row block of a CSR dictionary (``values``, ``cols`` and the row
+    pointers under ``rows_key``, as test/test_spmv.py:20-27 and
+    benchmarks/sddmm.py:43-52 build them): row pointers rebased to start at 0,
+    the block's slices of ``values`` / ``cols``. Returns the local dictionary
+    (extra keys ``row_begin``, ``row_end``, ``nnz_begin``, ``nnz_end``) and the
+    ``world + 1`` row boundaries."""
+    ptrs = A[rows_key]
+    bounds = row_block_partition(ptrs, world)
+    lo, hi = int(bounds[rank]), int(bounds[rank + 1])
+    z0, z1 = int(ptrs[lo]), int(ptrs[hi])
+    local = {
+        rows_key: (ptrs[lo:hi + 1] - z0),
+        "cols": A["cols"][z0:z1],
+        "values": A["values"][z0:z1],
+        "nrows": hi - lo, "nnz": z1 - z0,
+        "row_begin": lo, "row_end": hi, "nnz_begin": z0, "nnz_end": z1,
+    }
+    if hasattr(local[rows_key], "contiguous"):
+        local = {k: (v.contiguous() if hasattr(v, "contiguous") else v) for k, v in local.items()}
+    return local, bounds
+
+
+def _default_spmv(A_local, x, y_local):
+    import parpy_b200 as parpy
+    from . import kernels
+    A = {k: A_local[k] for k in ("values", "rows", "cols", "nrows")}
+    kernels.spmv_row(A, x, y_local, opts=parpy.par({"row": parpy.threads(max(1, A_local["nrows"]))}))
+
+
+def spmv_sharded(A, x, y, group=None, local_op=None):
+    """``y += A @ x`` (test/test_spmv.py:12-18) with the rows of ``A`` split into
+    ``world`` contiguous blocks of about equal non-zero count. ``A``, ``x`` and
+    ``y`` are the full operands, identical on every rank; each rank runs the
+    single-GPU kernel on its block and one all-gather completes ``y`` in place
+    on every rank. ``local_op(A_local, x, y_local)`` replaces the native kernel
+    (the CPU test suite passes the oracle)."""
+    import torch
+    import torch.distributed as td
+    rank, world = td.get_rank(group), td.get_world_size(group)
+    local, bounds = shard_csr(A, rank, world)
+    y_local = y[local["row_begin"]:local["row_end"]].clone()
+    (local_op or _default_spmv)(local, x, y_local)
+    blocks = _gather_blocks(y_local, np.diff(bounds), group)
+    for r in range(world):
+        y[int(bounds[r]):int(bounds[r + 1])] = blocks[r]
+    return y
+
+
+def _default_sddmm(A_rows, B, C_local, D_local, alpha, beta):
+    import parpy_b200 as parpy
+    from . import kernels
+    C = {k: C_local[k] for k in ("crows", "rows", "cols", "values", "nnz")}
+    n = C_local["nrows"]
+    kernels.parpy_sddmm_csr_kernel(A_rows, B, C, D_local, n, alpha, beta,
+                                   opts=parpy.par({"i": parpy.threads(max(1, C_local["nnz"]))}))
+
+
+def sddmm_sharded(A, B, C, D, alpha, beta, group=None, local_op=None):
+    """``D[i] = alpha * A[row_i, :] . B[:, col_i] + beta * C.values[i]``
+    (benchmarks/sddmm.py:28-41) with the rows of the mask ``C`` (``crows``,
+    ``cols``, ``values``, ``rows``, ``nnz``) split into contiguous blocks of about
+    equal non-zero count. Full operands on every rank; each rank computes the
+    values of its block's non-zeros (and their row indices, which the reference's
+    kernel also writes into ``C['rows']``) and one all-gather each completes
+    ``D`` and ``C['rows']`` in place."""
+    import torch
+    import torch.distributed as td
+    rank, world = td.get_rank(group), td.get_world_size(group)
+    local, bounds = shard_csr(C, rank, world, rows_key="crows")
+    lo, hi = local["row_begin"], local["row_end"]
+    local["rows"] = torch.zeros(local["nnz"], dtype=torch.int64, device=D.device)
+    D_local = torch.zeros(local["nnz"], dtype=D.dtype, device=D.device)
+    (local_op or _default_sddmm)(A[lo:hi].contiguous(), B, local, D_local, alpha, beta)
+    crows = C["crows"]
+    edges = [int(crows[int(b)]) for b in bounds]
+    sizes = np.diff(edges)
+    d_blocks = _gather_blocks(D_local, sizes, group)
+    r_blocks = _gather_blocks(local["rows"] + lo, sizes, group)
+    for r in range(world):
+        D[edges[r]:edges[r + 1]] = d_blocks[r]
+        C["rows"][edges[r]:edges[r + 1]] = r_blocks[r]
+    return D
+
+
+def slice_bounds(n, world, align=4):
+    """``world + 1`` boundaries of equal contiguous slices of an ``n``-vector,
+    multiples of ``align`` elements (16 bytes of float32) except the last."""
+    per = -(-n // world)
+    per = -(-per // align) * align
+    return np.minimum(np.arange(world + 1, dtype=np.int64) * per, n)
+
+
+def _default_sum_max(v_local):
+    from . import kernels
+    return kernels.sum_max(v_local)
+
+
+def sum_max_sharded(v_local, group=None, local_op=None):
+    """Sum and maximum of a float32 vector whose slices live one per rank: the
+    single-GPU one-pass kernel on the local slice, one all-gather of the
+    ``(sum, max)`` pairs, partial sums added in rank order (so every rank holds
+    the same bits). Returns a 2-element tensor on ``v_local``'s device."""
+    import torch
+    import torch.distributed as td
+    world = td.get_world_size(group)
+    pair = (local_op or _default_sum_max)(v_local).reshape(1, 2)
+    parts = torch.cat(_gather_blocks(pair, [1] * world, group), dim=0)
+    total = parts[0, 0].clone()
+    for r in range(1, world):
+        total = total + parts[r, 0]
+    return torch.stack([total, parts[:, 1].max()])

@@ -138,31 +138,84 @@ def read_trellis_inputs(model_path, signals_path):
     return read_model(model_path), read_signals(signals_path)
 
 
-def viterbi(hmm, seqs, batch_size=1024, batch_overlap=128):
+def forward_status():
+    """Reads and clears the forward kernels' device status word (synchronises the
+    device). Returns ``{"length_clamped": bool, "observation_clamped": bool}``:
+    a sequence length outside [1, maxlen], or an observation byte that is not a
+    row of ``output_prob``, was met (and clamped) by a call since the last read."""
+    import ctypes
+    from . import _native
+    st = ctypes.c_uint32(0)
+    _native.check(_native.lib().parpy_b200_forward_status(ctypes.byref(st)), "forward_status")
+    return {"length_clamped": bool(st.value & 1), "observation_clamped": bool(st.value & 2)}
+
+
+def viterbi_status():
+    """Reads and clears the Viterbi kernel's device status word (synchronises the
+    device). Returns ``{"wait_timed_out": bool, "observation_clamped": bool}``."""
+    import ctypes
+    from . import _native
+    st = ctypes.c_uint32(0)
+    _native.check(_native.lib().parpy_b200_viterbi_status(ctypes.byref(st)), "viterbi_status")
+    return {"wait_timed_out": bool(st.value & 1), "observation_clamped": bool(st.value & 2)}
+
+
+def viterbi(hmm, seqs, batch_size=1024, batch_overlap=128, check=True):
     """Most likely state path of every sequence (windowed Viterbi with the
     semantics of benchmarks/7mer/trellis.py:25-83 and benchmarks/7mer/hmm.cu).
-    ``hmm`` and ``seqs`` are the dictionaries ``forward_kernel`` takes, on the
-    device. Returns a uint32-valued int64 CUDA tensor [B, maxlen] whose row i holds
-    ``lens[i]`` decoded states, and the lengths; use ``viterbi_paths`` for a list
-    of per-sequence NumPy arrays."""
-    import ctypes
+    ``hmm`` and ``seqs`` are the dictionaries ``forward_kernel`` takes, as
+    contiguous CUDA tensors on the current device (float32 tables, int8/uint8
+    observations). Returns an int32 CUDA tensor [B, maxlen] whose row i holds
+    ``lens[i]`` decoded states (read it as uint32: state = layer * K + kmer), and
+    the int64 lengths; use ``viterbi_paths`` for a list of per-sequence NumPy
+    arrays. With ``check`` (default) the call waits for the kernel and raises
+    ``RuntimeError`` if one of its bounded waits ran out, in which case the paths
+    are not valid; ``check=False`` leaves the call asynchronous and the status to
+    :func:`viterbi_status`. Back-pointer scratch of up to 3 GiB per (device,
+    stream) is kept by the library between calls."""
     import torch
     from . import _native
     from .buffer import from_array
-    from .ops import scalar
-    n = int(scalar(from_array(hmm["num_states"]), "num_states")) if hasattr(hmm["num_states"], "shape") else int(hmm["num_states"])
-    data, lens = seqs["data"], seqs["lens"]
+    from .ops import current_stream, ptr, scalar, tensor
+    as_scalar = lambda v, what: scalar(from_array(v), what) if hasattr(v, "shape") else v
+    n = int(as_scalar(hmm["num_states"], "hmm['num_states']"))
+    gamma = float(as_scalar(hmm["gamma"], "hmm['gamma']"))
+    synth = float(as_scalar(hmm["synthetic_248"], "hmm['synthetic_248']"))
+    f32 = torch.float32
+
+    def dev(v, what, dtype, ndim):
+        if not (isinstance(v, torch.Tensor) and v.is_cuda):
+            raise TypeError(f"viterbi: {what} must be a CUDA tensor")
+        if not v.is_contiguous():
+            raise ValueError(f"viterbi: {what} must be contiguous")
+        return tensor(from_array(v), what, dtype, ndim)
+    init = dev(hmm["initial_prob"], "hmm['initial_prob']", f32, 1)
+    outp = dev(hmm["output_prob"], "hmm['output_prob']", f32, 2)
+    t1 = dev(hmm["trans1"], "hmm['trans1']", f32, 2)
+    t2 = dev(hmm["trans2"], "hmm['trans2']", f32, 1)
+    data = dev(seqs["data"], "seqs['data']", (torch.int8, torch.uint8), 2)
+    lens = dev(seqs["lens"], "seqs['lens']", (torch.int64, torch.int32), 1)
+    if n < 64 or n % 64 != 0:
+        raise RuntimeError(f"viterbi: num_states={n} must be a positive multiple of 64")
+    k = n // 16
+    if init.shape[0] != n or tuple(t1.shape) != (k, 4) or t2.shape[0] != 16 or outp.shape[1] != k:
+        raise RuntimeError(f"viterbi: table shapes {tuple(init.shape)}, {tuple(t1.shape)}, {tuple(t2.shape)}, "
+                           f"{tuple(outp.shape)} do not match num_states={n}")
+    batch, maxlen = data.shape
+    if lens.shape[0] != batch:
+        raise RuntimeError(f"viterbi: lens {tuple(lens.shape)} does not match data {tuple(data.shape)}")
     if lens.dtype != torch.int64:
         lens = lens.to(torch.int64)
-    batch, maxlen = data.shape
     out = torch.zeros((batch, maxlen), dtype=torch.int32, device=data.device)
-    P = ctypes.c_void_p
-    rc = _native.lib().parpy_b200_viterbi(
-        float(hmm["gamma"]), P(hmm["initial_prob"].data_ptr()), n, P(hmm["output_prob"].data_ptr()),
-        float(hmm["synthetic_248"]), P(hmm["trans1"].data_ptr()), P(hmm["trans2"].data_ptr()),
-        P(data.data_ptr()), P(lens.data_ptr()), maxlen, batch, batch_size, batch_overlap,
-        P(out.data_ptr()), maxlen, P(torch.cuda.current_stream().cuda_stream))
+    n_obs = int(outp.shape[0])
+    rc = _native.lib().parpy_b200_viterbi_ex(
+        gamma, ptr(init), n, ptr(outp), n_obs if n_obs <= 256 else 0, synth, ptr(t1), ptr(t2), ptr(data), ptr(lens),
+        maxlen, batch, batch_size, batch_overlap, ptr(out), maxlen, current_stream())
     _native.check(rc, "viterbi")
+    if check:
+        st = viterbi_status()
+        if st["wait_timed_out"]:
+            raise RuntimeError("viterbi: a wait inside the kernel ran out; the decoded paths are not valid")
     return out, lens
 
 

@@ -171,9 +171,10 @@ def _forward_call(opts, hmm, seqs, result, alpha1, alpha2):
     if lens.dtype != torch.int64:
         lens = lens.to(torch.int64)
     flags = _forward_flags(opts)
-    rc = _native.lib().parpy_b200_forward(
-        gamma, ptr(init), n, ptr(outp), synth, ptr(t1), ptr(t2), ptr(data), ptr(lens), maxlen,
-        batch, ptr(res), ptr(a1), ptr(a2), flags, current_stream())
+    n_obs = int(outp.shape[0])
+    rc = _native.lib().parpy_b200_forward_ex(
+        gamma, ptr(init), n, ptr(outp), n_obs if n_obs <= 256 else 0, synth, ptr(t1), ptr(t2), ptr(data),
+        ptr(lens), maxlen, batch, ptr(res), ptr(a1), ptr(a2), flags, current_stream())
     _native.check(rc, "forward_kernel")
 
 
@@ -226,7 +227,9 @@ def _reduce_call(op, full):
         xt = tensor(x, "x", torch.float32, 2)
         ot = tensor(out, "out", torch.float32, 1)
         n = int(scalar(N, "N"))
-        if xt.shape[0] != n or ot.shape[0] < (1 if full else n):
+        # row / axis reductions write all of `out` (a host `out` is staged without its old
+        # contents and copied back whole), so its length must be N exactly
+        if xt.shape[0] != n or (ot.shape[0] < 1 if full else ot.shape[0] != n):
             raise RuntimeError(f"reduce: x {tuple(xt.shape)} / out {tuple(ot.shape)} do not match N={n}")
         rows, width = (1, xt.numel()) if full else (n, xt.shape[1])
         _native.check(_native.lib().parpy_b200_reduce_rows(op, ptr(xt), ptr(ot), rows, width,

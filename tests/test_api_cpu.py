@@ -177,8 +177,9 @@ def test_hdf5_reader_reproduces_the_committed_fixtures():
     # the minimal HDF5 reader + the loader steps of benchmarks/forward.py:40-56 against tests/golden/*.npz
     import os
     import sys
-    ref = os.environ.get("PARPY_REFERENCE_ROOT", "/root/reference")
-    if not os.path.isdir(os.path.join(ref, "test", "data")):
+    from oracle import build as oracle_build
+    ref = oracle_build.reference_root()
+    if not ref or not os.path.isdir(os.path.join(ref, "test", "data")):
         pytest.skip("reference checkout with test/data not present")
     from conftest import GOLDEN
     sys.path.insert(0, GOLDEN)

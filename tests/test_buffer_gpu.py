@@ -64,3 +64,49 @@ def test_round_trip_and_write_back_on_release():
     del buf
     assert np.array_equal(host, np.full(8, 3.0, dtype=np.float32))
     parpy.sync(CUDA)
+
+
+class ForeignDeviceArray:
+    """A device array that is not a torch tensor: only ``__cuda_array_interface__``
+    (version 3), the way a CuPy array presents itself (test/test_cupy.py). Backed
+    by a torch allocation that it keeps alive."""
+
+    def __init__(self, tensor, readonly=False, strides=None):
+        self._keep = tensor
+        typestr = {torch.float32: "<f4", torch.int64: "<i8", torch.int8: "|i1"}[tensor.dtype]
+        self.__cuda_array_interface__ = {
+            "shape": tuple(tensor.shape), "typestr": typestr, "data": (tensor.data_ptr(), readonly),
+            "strides": strides, "version": 3,
+        }
+
+
+def test_foreign_cuda_array_interface_is_used_without_a_copy():
+    # the reference's add(a, b, c, N) test with CuPy arrays (test/test_cupy.py:9-24), on this
+    # package's row-sum kernel: inputs and output are foreign device arrays
+    base = torch.randn(64, 96, device="cuda")
+    out = torch.zeros(64, device="cuda")
+    x, o = ForeignDeviceArray(base), ForeignDeviceArray(out)
+    buf = parpy.buffer.from_array(x, CUDA)
+    assert buf._get_ptr() == base.data_ptr() and buf.src is None and buf.shape == (64, 96)
+    from parpy_b200 import kernels
+    kernels.sum_rows(x, o, 64, opts=parpy.par({"N": parpy.threads(64)}))
+    torch.cuda.synchronize()
+    assert torch.allclose(out, base.sum(dim=1), atol=1e-4)          # written in place, no staging
+    # read-only and strided memory are rejected as the reference does (python/parpy/buffer.py:15-31)
+    with pytest.raises(ValueError, match="read-only"):
+        parpy.buffer.from_array(ForeignDeviceArray(base, readonly=True), CUDA)
+    with pytest.raises(ValueError, match="contiguous"):
+        parpy.buffer.from_array(ForeignDeviceArray(base.t(), strides=(4, 384)), CUDA)
+
+
+def test_forward_accepts_foreign_device_arrays():
+    from parpy_b200 import hmm as hmm_mod, synthetic
+    hmm, seqs = synthetic.hmm_model(4, seed=3), synthetic.hmm_sequences(6, 3, 40, seed=4)
+    dh, ds = hmm_mod.to_device(hmm), hmm_mod.to_device(seqs)
+    want = hmm_mod.forward_parpy(dh, ds)
+    wrap = lambda d: {k: (ForeignDeviceArray(v) if isinstance(v, torch.Tensor) and v.dim() > 0 else v)
+                      for k, v in d.items()}
+    result = torch.zeros(6, device="cuda")
+    hmm_mod.forward_kernel(wrap(dh), wrap(ds), ForeignDeviceArray(result), None, None,
+                           opts=parpy.par({"inst": parpy.threads(6)}))
+    assert torch.equal(result, want)

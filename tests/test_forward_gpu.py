@@ -52,7 +52,7 @@ def test_reference_shaped_entries_on_default_stream(native, entry):
 
 
 def test_5mer_config_against_oracle(native, oracle_mod):
-    # BASELINE config: 5mer, 100 sequences of T=2000 (oracle on a subset to keep CPU time bounded)
+    # 5mer benchmark workload: 100 sequences of T=2000 (oracle on a subset to keep CPU time bounded)
     from parpy_b200 import synthetic
     hmm = synthetic.hmm_model(5)
     seqs = synthetic.hmm_sequences(100, 2000, 2000)
@@ -88,7 +88,7 @@ def test_7mer_against_oracle_with_final_alpha(native, oracle_mod):
 
 
 def test_7mer_full_config_properties(native):
-    # BASELINE config: 500 sequences, lengths uniform in [1000, 4000]; size-independent checks.
+    # 7mer benchmark workload: 500 sequences, lengths uniform in [1000, 4000]; size-independent checks.
     from parpy_b200 import synthetic
     hmm = synthetic.hmm_model(7)
     seqs = synthetic.hmm_sequences(500, 1000, 4000)
@@ -115,6 +115,44 @@ def test_7mer_full_config_properties(native):
     # the five-term form agrees with the factored form far inside the tolerance
     rc, res5, _, _ = cabi_forward(native, dh, to_dev(sub), FLAGS["five_term"])
     assert max_rel(res3.cpu().numpy(), res5.cpu().numpy()) <= REL_ORACLE
+
+
+def test_7mer_benchmark_batch_full_length_against_oracle(native, oracle_mod, capsys):
+    # The benchmark's own batch (500 sequences, lengths uniform in [1000, 4000], seed 1234) through
+    # the default kernel; the longest, the shortest and six more sequences are scored at full length
+    # by the CPU oracle (benchmarks/forward.py:103-158 restated). fp32 log-space rounding drifts with
+    # length, so this is the check at the lengths the throughput figure is quoted on. Tolerance of
+    # the reference's own test: test/test_forward.py:176-178 (rtol 1e-5).
+    from parpy_b200 import synthetic
+    hmm = synthetic.hmm_model(7)
+    seqs = synthetic.hmm_sequences(500, 1000, 4000)
+    lens = seqs["lens"].numpy()
+    rest = np.random.default_rng(7).permutation(500)
+    pick = [int(np.argmax(lens)), int(np.argmin(lens))]
+    pick += [int(i) for i in rest if int(i) not in pick][:6]
+    pick = np.array(sorted(pick))
+    sub = {"data": seqs["data"][pick].contiguous(), "lens": seqs["lens"][pick].contiguous(),
+           "maxlen": seqs["maxlen"], "num_instances": torch.tensor(len(pick))}
+    exp = oracle_mod.forward(hmm, sub)
+    dh = to_dev(hmm)
+    rc, res, _, _ = cabi_forward(native, dh, to_dev(seqs))
+    assert rc == 0, native.error_message()
+    got = res.cpu().numpy()
+    assert np.isfinite(got).all()
+    err = {"default": max_rel(got[pick], exp)}
+    ds = to_dev(sub)
+    for name in ("five_term", "scaled"):
+        rc, r, _, _ = cabi_forward(native, dh, ds, FLAGS[name])
+        assert rc == 0, native.error_message()
+        err[name] = max_rel(r.cpu().numpy(), exp)
+    with capsys.disabled():
+        print("\n7mer full-length parity (max rel vs oracle, lengths %d..%d): %s"
+              % (lens[pick].min(), lens[pick].max(), ", ".join(f"{k} {v:.2e}" for k, v in err.items())))
+    assert err["default"] <= REL_ORACLE
+    assert err["five_term"] <= REL_ORACLE
+    # the scaled kernel follows exact arithmetic; its distance from the fp32 oracle is the
+    # oracle's own accumulated rounding, which the library target bounds
+    assert err["scaled"] <= REL_TARGET
 
 
 def test_padding_is_never_used_and_uint8_is_accepted(native):
@@ -351,6 +389,34 @@ def test_forward_python_surface(device, nthreads):
     assert not a1.any() and not a2.any()        # resident kernel: scratch untouched
 
 
+def test_tuner_loop_of_the_reference_benchmark_gives_one_answer():
+    # benchmarks/forward.py:200-218 (ParPyTuned): the benchmark times forward_parpy(hmm, seqs, nthreads)
+    # for nthreads = 2^10 .. 2^18 <= num_states and keeps the fastest. The native kernel picks its own
+    # mapping, so every setting must return the same log-likelihoods; 5-mer workload (16384 states).
+    import statistics
+    from parpy_b200 import hmm as hmm_mod, synthetic
+    hmm = hmm_mod.to_device(synthetic.hmm_model(5))
+    seqs = hmm_mod.to_device(synthetic.hmm_sequences(100, 200, 200))
+    best_time, best_nthreads, results = float("inf"), 0, {}
+    for nthreads in [2 ** n for n in range(10, 19) if 2 ** n <= int(hmm["num_states"])]:
+        times = []
+        for run in range(1 + 5):                      # nwarmup=1, nruns=5
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            results[nthreads] = hmm_mod.forward_parpy(hmm, seqs, nthreads)
+            e1.record()
+            torch.cuda.synchronize()
+            if run:
+                times.append(e0.elapsed_time(e1))
+        if statistics.mean(times) < best_time:
+            best_time, best_nthreads = statistics.mean(times), nthreads
+    assert sorted(results) == [1024, 2048, 4096, 8192, 16384] and best_nthreads in results
+    first = results[1024]
+    assert torch.isfinite(first).all()
+    for r in results.values():
+        assert torch.equal(r, first)
+
+
 def test_forward_python_surface_numpy_and_write_alpha(oracle_mod):
     import parpy_b200 as parpy
     from parpy_b200.hmm import forward_kernel
@@ -508,3 +574,85 @@ def test_large_batches_long_sequences_and_side_streams(native, oracle_mod):
     torch.cuda.synchronize()
     assert rc1 == rc2 == rc3 == rc4 == 0
     assert torch.equal(r1, e1) and torch.equal(r2, e2)
+
+
+# ---- the static schedule and the observation check --------------------------------------------------------
+def _schedule(native, lens, clusters):
+    d = lens.cuda()
+    out = torch.full((len(lens),), -1, dtype=torch.int32, device="cuda")
+    rc = native.lib().parpy_b200_forward_schedule(ctypes.c_void_p(d.data_ptr()), len(lens), clusters,
+                                                  ctypes.c_void_p(out.data_ptr()),
+                                                  ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0, native.error_message()
+    return out.cpu().numpy()
+
+
+@pytest.mark.parametrize("batch,lo,hi,clusters", [(500, 1000, 4000, 33), (62, 1000, 4000, 33), (4096, 1, 300, 37),
+                                                  (100, 2000, 2000, 148), (7, 5, 9, 33), (1000, 10, 100000, 16)])
+def test_static_schedule_is_a_partition_and_beats_greedy_packing(native, batch, lo, hi, clusters):
+    from parpy_b200 import dist, synthetic
+    lens = synthetic.hmm_sequences(batch, lo, min(hi, 300), seed=batch)["lens"] if hi > 4000 else \
+        synthetic.hmm_sequences(batch, lo, hi, seed=batch)["lens"]
+    if hi > 4000:   # a heavy tail: a few very long sequences among short ones
+        lens = lens.clone()
+        lens[::97] = hi
+    cl = _schedule(native, lens, clusters)
+    used = min(clusters, batch)
+    assert cl.min() >= 0 and cl.max() < used                       # every sequence has exactly one cluster
+    loads = np.bincount(cl, weights=lens.numpy().astype(np.float64), minlength=used)
+    greedy = dist.cluster_schedule(lens.numpy(), clusters)          # longest first to the least loaded
+    assert loads.max() <= greedy.max()
+    assert np.array_equal(cl, _schedule(native, lens, clusters))   # deterministic
+    if batch == 500:
+        # the benchmark batch on its 33 clusters: greedy leaves 2 %, the repaired schedule under 0.1 %
+        assert loads.max() / loads.mean() < 1.001 < greedy.max() / greedy.mean()
+
+
+def test_results_do_not_depend_on_the_number_of_resident_clusters(native, monkeypatch):
+    from parpy_b200 import synthetic
+    hmm, seqs = to_dev(synthetic.hmm_model(6, seed=2)), to_dev(synthetic.hmm_sequences(90, 1, 50, seed=3))
+    rc, base, _, _ = cabi_forward(native, hmm, seqs)
+    assert rc == 0, native.error_message()
+    for n in ("1", "2", "7"):
+        monkeypatch.setenv("PARPY_B200_FWD_CLUSTERS", n)
+        for flags in (0, FLAGS["scaled"]):
+            rc, res, _, _ = cabi_forward(native, hmm, seqs, flags)
+            assert rc == 0, native.error_message()
+            if flags == 0:
+                assert torch.equal(res, base)
+            else:
+                assert max_rel(res.cpu().numpy(), base.cpu().numpy()) <= REL_TARGET
+
+
+def test_out_of_range_observations_are_clamped_and_flagged(native):
+    # A byte that is not a row of the emission table (>= n_obs) inside a sequence: with n_obs given
+    # the kernels read row n_obs - 1 instead of memory past the table and raise status bit 1.
+    import parpy_b200 as parpy
+    from parpy_b200 import hmm as hmm_mod, synthetic
+    for k in (3, 5, 6):
+        hmm = synthetic.hmm_model(k, seed=k)
+        seqs = synthetic.hmm_sequences(5, 30, 60, seed=k + 1, pad_value=0)
+        good = {k2: (v.clone() if isinstance(v, torch.Tensor) else v) for k2, v in seqs.items()}
+        good["data"][2, 17] = 100                                 # the last valid level
+        bad = {k2: (v.clone() if isinstance(v, torch.Tensor) else v) for k2, v in seqs.items()}
+        bad["data"][2, 17] = -56                                  # byte 200 on the host side of a staged array
+        hmm_mod.forward_status()
+        opts = parpy.par({"inst": parpy.threads(5)})
+        want = torch.zeros(5)
+        hmm_mod.forward_kernel(hmm, good, want, None, None, opts=opts)
+        assert hmm_mod.forward_status() == {"length_clamped": False, "observation_clamped": False}
+        got = torch.zeros(5)
+        hmm_mod.forward_kernel(hmm, bad, got, None, None, opts=opts)
+        assert hmm_mod.forward_status() == {"length_clamped": False, "observation_clamped": True}
+        assert torch.equal(got, want)
+        assert hmm_mod.forward_status() == {"length_clamped": False, "observation_clamped": False}
+    # Viterbi: same rule, its own status word
+    hmm = hmm_mod.to_device(synthetic.hmm_model(5, seed=9))
+    good = hmm_mod.to_device(good)
+    bad = hmm_mod.to_device(bad)
+    hmm_mod.viterbi_status()
+    want, _ = hmm_mod.viterbi(hmm, good, 32, 8)
+    assert hmm_mod.viterbi_status() == {"wait_timed_out": False, "observation_clamped": False}
+    got, _ = hmm_mod.viterbi(hmm, bad, 32, 8, check=False)
+    assert hmm_mod.viterbi_status() == {"wait_timed_out": False, "observation_clamped": True}
+    assert torch.equal(got, want)

@@ -345,7 +345,61 @@ def test_compile_string_round_trip(oracle_mod, tmp_path, monkeypatch):
     assert np.array_equal(y, 2.0 * a + 1.0)
 
 
-# ---- the BASELINE configurations at full size ---------------------------------------------------------
+# ---- row-block sharding on one GPU: the shards of every rank run one after another -------------------------
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_row_block_shards_reassemble_the_unsharded_result(oracle_mod, world):
+    # What each rank of an N-GPU job computes (parpy_b200.dist.shard_csr + the single-GPU kernel on
+    # the block), run here shard after shard on one GPU and put together without the collective.
+    from parpy_b200 import dist
+    A = synthetic.zipf_csr(20000, 20000, mean_nnz=16, cap=1024, seed=9)
+    g = torch.Generator().manual_seed(10)
+    x = torch.randn(20000, generator=g)
+    Ad = {k: (v.cuda() if isinstance(v, torch.Tensor) else v) for k, v in A.items()}
+    xd = x.cuda()
+    y_full = torch.zeros(20000, device="cuda")
+    kernels.spmv_row(Ad, xd, y_full, opts=opts(row=parpy.threads(20000)))
+    y_parts = torch.zeros(20000, device="cuda")
+    for r in range(world):
+        local, bounds = dist.shard_csr(Ad, r, world)
+        assert int(local["rows"][0]) == 0 and int(local["rows"][-1]) == local["nnz"]
+        y_local = y_parts[local["row_begin"]:local["row_end"]].clone()
+        dist._default_spmv(local, xd, y_local)
+        y_parts[local["row_begin"]:local["row_end"]] = y_local
+    exp = oracle_mod.spmv(A, x, np.zeros(20000, dtype=np.float32))
+    assert np.allclose(y_parts.cpu().numpy(), exp, atol=1e-4, rtol=1e-4)
+    # rows are summed in chunks of non-zeros whose cuts move with the block's first non-zero
+    assert np.allclose(y_parts.cpu().numpy(), y_full.cpu().numpy(), atol=1e-5, rtol=1e-5)
+
+    # SDDMM: every non-zero is an independent dot product, so the shards agree bit for bit
+    N, ncols, K = 1024, 1536, 64
+    C = synthetic.uniform_csr(N, ncols, 0.02, seed=11)
+    Am, Bm = torch.randn(N, K, generator=g).cuda(), torch.randn(K, ncols, generator=g).cuda()
+    Cd = {"crows": C["crows"].cuda(), "rows": torch.zeros(C["nnz"], dtype=torch.int64, device="cuda"),
+          "cols": C["cols"].cuda(), "values": C["values"].cuda(), "nnz": C["nnz"]}
+    D_full = torch.empty(C["nnz"], device="cuda")
+    kernels.parpy_sddmm_csr_kernel(Am, Bm, Cd, D_full, N, 1.5, 2.0, opts=opts(nnz=parpy.threads(C["nnz"])))
+    D_parts = torch.zeros(C["nnz"], device="cuda")
+    rows_parts = torch.zeros(C["nnz"], dtype=torch.int64, device="cuda")
+    for r in range(world):
+        local, bounds = dist.shard_csr(Cd, r, world, rows_key="crows")
+        local["rows"] = torch.zeros(local["nnz"], dtype=torch.int64, device="cuda")
+        D_local = torch.zeros(local["nnz"], device="cuda")
+        dist._default_sddmm(Am[local["row_begin"]:local["row_end"]].contiguous(), Bm, local, D_local, 1.5, 2.0)
+        D_parts[local["nnz_begin"]:local["nnz_end"]] = D_local
+        rows_parts[local["nnz_begin"]:local["nnz_end"]] = local["rows"] + local["row_begin"]
+    assert torch.equal(D_parts, D_full)
+    assert torch.equal(rows_parts, Cd["rows"])
+
+    # sum and max over slices: the maximum is exact, the sum agrees to fp32 summation order
+    v = torch.randn(1 << 22, generator=g).cuda()
+    whole = kernels.sum_max(v).cpu().numpy()
+    sb = dist.slice_bounds(v.numel(), world)
+    pairs = [kernels.sum_max(v[int(sb[r]):int(sb[r + 1])]).cpu().numpy() for r in range(world)]
+    assert max(p[1] for p in pairs) == whole[1]
+    assert abs(sum(float(p[0]) for p in pairs) - float(whole[0])) <= 1e-4 * float(v.abs().sum())
+
+
+# ---- the benchmark workloads at full size ------------------------------------------------------------
 def test_full_size_sddmm_config(oracle_mod):
     # CSR mask 8192 x 8192 at 1 % density, A [8192, 64], B [64, 8192]; (alpha, beta) = (1, 0) and (1.5, 2)
     N, K = 8192, 64

@@ -192,3 +192,27 @@ def test_viterbi_argument_checks(native):
     hmm5 = _dev(synthetic.hmm_model(5))
     with pytest.raises(RuntimeError, match="window of"):
         hmm_mod.viterbi(hmm5, seqs, batch_size=8, batch_overlap=8)
+
+
+@pytest.mark.gpu
+def test_a_wait_that_gives_up_reaches_the_host():
+    # The decoding kernel's waits for another CTA's data are bounded; when one runs out the kernel
+    # raises a status bit instead of hanging. Here a probe CTA waits on a barrier nothing completes
+    # (no other CTA involved, nothing in flight), gives up after 64 polls, and the host sees the bit.
+    import ctypes
+    from parpy_b200 import _native, hmm as hmm_mod
+    hmm_mod.viterbi_status()
+    assert hmm_mod.viterbi_status() == {"wait_timed_out": False, "observation_clamped": False}
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    _native.check(_native.lib().parpy_b200_viterbi_wait_probe(64, stream), "wait_probe")
+    assert hmm_mod.viterbi_status() == {"wait_timed_out": True, "observation_clamped": False}
+    assert hmm_mod.viterbi_status() == {"wait_timed_out": False, "observation_clamped": False}   # read-and-clear
+    # a decode that follows is healthy, and hmm.viterbi raises when the bit is up after its own call
+    hmm = hmm_mod.to_device(synthetic.hmm_model(5, seed=1))
+    seqs = hmm_mod.to_device(synthetic.hmm_sequences(3, 20, 40, seed=2))
+    out, _ = hmm_mod.viterbi(hmm, seqs, 16, 4)
+    assert int(out.max()) < 16 * 1024
+    _native.check(_native.lib().parpy_b200_viterbi_wait_probe(0, stream), "wait_probe")
+    with pytest.raises(RuntimeError, match="wait inside the kernel ran out"):
+        hmm_mod.viterbi(hmm, seqs, 16, 4)
+    hmm_mod.viterbi(hmm, seqs, 16, 4)
