@@ -870,14 +870,33 @@ __device__ __forceinline__ float2 ex2_poly2_negabs(float2 t2) {
                        __int_as_float(__float_as_int(p.y) + (__float_as_int(r.y) << 23)));
 }
 
+// ln(1 + x) for x in [0, 1] on the FMA pipe: x * P(x), P of degree 6 (minimax on [0, 1], max
+// absolute error 3.3e-7 evaluated in fp32; lg2.approx is specified to 2.4e-7). Folded into the
+// final multiply-add of the log-sum-exp, it costs five packed instructions more than the
+// MUFU form and takes two MUFU operations per pair off the pipe that bounds the kernel.
+__device__ __forceinline__ float2 log1p_poly2_times(float2 x) {
+    float2 p = dup2(0.01076451875269413f);
+    p = fma2(p, x, dup2(-0.05514521896839142f));
+    p = fma2(p, x, dup2(0.1346745640039444f));
+    p = fma2(p, x, dup2(-0.22589802742004395f));
+    p = fma2(p, x, dup2(0.3282422125339508f));
+    p = fma2(p, x, dup2(-0.4994717836380005f));
+    p = fma2(p, x, dup2(0.999981164932251f));
+    return p;   // ln(1 + x) = x * p
+}
+
 // log(exp(u) + exp(v)) for two states, every half rounded exactly like lse2_sel;
-// (-inf, -inf) gives -inf.
-__device__ __forceinline__ float2 lse2_pair(bool poly, float2 u, float2 v) {
+// (-inf, -inf) gives -inf. `lgpoly`: the logarithm is the polynomial above.
+__device__ __forceinline__ float2 lse2_pair(bool poly, float2 u, float2 v, bool lgpoly = false) {
     const float2 mx = max2(u, v);
     const float2 t = mul2(sub2(u, v), dup2(kLog2e));   // |t| = |u - v| * log2(e)
     float2 ex;
     if (poly) ex = ex2_poly2_negabs(t);
     else ex = make_float2(pb::ex2_approx(-fabsf(t.x)), pb::ex2_approx(-fabsf(t.y)));
+    if (lgpoly) {
+        const float2 r = fma2(ex, log1p_poly2_times(ex), mx);
+        return poly ? r : make_float2(fmaxf(r.x, -INFINITY), fmaxf(r.y, -INFINITY));
+    }
     const float2 s = add2(ex, dup2(1.0f));
     const float2 r = fma2(make_float2(pb::lg2_approx(s.x), pb::lg2_approx(s.y)), dup2(kLn2), mx);
     // the polynomial path maps the NaN of (-inf) - (-inf) to a zero term by itself
@@ -898,7 +917,8 @@ __device__ __forceinline__ float2 lse4_pair(float2 p0, float2 p1, float2 p2, flo
     return make_float2(fmaxf(r.x, -INFINITY), fmaxf(r.y, -INFINITY));
 }
 
-template <unsigned POLY_MASK>   // bit d set: layer d evaluates its exponential on the FMA pipe
+// POLY_MASK bit d: layer d evaluates its exponential on the FMA pipe; LG_MASK bit d: its logarithm.
+template <unsigned POLY_MASK, unsigned LG_MASK = 0u>
 __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p) {
     extern __shared__ __align__(16) float smem_dyn[];
     __shared__ int s_seq;
@@ -994,7 +1014,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
                 const float2 w = s_t2[0];
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
-                    a[0][h] = add2(lse2_pair((POLY_MASK & 1u) != 0, add2(w, q[h]), a[1][h]), ev[h]);
+                    a[0][h] = add2(lse2_pair((POLY_MASK & 1u) != 0, add2(w, q[h]), a[1][h], (LG_MASK & 1u) != 0), ev[h]);
             }
             st_cluster_v4(dst, a[0][0].x, a[0][0].y, a[0][1].x, a[0][1].y);
             cluster_arrive();
@@ -1003,16 +1023,16 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
                 const float2 w = s_t2[d];
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
-                    a[d][h] = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[h]), a[d + 1][h]), ev[h]);
+                    a[d][h] = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[h]), a[d + 1][h], ((LG_MASK >> d) & 1u) != 0), ev[h]);
             }
             // layers 7..15: the "next layer" operand comes from shared memory
             float4 nxt = As[tid];  // layer 8 (old)
             {
                 const float2 w = s_t2[kRegLayers - 1];
                 a[kRegLayers - 1][0] = add2(lse2_pair(((POLY_MASK >> (kRegLayers - 1)) & 1u) != 0, add2(w, q[0]),
-                                                      make_float2(nxt.x, nxt.y)), ev[0]);
+                                                      make_float2(nxt.x, nxt.y), ((LG_MASK >> (kRegLayers - 1)) & 1u) != 0), ev[0]);
                 a[kRegLayers - 1][1] = add2(lse2_pair(((POLY_MASK >> (kRegLayers - 1)) & 1u) != 0, add2(w, q[1]),
-                                                      make_float2(nxt.z, nxt.w)), ev[1]);
+                                                      make_float2(nxt.z, nxt.w), ((LG_MASK >> (kRegLayers - 1)) & 1u) != 0), ev[1]);
             }
 #pragma unroll
             for (int d = kRegLayers; d < kLayers; ++d) {
@@ -1024,8 +1044,8 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
                     v0.x += c; v0.y += c; v1.x += c; v1.y += c;
                 }
                 const float2 w = s_t2[d];
-                const float2 r0 = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[0]), v0), ev[0]);
-                const float2 r1 = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[1]), v1), ev[1]);
+                const float2 r0 = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[0]), v0, ((LG_MASK >> d) & 1u) != 0), ev[0]);
+                const float2 r1 = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[1]), v1, ((LG_MASK >> d) & 1u) != 0), ev[1]);
                 As[(d - kRegLayers) * NT + tid] = make_float4(r0.x, r0.y, r1.x, r1.y);
             }
             buf ^= 1u;
@@ -1468,6 +1488,258 @@ __global__ void __launch_bounds__(512, 1) hmm_forward_scaled(const FwdParams p) 
     }
 }
 
+// ---- scaled kernel, register/shared split layout --------------------------------------
+// hmm_forward_scaled laid out like hmm_forward_packed: 1024 threads x 4 k-mers per CTA,
+// layers 0..7 in registers, layers 8..15 and three of the four transition columns in
+// shared memory, so a 7-mer sequence takes a cluster of 4 CTAs (33 clusters on 132 SMs,
+// 32 warps per SM to hide the exchange) instead of 8. The multiply-adds run as packed
+// pairs. Layer 0 travels as the sender's mantissas plus ONE exponent per sending thread
+// (its 64 states share it), which the receiver combines with the exponent field of each
+// mantissa; that is 20 bytes per thread and step instead of 32 and lets two exchange
+// buffers fit beside the state. Same arithmetic as hmm_forward_scaled value for value.
+__global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_split(const FwdParams p) {
+    extern __shared__ __align__(16) float smem_dyn[];
+    __shared__ int s_seq;
+    __shared__ float s_warp[32];
+    __shared__ int s_warp_i[32];
+    __shared__ float s_cl[16];
+    __shared__ int s_cl_i[16];
+    __shared__ float4 s_A4[kLayers / 4];  // exp(trans2[d]), four layers per 16-byte load
+
+    const int tid = threadIdx.x;
+    const int NT = blockDim.x;
+    const unsigned rank = cluster_ctarank();
+    const unsigned CS = cluster_nctarank();
+    const int K = p.K;
+    const int Kq = K >> 2;
+    const int M = NT;
+    const int g = (rank * NT + tid) * 4;
+    const int lane = tid & 31, warp = tid >> 5, nwarps = (NT + 31) >> 5;
+
+    float *a0x = smem_dyn;                                            // [2][4][M] mantissas
+    int *a0w = reinterpret_cast<int *>(smem_dyn + 8 * M);             // [2][4][M/4] sender exponents
+    float4 *Ts = reinterpret_cast<float4 *>(smem_dyn + 10 * M);       // [3][NT] exp(trans1) columns j = 0..2
+    float4 *As = Ts + 3 * NT;                                         // [8][NT] layers 8..15
+
+    float2 T3[2];   // column j = 3 stays in registers
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float4 v = __ldg(reinterpret_cast<const float4 *>(p.trans1) + (j * Kq + (g >> 2)));
+        const float4 w = make_float4(fast_exp(v.x), fast_exp(v.y), fast_exp(v.z), fast_exp(v.w));
+        if (j < 3) {
+            Ts[j * NT + tid] = w;
+        } else {
+            T3[0] = make_float2(w.x, w.y);
+            T3[1] = make_float2(w.z, w.w);
+        }
+    }
+    if (tid < kLayers) reinterpret_cast<float *>(s_A4)[tid] = expf(__ldg(p.trans2 + tid));
+    unsigned dstx0, dstw0;
+    {
+        const int dj = g / Kq, rem = g % Kq;
+        const int dr = rem / M, di = rem % M;
+        dstx0 = map_to_rank(smem_u32(a0x) + 4u * (dj * M + di), dr);
+        dstw0 = map_to_rank(smem_u32(a0w) + 4u * (dj * (M >> 2) + (di >> 2)), dr);
+    }
+    const unsigned bufx_bytes = 16u * M, bufw_bytes = 4u * M;
+    const unsigned cl_addr = smem_u32(s_cl);
+    const unsigned cli_addr = smem_u32(s_cl_i);
+
+    first_position(p, CS, tid, &s_seq);
+    for (;;) {
+        const int seq = next_sequence(p, rank, CS, tid, &s_seq);
+        if (seq < 0) break;
+
+        long long len = p.lens[seq];
+        if (len < 1 || len > p.maxlen) {
+            if (tid == 0 && rank == 0) atomicOr(&g_status, 1u);
+            len = len < 1 ? 1 : p.maxlen;
+        }
+        const uint8_t *obs = p.data + static_cast<long long>(seq) * p.maxlen;
+        const int T_len = static_cast<int>(len);
+
+        // ---- t = 0: x = exp(initial_prob) * exp(emission), W = 0 ------------------------
+        float2 x[kRegLayers][2];
+        int o_next;
+        int W = 0;       // exponent shared by this thread's 64 states
+        int kt;          // exponent of the largest mantissa (magnitude hint)
+        {
+            const int o0 = obs_at(p, obs, 0);
+            o_next = obs_at(p, obs, T_len > 1 ? 1 : 0);
+            const float4 e0 = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o0 * K + g));
+            const float el[4] = {fast_exp(e0.x), fast_exp(e0.y), fast_exp(e0.z), fast_exp(e0.w)};
+            float m = 0.0f;
+#pragma unroll
+            for (int d = 0; d < kLayers; ++d) {
+                const float4 v = __ldg(reinterpret_cast<const float4 *>(p.initial_prob + d * K + g));
+                const float4 r = make_float4(fast_exp(v.x) * el[0], fast_exp(v.y) * el[1], fast_exp(v.z) * el[2],
+                                             fast_exp(v.w) * el[3]);
+                m = max3(m, fmaxf(r.x, r.y), fmaxf(r.z, r.w));
+                if (d < kRegLayers) {
+                    x[d][0] = make_float2(r.x, r.y);
+                    x[d][1] = make_float2(r.z, r.w);
+                } else {
+                    As[(d - kRegLayers) * NT + tid] = r;
+                }
+            }
+            kt = exponent_of(m);
+        }
+        st_cluster_v4(dstx0, x[0][0].x, x[0][0].y, x[0][1].x, x[0][1].y);
+        st_cluster_s32(dstw0, W);
+        cluster_arrive();
+
+        for (int t = 1; t < T_len; ++t) {
+            // this step's emission slice (in flight while the exchange completes); the observation after it
+            const float4 e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o_next * K + g));
+            o_next = obs_at(p, obs, t + 1 < T_len ? t + 1 : T_len - 1);
+
+            cluster_wait();
+            const unsigned buf = (t & 1) ^ 1u;   // buffer that holds the previous step's layer 0
+            const float *px = a0x + (buf ? 4 * M : 0) + tid;
+            const int *pw = a0w + (buf ? M : 0) + (tid >> 2);
+            const float xa0 = px[0], xa1 = px[M], xa2 = px[2 * M], xa3 = px[3 * M];
+            const int wp0 = pw[0], wp1 = pw[M >> 2], wp2 = pw[2 * (M >> 2)], wp3 = pw[3 * (M >> 2)];
+            const unsigned dstx = dstx0 + (buf ? 0u : bufx_bytes);
+            const unsigned dstw = dstw0 + (buf ? 0u : bufw_bytes);
+
+            // magnitude of each incoming value = sender exponent + exponent field of its mantissa;
+            // the new exponent is the largest magnitude this thread is about to combine
+            const int ea0 = xa0 > 0.0f ? wp0 + exponent_of(xa0) : kExpFloor - 200;
+            const int ea1 = xa1 > 0.0f ? wp1 + exponent_of(xa1) : kExpFloor - 200;
+            const int ea2 = xa2 > 0.0f ? wp2 + exponent_of(xa2) : kExpFloor - 200;
+            const int ea3 = xa3 > 0.0f ? wp3 + exponent_of(xa3) : kExpFloor - 200;
+            int Wn = max(max(ea0, ea1), max(ea2, ea3));
+            Wn = max(Wn, W + kt);
+            Wn = max(Wn, kExpFloor);
+            // incoming values relative to 2^Wn (a power-of-two factor: exact); Wn >= wp + exponent, so
+            // the product stays below 2; below 2^-126 it flushes to zero
+            const float2 y0 = dup2(xa0 * pow2_clamped(wp0 - Wn)), y1 = dup2(xa1 * pow2_clamped(wp1 - Wn));
+            const float2 y2 = dup2(xa2 * pow2_clamped(wp2 - Wn)), y3 = dup2(xa3 * pow2_clamped(wp3 - Wn));
+            const float2 own = dup2(pow2_clamped(W - Wn));
+            float2 QE[2], Eo[2];
+            {
+                const float4 t0 = Ts[tid], t1 = Ts[NT + tid], t2 = Ts[2 * NT + tid];
+                const float2 q0 = fma2(T3[0], y3, fma2(make_float2(t2.x, t2.y), y2,
+                                  fma2(make_float2(t1.x, t1.y), y1, mul2(make_float2(t0.x, t0.y), y0))));
+                const float2 q1 = fma2(T3[1], y3, fma2(make_float2(t2.z, t2.w), y2,
+                                  fma2(make_float2(t1.z, t1.w), y1, mul2(make_float2(t0.z, t0.w), y0))));
+                const float2 el2[2] = {make_float2(fast_exp(e.x), fast_exp(e.y)), make_float2(fast_exp(e.z), fast_exp(e.w))};
+                QE[0] = mul2(q0, el2[0]);
+                QE[1] = mul2(q1, el2[1]);
+                Eo[0] = mul2(el2[0], own);
+                Eo[1] = mul2(el2[1], own);
+            }
+            // layer 0 first: it is what the other CTAs wait for
+            // exp(trans2) of four layers per shared-memory load (the shared-memory pipe bounds this kernel)
+            float4 a4 = s_A4[0];
+            const auto A_of = [&](int d) { return dup2(d % 4 == 0 ? a4.x : d % 4 == 1 ? a4.y : d % 4 == 2 ? a4.z : a4.w); };
+            {
+                const float2 a = A_of(0);
+                x[0][0] = fma2(a, QE[0], mul2(Eo[0], x[1][0]));
+                x[0][1] = fma2(a, QE[1], mul2(Eo[1], x[1][1]));
+            }
+            st_cluster_v4(dstx, x[0][0].x, x[0][0].y, x[0][1].x, x[0][1].y);
+            st_cluster_s32(dstw, Wn);
+            cluster_arrive();
+            float m = max3(fmaxf(x[0][0].x, x[0][0].y), x[0][1].x, x[0][1].y);
+#pragma unroll
+            for (int d = 1; d < kRegLayers - 1; ++d) {
+                if (d % 4 == 0) a4 = s_A4[d / 4];
+                const float2 a = A_of(d);
+                x[d][0] = fma2(a, QE[0], mul2(Eo[0], x[d + 1][0]));
+                x[d][1] = fma2(a, QE[1], mul2(Eo[1], x[d + 1][1]));
+                m = max3(m, x[d][0].x, x[d][0].y);
+                m = max3(m, x[d][1].x, x[d][1].y);
+            }
+            float4 nxt = As[tid];   // layer 8 (old)
+            {
+                const float2 a = A_of(kRegLayers - 1);
+                x[kRegLayers - 1][0] = fma2(a, QE[0], mul2(Eo[0], make_float2(nxt.x, nxt.y)));
+                x[kRegLayers - 1][1] = fma2(a, QE[1], mul2(Eo[1], make_float2(nxt.z, nxt.w)));
+                m = max3(m, x[kRegLayers - 1][0].x, x[kRegLayers - 1][0].y);
+                m = max3(m, x[kRegLayers - 1][1].x, x[kRegLayers - 1][1].y);
+            }
+#pragma unroll
+            for (int d = kRegLayers; d < kLayers; ++d) {
+                // old value of layer min(d+1, 15); layers 14 and 15 both read old layer 15
+                if (d < kLayers - 1) nxt = As[(d + 1 - kRegLayers) * NT + tid];
+                float2 v0 = make_float2(nxt.x, nxt.y), v1 = make_float2(nxt.z, nxt.w);
+                if (d >= 14) {
+                    const float c = d == 15 ? p.gamma_lin : p.synthetic_lin;
+                    v0.x *= c; v0.y *= c; v1.x *= c; v1.y *= c;
+                }
+                if (d % 4 == 0) a4 = s_A4[d / 4];
+                const float2 a = A_of(d);
+                const float2 r0 = fma2(a, QE[0], mul2(Eo[0], v0));
+                const float2 r1 = fma2(a, QE[1], mul2(Eo[1], v1));
+                As[(d - kRegLayers) * NT + tid] = make_float4(r0.x, r0.y, r1.x, r1.y);
+                m = max3(m, r0.x, r0.y);
+                m = max3(m, r1.x, r1.y);
+            }
+            kt = exponent_of(m);
+            W = Wn;
+        }
+        cluster_wait();
+
+        // ---- log-likelihood: log(sum of all states) with a common exponent --------------
+        int gexp = W + kt;
+        gexp = __reduce_max_sync(0xffffffffu, gexp);
+        if (lane == 0) s_warp_i[warp] = gexp;
+        __syncthreads();
+        if (tid < (int)CS) {
+            int v = kExpFloor - 200;
+            for (int w = 0; w < nwarps; ++w) v = max(v, s_warp_i[w]);
+            st_cluster_s32(map_to_rank(cli_addr + 4u * rank, tid), v);
+        }
+        cluster_arrive();
+        cluster_wait();
+        int G = kExpFloor - 200;
+        for (unsigned r = 0; r < CS; ++r) G = max(G, s_cl_i[r]);
+        float tsum = 0.0f;
+#pragma unroll
+        for (int d = 0; d < kRegLayers; ++d) tsum += (x[d][0].x + x[d][0].y) + (x[d][1].x + x[d][1].y);
+#pragma unroll
+        for (int d = 0; d < kLayers - kRegLayers; ++d) {
+            const float4 v = As[d * NT + tid];
+            tsum += (v.x + v.y) + (v.z + v.w);
+        }
+        tsum *= pow2_clamped(W - G);
+        tsum = pb::warp_sum(tsum);
+        if (lane == 0) s_warp[warp] = tsum;
+        __syncthreads();
+        if (tid < (int)CS) {
+            float sacc = 0.0f;
+            for (int w = 0; w < nwarps; ++w) sacc += s_warp[w];
+            st_cluster_f32(map_to_rank(cl_addr + 4u * rank, tid), sacc);
+        }
+        cluster_arrive();
+        cluster_wait();
+        if (rank == 0 && tid == 0) {
+            double sacc = 0.0;
+            for (unsigned r = 0; r < CS; ++r) sacc += (double)s_cl[r];
+            // natural log of sum * 2^G; an impossible sequence (sum == 0) gives -inf
+            p.result[seq] = sacc > 0.0 ? (float)(log(sacc) + (double)G * 0.6931471805599453) : -INFINITY;
+        }
+        if (p.write_alpha) {
+            float *dst_alpha = ((len & 1) ? p.alpha1 : p.alpha2) + (long long)seq * (kLayers * (long long)K);
+            const float wl = (float)W * kLn2;
+#pragma unroll
+            for (int d = 0; d < kLayers; ++d) {
+                const float4 s4 = d < kRegLayers ? make_float4(x[d % kRegLayers][0].x, x[d % kRegLayers][0].y,
+                                                               x[d % kRegLayers][1].x, x[d % kRegLayers][1].y)
+                                                 : As[(d - kRegLayers) * NT + tid];
+                float4 v;
+                v.x = fast_log(s4.x) + wl;
+                v.y = fast_log(s4.y) + wl;
+                v.z = fast_log(s4.z) + wl;
+                v.w = fast_log(s4.w) + wl;
+                *reinterpret_cast<float4 *>(dst_alpha + (long long)d * K + g) = v;
+            }
+        }
+        // the next pop starts with a full cluster barrier
+    }
+}
+
 // ---- streaming kernels --------------------------------------------------------
 __global__ void hmm_stream_init(const FwdParams p) {
     const long long N = (long long)kLayers * p.K;
@@ -1575,7 +1847,8 @@ bool make_plan(long long K, Plan *pl, bool allow_split, bool need_kpt4 = false) 
     // Large state spaces: the split layout (1024 threads x 4 k-mers per CTA) halves
     // the CTAs a sequence needs, so clusters pack the GPCs without idle SMs.
     bool want_split = allow_split && kpt == 4 && K >= 4096;
-    if (const char *env = getenv("PARPY_B200_FWD_SPLIT")) want_split = want_split && atoi(env) != 0;
+    if (const char *env = getenv(need_kpt4 ? "PARPY_B200_SCALED_SPLIT" : "PARPY_B200_FWD_SPLIT"))
+        want_split = want_split && atoi(env) != 0;
     if (want_split) {
         nt = 1024;
         cs = K / 4 / 1024;
@@ -1583,7 +1856,7 @@ bool make_plan(long long K, Plan *pl, bool allow_split, bool need_kpt4 = false) 
     }
     if (cs > 16) return false;
     bool cta = false;
-    if (allow_split && K == 1024 && !getenv("PARPY_B200_FWD_KPT") && !getenv("PARPY_B200_FWD_NT")) {
+    if (allow_split && !need_kpt4 && K == 1024 && !getenv("PARPY_B200_FWD_KPT") && !getenv("PARPY_B200_FWD_NT")) {
         int packed = 1;
         if (const char *env = getenv("PARPY_B200_FWD_PACKED")) packed = atoi(env);
         if (packed) {
@@ -1605,7 +1878,7 @@ using ResidentKernel = void (*)(const FwdParams);
 
 ResidentKernel pick_kernel(const Plan &pl, bool five) {
     const int kpt = pl.kpt;
-    if (pl.scaled) return hmm_forward_scaled;
+    if (pl.scaled) return pl.split ? hmm_forward_scaled_split : hmm_forward_scaled;
     if (pl.cta && !five) {
         int npoly = 8;   // measured on 100 sequences x 2000 steps: 8 -> 2.67 ms, 10 -> 2.69, 12 -> 2.81
 
@@ -1633,6 +1906,18 @@ ResidentKernel pick_kernel(const Plan &pl, bool five) {
             // layers 1..8 1.793e12, odd layers 1.764e12, 9 layers 1.747e12, 10 layers 1.751e12,
             // 11 layers 1.712e12, layers 8..15 1.707e12.
             if (!getenv("PARPY_B200_FWD_POLY")) npoly = 7;
+            // experiment: logarithms of N layers on the FMA pipe (exponentials all on the MUFU pipe)
+            if (const char *lg = getenv("PARPY_B200_FWD_LG")) {
+                switch (atoi(lg)) {
+                    case 12: return hmm_forward_packed<0x0000u, 0xEEEEu>;
+                    case 13: return hmm_forward_packed<0x0000u, 0xFBFAu>;
+                    case 14: return hmm_forward_packed<0x0000u, 0xFEFEu>;
+                    case 15: return hmm_forward_packed<0x0000u, 0xFFFEu>;
+                    case 16: return hmm_forward_packed<0x0000u, 0xFFFFu>;
+                    case 114: return hmm_forward_packed<0x0100u, 0xFEFEu>;
+                    default: break;
+                }
+            }
             switch (npoly) {
                 case 0: return hmm_forward_packed<0x0000u>;
                 case 5: return hmm_forward_packed<0x2492u>;   // layers 1,4,7,10,13
@@ -1660,7 +1945,9 @@ int32_t resident_config(const Plan &pl, bool five, cudaLaunchConfig_t *cfg,
                         cudaLaunchAttribute *attr, int *max_clusters, ResidentKernel *kern) {
     ResidentKernel k = pick_kernel(pl, five);
     size_t smem = size_t(2) * 4 * (size_t(pl.nt) * pl.kpt / 4) * sizeof(float);
-    if (pl.cta && !five) smem = 0;  // static shared memory only
+    if (pl.cta && !five && !pl.scaled) smem = 0;  // static shared memory only
+    else if (pl.scaled && pl.split)   // mantissas + sender exponents, 3 transition columns, layers 8..15
+        smem = size_t(10) * pl.nt * sizeof(float) + size_t(3 + 8) * pl.nt * sizeof(float4);
     else if (pl.scaled) smem *= 2;  // mantissas + exponents
     else if (pl.split && !five) smem += size_t(4 + 8) * pl.nt * sizeof(float4);  // transition columns + layers 8..15
     if (pl.cs > 8) PB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
@@ -1762,7 +2049,7 @@ int32_t forward_impl(float gamma, const float *initial_prob, int64_t num_states,
     p.write_alpha = write_alpha ? 1 : 0;
 
     Plan pl;
-    const bool resident = !streaming_forced && make_plan(K, &pl, !five && !scaled, scaled);
+    const bool resident = !streaming_forced && make_plan(K, &pl, !five, scaled);
     PB_REQUIRE(!scaled || (resident && pl.kpt == 4),
                "forward: the scaled kernel needs at least 1024 k-mers (num_states=%lld)", (long long)num_states);
     pl.scaled = scaled;

@@ -138,6 +138,25 @@ def read_trellis_inputs(model_path, signals_path):
     return read_model(model_path), read_signals(signals_path)
 
 
+def forward_schedule(lens, clusters):
+    """The static schedule the forward kernels build for a batch (at most 4096
+    sequences): a NumPy int32 array giving, for every sequence, the resident
+    cluster that scores it. ``lens`` are the sequence lengths (any integer array
+    or tensor), ``clusters`` the number of resident clusters (see
+    ``parpy_b200_forward_plan``). A launch lasts as long as its busiest cluster,
+    i.e. as the largest per-cluster sum of lengths."""
+    import ctypes
+    import torch
+    from . import _native
+    t = torch.as_tensor(lens).to(torch.int64).cuda().contiguous()
+    out = torch.empty(t.numel(), dtype=torch.int32, device="cuda")
+    P = ctypes.c_void_p
+    _native.check(_native.lib().parpy_b200_forward_schedule(
+        P(t.data_ptr()), t.numel(), int(clusters), P(out.data_ptr()),
+        P(torch.cuda.current_stream().cuda_stream)), "forward_schedule")
+    return out.cpu().numpy()
+
+
 def forward_status():
     """Reads and clears the forward kernels' device status word (synchronises the
     device). Returns ``{"length_clamped": bool, "observation_clamped": bool}``:

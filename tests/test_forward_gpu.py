@@ -289,15 +289,38 @@ def test_scaled_variant_against_golden_oracle_and_log_space(native, oracle_mod):
     assert rc != 0 and "scaled kernel needs" in native.error_message()
 
 
+@pytest.mark.parametrize("k,nseq,lo,hi", [(7, 40, 30, 400), (6, 50, 1, 300)])
+def test_scaled_layouts_agree_bit_for_bit(native, monkeypatch, k, nseq, lo, hi):
+    # The scaled kernel in its two layouts: clusters of 512-thread CTAs with all 16 layers in registers
+    # (PARPY_B200_SCALED_SPLIT=0), and 1024-thread CTAs with layers 8..15 in shared memory and one
+    # exponent per sending thread in the exchange (default from 4096 k-mers). Every scaling is by a
+    # power of two, so the two must produce the same bits, final alpha included.
+    from parpy_b200 import synthetic
+    hmm = synthetic.hmm_model(k, seed=20 + k)
+    seqs = synthetic.hmm_sequences(nseq, lo, hi, seed=30 + k)
+    dh, ds = to_dev(hmm), to_dev(seqs)
+    out = {}
+    for split in ("0", "1"):
+        monkeypatch.setenv("PARPY_B200_SCALED_SPLIT", split)
+        rc, res, a1, a2 = cabi_forward(native, dh, ds, FLAGS["scaled"] | 2, alpha=True)
+        assert rc == 0, native.error_message()
+        out[split] = (res.cpu().numpy().copy(), a1.cpu().numpy().copy(), a2.cpu().numpy().copy())
+    assert np.isfinite(out["1"][0]).all()
+    assert np.array_equal(out["0"][0], out["1"][0])
+    assert np.array_equal(out["0"][1], out["1"][1]) and np.array_equal(out["0"][2], out["1"][2])
+
+
 def test_8mer_runs_on_a_16_cta_cluster(native, oracle_mod):
-    # 4^8 k-mers x 16 layers = 1,048,576 states: non-portable cluster of 16 CTAs
+    # 4^8 k-mers x 16 layers = 1,048,576 states: non-portable cluster of 16 CTAs, log-space and
+    # scaled kernels (the scaled one only exists in the 1024-thread layout at this size)
     from parpy_b200 import synthetic
     hmm = synthetic.hmm_model(8, seed=8)
     seqs = synthetic.hmm_sequences(3, 1, 16, seed=9)
     exp = oracle_mod.forward(hmm, seqs)
-    rc, res, _, _ = cabi_forward(native, to_dev(hmm), to_dev(seqs))
-    assert rc == 0, native.error_message()
-    assert max_rel(res.cpu().numpy(), exp) <= REL_ORACLE
+    for flags in (0, FLAGS["scaled"]):
+        rc, res, _, _ = cabi_forward(native, to_dev(hmm), to_dev(seqs), flags)
+        assert rc == 0, native.error_message()
+        assert max_rel(res.cpu().numpy(), exp) <= REL_ORACLE
 
 
 def test_empty_batch_and_single_step(native):
