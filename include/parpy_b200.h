@@ -145,7 +145,10 @@ int32_t parpy_b200_forward_schedule(const int64_t *lens, int64_t num_instances, 
 
 /* Reads and clears the device status word of the current device (host call,
  * synchronises the device). Bit 0: a sequence length outside [1, maxlen] was
- * clamped. Bit 1: an observation byte >= n_obs was clamped (parpy_b200_forward_ex). */
+ * clamped. Bit 1: an observation byte >= n_obs was clamped (parpy_b200_forward_ex).
+ * Bit 2: a bounded wait for another CTA's values ran out inside a kernel (scaled
+ * kernel, st.async exchange); the results of the calls since the last read are
+ * not valid. */
 int32_t parpy_b200_forward_status(uint32_t *status);
 
 /* Forward pass for callers that must not trigger a device allocation.

@@ -26,6 +26,7 @@
 #include "../../include/parpy_b200.h"
 #include "common.cuh"
 #include "cluster.cuh"
+#include "tmem.cuh"
 
 namespace {
 
@@ -38,6 +39,7 @@ constexpr int kSegInts = kMaxBins + 64;   // ints reserved for the per-cluster s
 
 // Device status word. Bit 0: a sequence length outside [1, maxlen] was clamped.
 // Bit 1: an observation >= n_obs inside a sequence was clamped to n_obs - 1.
+// Bit 2: a bounded wait of the st.async exchange ran out; that call's results are not valid.
 __device__ unsigned g_status;
 
 // Fixed scheduling scratch of parpy_b200_forward_noalloc: the sequence order
@@ -75,17 +77,16 @@ struct FwdParams {
     float synthetic_lin;
 };
 
-// Observation byte t of a sequence, kept inside the emission table: a value past the
-// last row is clamped and flagged (by one thread per cluster).
-__device__ __forceinline__ int obs_at(const FwdParams &p, const uint8_t *obs, int t) {
-    int o = obs[t];
-    if (o > p.obs_max) {
-        unsigned r;
-        asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-        if (threadIdx.x == 0 && r == 0) atomicOr(&g_status, 2u);
-        o = p.obs_max;
-    }
-    return o;
+// Observation byte t of a sequence, kept inside the emission table: a value past the last
+// row is clamped and remembered in `bad` (no branch in the time loop; the caller raises the
+// status bit once per sequence with flag_bad_observation).
+__device__ __forceinline__ int obs_at(const FwdParams &p, const uint8_t *obs, int t, bool &bad) {
+    const int o = obs[t];
+    bad = bad || o > p.obs_max;
+    return min(o, p.obs_max);
+}
+__device__ __forceinline__ void flag_bad_observation(bool bad, bool reporter) {
+    if (bad && reporter) atomicOr(&g_status, 2u);
 }
 
 // ---- log-sum-exp building blocks -------------------------------------------
@@ -467,15 +468,16 @@ hmm_forward_resident(const FwdParams p) {
         }
         const uint8_t *obs = p.data + static_cast<long long>(seq) * p.maxlen;
         const int T_len = static_cast<int>(len);
+        bool bad_obs = false;   // an observation byte outside the emission table was met
 
         // ---- t = 0 (benchmarks/forward.py:94-101) ------------------------------
         float a[kLayers][KPT];
         float e[KPT], e_next[KPT];
         int o_next;
         {
-            const int o0 = obs_at(p, obs, 0);
-            const int o1 = obs_at(p, obs, T_len > 1 ? 1 : 0);
-            o_next = obs_at(p, obs, T_len > 2 ? 2 : T_len - 1);
+            const int o0 = obs_at(p, obs, 0, bad_obs);
+            const int o1 = obs_at(p, obs, T_len > 1 ? 1 : 0, bad_obs);
+            o_next = obs_at(p, obs, T_len > 2 ? 2 : T_len - 1, bad_obs);
             if constexpr (KPT == 4) {
                 const float4 v0 = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o0 * K + g));
                 const float4 v1 = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o1 * K + g));
@@ -517,7 +519,7 @@ hmm_forward_resident(const FwdParams p) {
                     e_next[0] = __ldg(row);
                 }
                 const int tn = t + 2 < T_len ? t + 2 : T_len - 1;
-                o_next = obs_at(p, obs, tn);
+                o_next = obs_at(p, obs, tn, bad_obs);
             }
 
             cluster_wait();  // layer 0 of step t-1 from every CTA has landed
@@ -612,6 +614,7 @@ hmm_forward_resident(const FwdParams p) {
             float s = 0.0f;
             for (unsigned r = 0; r < CS; ++r) s += s_cl[r];
             p.result[seq] = gmax + fast_log(s);
+            flag_bad_observation(bad_obs, true);
         }
 
         if (p.write_alpha) {
@@ -689,14 +692,15 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_split(const FwdParams p) 
         }
         const uint8_t *obs = p.data + static_cast<long long>(seq) * p.maxlen;
         const int T_len = static_cast<int>(len);
+        bool bad_obs = false;   // an observation byte outside the emission table was met
 
         // t = 0
         float a[kRegLayers][4];
         float4 e;
         int o_next;
         {
-            const int o0 = obs_at(p, obs, 0);
-            o_next = obs_at(p, obs, T_len > 1 ? 1 : 0);
+            const int o0 = obs_at(p, obs, 0, bad_obs);
+            o_next = obs_at(p, obs, T_len > 1 ? 1 : 0, bad_obs);
             e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o0 * K + g));
 #pragma unroll
             for (int d = 0; d < kLayers; ++d) {
@@ -713,7 +717,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_split(const FwdParams p) 
         for (int t = 1; t < T_len; ++t) {
             // this step's emission slice; the observation after it
             e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o_next * K + g));
-            o_next = obs_at(p, obs, t + 1 < T_len ? t + 1 : T_len - 1);
+            o_next = obs_at(p, obs, t + 1 < T_len ? t + 1 : T_len - 1, bad_obs);
             const float ev[4] = {e.x, e.y, e.z, e.w};
 
             cluster_wait();
@@ -814,6 +818,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_split(const FwdParams p) 
             float sacc = 0.0f;
             for (unsigned r = 0; r < CS; ++r) sacc += s_cl[r];
             p.result[seq] = gmax + fast_log(sacc);
+            flag_bad_observation(bad_obs, true);
         }
         if (p.write_alpha) {
             float *dst_alpha = ((len & 1) ? p.alpha1 : p.alpha2) + (long long)seq * (kLayers * (long long)K);
@@ -918,13 +923,17 @@ __device__ __forceinline__ float2 lse4_pair(float2 p0, float2 p1, float2 p2, flo
 }
 
 // POLY_MASK bit d: layer d evaluates its exponential on the FMA pipe; LG_MASK bit d: its logarithm.
-template <unsigned POLY_MASK, unsigned LG_MASK = 0u>
+// TMEM: layers RL..15 and the transition columns live in tensor memory instead of shared memory
+// (RL = layers kept in registers; the shared-memory layout is fixed at 8).
+template <unsigned POLY_MASK, unsigned LG_MASK = 0u, bool TMEM = false, int RL = kRegLayers>
 __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p) {
+    static_assert(TMEM ? (RL >= 4 && RL <= 8 && RL % 2 == 0) : RL == kRegLayers, "register layers");
     extern __shared__ __align__(16) float smem_dyn[];
     __shared__ int s_seq;
     __shared__ float s_warp[32];
     __shared__ float s_cl[16];
     __shared__ float2 s_t2[kLayers];   // (trans2[d], trans2[d])
+    __shared__ unsigned s_tmem;        // base address of the CTA's tensor memory (TMEM)
 
     const int tid = threadIdx.x;
     const int NT = blockDim.x;
@@ -939,10 +948,22 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
     float *a0s = smem_dyn;                                             // [2][4][M]
     float4 *Ts = reinterpret_cast<float4 *>(smem_dyn + 8 * M);         // [4][NT] transition columns
     float4 *As = Ts + 4 * NT;                                          // [8][NT] layers 8..15
+    // tensor memory: the 8 warps that share a lane quarter take 64 columns each; a thread's
+    // columns 0..31 hold layers 8..15 (4 k-mers each), columns 32..47 the transition columns
+    unsigned tm_all = 0, tm = 0;
+    if constexpr (TMEM) {
+        if (warp == 0) tmem_alloc_all(&s_tmem);
+        tmem_publish();
+        tm_all = s_tmem;
+        tm = tmem_warp_base(tm_all, warp, 64 * (warp >> 2));
+    }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-        Ts[j * NT + tid] = __ldg(reinterpret_cast<const float4 *>(p.trans1) + (j * Kq + (g >> 2)));
+        const float4 v = __ldg(reinterpret_cast<const float4 *>(p.trans1) + (j * Kq + (g >> 2)));
+        if constexpr (TMEM) tmem_st4(tm + 4 * (kLayers - RL) + 4 * j, v);
+        else Ts[j * NT + tid] = v;
     }
+    if constexpr (TMEM) tmem_wait_st();
     if (tid < kLayers) s_t2[tid] = dup2(__ldg(p.trans2 + tid));
     const float gamma2 = p.gamma, syn2 = p.synthetic;
 
@@ -969,23 +990,26 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
         }
         const uint8_t *obs = p.data + static_cast<long long>(seq) * p.maxlen;
         const int T_len = static_cast<int>(len);
+        bool bad_obs = false;   // an observation byte outside the emission table was met
 
         // t = 0
-        float2 a[kRegLayers][2];
+        float2 a[RL][2];
         float4 e;
         int o_next;
         {
-            const int o0 = obs_at(p, obs, 0);
-            o_next = obs_at(p, obs, T_len > 1 ? 1 : 0);
+            const int o0 = obs_at(p, obs, 0, bad_obs);
+            o_next = obs_at(p, obs, T_len > 1 ? 1 : 0, bad_obs);
             e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o0 * K + g));
 #pragma unroll
             for (int d = 0; d < kLayers; ++d) {
                 const float4 v = __ldg(reinterpret_cast<const float4 *>(p.initial_prob + d * K + g));
                 const float2 lo = make_float2(v.x + e.x, v.y + e.y);
                 const float2 hi = make_float2(v.z + e.z, v.w + e.w);
-                if (d < kRegLayers) { a[d][0] = lo; a[d][1] = hi; }
-                else As[(d - kRegLayers) * NT + tid] = make_float4(lo.x, lo.y, hi.x, hi.y);
+                if (d < RL) { a[d][0] = lo; a[d][1] = hi; }
+                else if constexpr (TMEM) tmem_st4(tm + 4 * (d - RL), make_float4(lo.x, lo.y, hi.x, hi.y));
+                else As[(d - RL) * NT + tid] = make_float4(lo.x, lo.y, hi.x, hi.y);
             }
+            if constexpr (TMEM) tmem_wait_st();
         }
         unsigned buf = 0;
         st_cluster_v4(dst0, a[0][0].x, a[0][0].y, a[0][1].x, a[0][1].y);
@@ -994,8 +1018,15 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
         for (int t = 1; t < T_len; ++t) {
             // this step's emission slice; the observation after it
             e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o_next * K + g));
-            o_next = obs_at(p, obs, t + 1 < T_len ? t + 1 : T_len - 1);
+            o_next = obs_at(p, obs, t + 1 < T_len ? t + 1 : T_len - 1, bad_obs);
             const float2 ev[2] = {make_float2(e.x, e.y), make_float2(e.z, e.w)};
+            float4 t0, t1, t2, t3;   // transition columns
+            if constexpr (TMEM) {    // in flight while the exchange completes
+                tmem_ld4(tm + 4 * (kLayers - RL), t0);
+                tmem_ld4(tm + 4 * (kLayers - RL) + 4, t1);
+                tmem_ld4(tm + 4 * (kLayers - RL) + 8, t2);
+                tmem_ld4(tm + 4 * (kLayers - RL) + 12, t3);
+            }
 
             cluster_wait();
             const float *seg = a0s + (buf ? 4 * M : 0) + tid;
@@ -1004,7 +1035,11 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
 
             float2 q[2];
             {
-                const float4 t0 = Ts[tid], t1 = Ts[NT + tid], t2 = Ts[2 * NT + tid], t3 = Ts[3 * NT + tid];
+                if constexpr (TMEM) {
+                    tmem_wait_ld(t0, t1, t2, t3);
+                } else {
+                    t0 = Ts[tid], t1 = Ts[NT + tid], t2 = Ts[2 * NT + tid], t3 = Ts[3 * NT + tid];
+                }
                 q[0] = lse4_pair(add2(make_float2(t0.x, t0.y), a0), add2(make_float2(t1.x, t1.y), a1),
                                  add2(make_float2(t2.x, t2.y), a2), add2(make_float2(t3.x, t3.y), a3));
                 q[1] = lse4_pair(add2(make_float2(t0.z, t0.w), a0), add2(make_float2(t1.z, t1.w), a1),
@@ -1019,26 +1054,44 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
             st_cluster_v4(dst, a[0][0].x, a[0][0].y, a[0][1].x, a[0][1].y);
             cluster_arrive();
 #pragma unroll
-            for (int d = 1; d < kRegLayers - 1; ++d) {
+            for (int d = 1; d < RL - 1; ++d) {
                 const float2 w = s_t2[d];
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
                     a[d][h] = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[h]), a[d + 1][h], ((LG_MASK >> d) & 1u) != 0), ev[h]);
             }
             // layers 7..15: the "next layer" operand comes from shared memory
-            float4 nxt = As[tid];  // layer 8 (old)
+            float4 nxt, nxt2;   // TMEM: old values of the next layer, requested one layer ahead
+            if constexpr (TMEM) {
+                tmem_ld4(tm, nxt);       // layer 8 (old)
+                tmem_wait_ld(nxt);
+                tmem_ld4(tm + 4, nxt2);  // layer 9 (old)
+            } else {
+                nxt = As[tid];           // layer 8 (old)
+            }
             {
-                const float2 w = s_t2[kRegLayers - 1];
-                a[kRegLayers - 1][0] = add2(lse2_pair(((POLY_MASK >> (kRegLayers - 1)) & 1u) != 0, add2(w, q[0]),
-                                                      make_float2(nxt.x, nxt.y), ((LG_MASK >> (kRegLayers - 1)) & 1u) != 0), ev[0]);
-                a[kRegLayers - 1][1] = add2(lse2_pair(((POLY_MASK >> (kRegLayers - 1)) & 1u) != 0, add2(w, q[1]),
-                                                      make_float2(nxt.z, nxt.w), ((LG_MASK >> (kRegLayers - 1)) & 1u) != 0), ev[1]);
+                const float2 w = s_t2[RL - 1];
+                a[RL - 1][0] = add2(lse2_pair(((POLY_MASK >> (RL - 1)) & 1u) != 0, add2(w, q[0]),
+                                                      make_float2(nxt.x, nxt.y), ((LG_MASK >> (RL - 1)) & 1u) != 0), ev[0]);
+                a[RL - 1][1] = add2(lse2_pair(((POLY_MASK >> (RL - 1)) & 1u) != 0, add2(w, q[1]),
+                                                      make_float2(nxt.z, nxt.w), ((LG_MASK >> (RL - 1)) & 1u) != 0), ev[1]);
             }
 #pragma unroll
-            for (int d = kRegLayers; d < kLayers; ++d) {
+            for (int d = RL; d < kLayers; ++d) {
                 // old alpha[min(d+1,15)]; layers 14 and 15 both read old layer 15
-                if (d < kLayers - 1) nxt = As[(d + 1 - kRegLayers) * NT + tid];
-                float2 v0 = make_float2(nxt.x, nxt.y), v1 = make_float2(nxt.z, nxt.w);
+                if constexpr (TMEM) {
+                    // layer d + 1 was requested during layer d - 1; layer d + 2 is requested now, before
+                    // layer d is written (a load has completed before anything overwrites its columns)
+                    if (d < kLayers - 1) {
+                        float4 &cur = (d & 1) ? nxt : nxt2, &ahead = (d & 1) ? nxt2 : nxt;
+                        tmem_wait_ld(cur);
+                        if (d + 2 < kLayers) tmem_ld4(tm + 4 * (d + 2 - RL), ahead);
+                    }
+                } else {
+                    if (d < kLayers - 1) nxt = As[(d + 1 - RL) * NT + tid];
+                }
+                const float4 &old = !TMEM ? nxt : (d < kLayers - 1) ? ((d & 1) ? nxt : nxt2) : ((d & 1) ? nxt2 : nxt);
+                float2 v0 = make_float2(old.x, old.y), v1 = make_float2(old.z, old.w);
                 if (d >= 14) {
                     const float c = d == 15 ? gamma2 : syn2;
                     v0.x += c; v0.y += c; v1.x += c; v1.y += c;
@@ -1046,8 +1099,10 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
                 const float2 w = s_t2[d];
                 const float2 r0 = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[0]), v0, ((LG_MASK >> d) & 1u) != 0), ev[0]);
                 const float2 r1 = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[1]), v1, ((LG_MASK >> d) & 1u) != 0), ev[1]);
-                As[(d - kRegLayers) * NT + tid] = make_float4(r0.x, r0.y, r1.x, r1.y);
+                if constexpr (TMEM) tmem_st4(tm + 4 * (d - RL), make_float4(r0.x, r0.y, r1.x, r1.y));
+                else As[(d - RL) * NT + tid] = make_float4(r0.x, r0.y, r1.x, r1.y);
             }
+            if constexpr (TMEM) tmem_wait_st();   // the next step reads what this one stored
             buf ^= 1u;
         }
         cluster_wait();
@@ -1055,11 +1110,17 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
         // final log-sum-exp over all states
         float tmax = -INFINITY;
 #pragma unroll
-        for (int d = 0; d < kRegLayers; ++d)
+        for (int d = 0; d < RL; ++d)
             tmax = fmaxf(tmax, fmaxf(fmaxf(a[d][0].x, a[d][0].y), fmaxf(a[d][1].x, a[d][1].y)));
 #pragma unroll
-        for (int d = 0; d < kLayers - kRegLayers; ++d) {
-            const float4 v = As[d * NT + tid];
+        for (int d = 0; d < kLayers - RL; ++d) {
+            float4 v;
+            if constexpr (TMEM) {
+                tmem_ld4(tm + 4 * d, v);
+                tmem_wait_ld(v);
+            } else {
+                v = As[d * NT + tid];
+            }
             tmax = fmaxf(tmax, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
         }
         tmax = pb::warp_max(tmax);
@@ -1076,12 +1137,18 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
         for (unsigned r = 0; r < CS; ++r) gmax = fmaxf(gmax, s_cl[r]);
         float tsum = 0.0f;
 #pragma unroll
-        for (int d = 0; d < kRegLayers; ++d)
+        for (int d = 0; d < RL; ++d)
             tsum += fast_exp(a[d][0].x - gmax) + fast_exp(a[d][0].y - gmax) +
                     fast_exp(a[d][1].x - gmax) + fast_exp(a[d][1].y - gmax);
 #pragma unroll
-        for (int d = 0; d < kLayers - kRegLayers; ++d) {
-            const float4 v = As[d * NT + tid];
+        for (int d = 0; d < kLayers - RL; ++d) {
+            float4 v;
+            if constexpr (TMEM) {
+                tmem_ld4(tm + 4 * d, v);
+                tmem_wait_ld(v);
+            } else {
+                v = As[d * NT + tid];
+            }
             tsum += fast_exp(v.x - gmax) + fast_exp(v.y - gmax) + fast_exp(v.z - gmax) + fast_exp(v.w - gmax);
         }
         tsum = pb::warp_sum(tsum);
@@ -1100,17 +1167,29 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
             float sacc = 0.0f;
             for (unsigned r = 0; r < CS; ++r) sacc += s_cl[r];
             p.result[seq] = gmax + fast_log(sacc);
+            flag_bad_observation(bad_obs, true);
         }
         if (p.write_alpha) {
             float *dst_alpha = ((len & 1) ? p.alpha1 : p.alpha2) + (long long)seq * (kLayers * (long long)K);
 #pragma unroll
             for (int d = 0; d < kLayers; ++d) {
-                const float4 v = d < kRegLayers ? make_float4(a[d % kRegLayers][0].x, a[d % kRegLayers][0].y,
-                                                        a[d % kRegLayers][1].x, a[d % kRegLayers][1].y)
-                                          : As[(d - kRegLayers) * NT + tid];
+                float4 v = make_float4(a[d % RL][0].x, a[d % RL][0].y,
+                                       a[d % RL][1].x, a[d % RL][1].y);
+                if (d >= RL) {
+                    if constexpr (TMEM) {
+                        tmem_ld4(tm + 4 * (d - RL), v);
+                        tmem_wait_ld(v);
+                    } else {
+                        v = As[(d - RL) * NT + tid];
+                    }
+                }
                 *reinterpret_cast<float4 *>(dst_alpha + (long long)d * K + g) = v;
             }
         }
+    }
+    if constexpr (TMEM) {
+        tmem_publish();   // every warp is done with its columns
+        if (warp == 0) tmem_free_all(tm_all);
     }
 }
 
@@ -1121,7 +1200,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
 // exponential on the layers of POLY_MASK). Layer 0 is exchanged
 // through the CTA's own shared memory, so a time step costs one __syncthreads instead of
 // a cluster barrier, which is what bounds the step time of small state spaces.
-template <unsigned POLY_MASK>
+template <unsigned POLY_MASK, unsigned LG_MASK = 0u>
 __global__ void __launch_bounds__(256, 1) hmm_forward_packed_cta(const FwdParams p) {
     __shared__ __align__(16) float a0s[2][1024];   // layer 0 of all k-mers, double buffered
     __shared__ int s_seq;
@@ -1171,13 +1250,14 @@ __global__ void __launch_bounds__(256, 1) hmm_forward_packed_cta(const FwdParams
         }
         const uint8_t *obs = p.data + static_cast<long long>(seq) * p.maxlen;
         const int T_len = static_cast<int>(len);
+        bool bad_obs = false;   // an observation byte outside the emission table was met
 
         float2 a[kLayers][2];
         float4 e;
         int o_next;
         {
-            const int o0 = obs_at(p, obs, 0);
-            o_next = obs_at(p, obs, T_len > 1 ? 1 : 0);
+            const int o0 = obs_at(p, obs, 0, bad_obs);
+            o_next = obs_at(p, obs, T_len > 1 ? 1 : 0, bad_obs);
             e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o0 * K + g));
 #pragma unroll
             for (int d = 0; d < kLayers; ++d) {
@@ -1191,7 +1271,7 @@ __global__ void __launch_bounds__(256, 1) hmm_forward_packed_cta(const FwdParams
 
         for (int t = 1; t < T_len; ++t) {
             e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o_next * K + g));
-            o_next = obs_at(p, obs, t + 1 < T_len ? t + 1 : T_len - 1);
+            o_next = obs_at(p, obs, t + 1 < T_len ? t + 1 : T_len - 1, bad_obs);
             const float2 ev[2] = {make_float2(e.x, e.y), make_float2(e.z, e.w)};
 
             __syncthreads();   // layer 0 of step t-1 is complete; the other buffer is free
@@ -1212,7 +1292,7 @@ __global__ void __launch_bounds__(256, 1) hmm_forward_packed_cta(const FwdParams
                         v.x += c;
                         v.y += c;
                     }
-                    a[d][h] = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[h]), v), ev[h]);
+                    a[d][h] = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[h]), v, ((LG_MASK >> d) & 1u) != 0), ev[h]);
                 }
                 if (d == 0)
                     *reinterpret_cast<float4 *>(&a0s[buf ^ 1u][g]) =
@@ -1244,6 +1324,7 @@ __global__ void __launch_bounds__(256, 1) hmm_forward_packed_cta(const FwdParams
             float sacc = 0.0f;
             for (int w = 0; w < nwarps; ++w) sacc += s_warp[w];
             p.result[seq] = gmax + fast_log(sacc);
+            flag_bad_observation(bad_obs, true);
         }
         if (p.write_alpha) {
             float *dst_alpha = ((len & 1) ? p.alpha1 : p.alpha2) + (long long)seq * (kLayers * (long long)K);
@@ -1347,6 +1428,7 @@ __global__ void __launch_bounds__(512, 1) hmm_forward_scaled(const FwdParams p) 
         }
         const uint8_t *obs = p.data + static_cast<long long>(seq) * p.maxlen;
         const int T_len = static_cast<int>(len);
+        bool bad_obs = false;   // an observation byte outside the emission table was met
 
         // ---- t = 0: x = exp(initial_prob) * exp(emission), W = 0 ------------------------
         float x[kLayers][4];
@@ -1355,9 +1437,9 @@ __global__ void __launch_bounds__(512, 1) hmm_forward_scaled(const FwdParams p) 
         int W = 0;       // exponent shared by this thread's 64 states
         int kt;          // exponent of the largest mantissa (magnitude hint)
         {
-            const int o0 = obs_at(p, obs, 0);
-            const int o1 = obs_at(p, obs, T_len > 1 ? 1 : 0);
-            o_next = obs_at(p, obs, T_len > 2 ? 2 : T_len - 1);
+            const int o0 = obs_at(p, obs, 0, bad_obs);
+            const int o1 = obs_at(p, obs, T_len > 1 ? 1 : 0, bad_obs);
+            o_next = obs_at(p, obs, T_len > 2 ? 2 : T_len - 1, bad_obs);
             const float4 e0 = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o0 * K + g));
             e_next = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o1 * K + g));
             const float el[4] = {fast_exp(e0.x), fast_exp(e0.y), fast_exp(e0.z), fast_exp(e0.w)};
@@ -1383,7 +1465,7 @@ __global__ void __launch_bounds__(512, 1) hmm_forward_scaled(const FwdParams p) 
             // emission probabilities of o_t (log values were fetched a step ago)
             const float el[4] = {fast_exp(e_next.x), fast_exp(e_next.y), fast_exp(e_next.z), fast_exp(e_next.w)};
             e_next = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o_next * K + g));
-            o_next = obs_at(p, obs, t + 2 < T_len ? t + 2 : T_len - 1);
+            o_next = obs_at(p, obs, t + 2 < T_len ? t + 2 : T_len - 1, bad_obs);
 
             cluster_wait();
             const int off = (buf ? 4 * M : 0) + tid;
@@ -1470,6 +1552,7 @@ __global__ void __launch_bounds__(512, 1) hmm_forward_scaled(const FwdParams p) 
             for (unsigned r = 0; r < CS; ++r) sacc += (double)s_cl[r];
             // natural log of sum * 2^G; an impossible sequence (sum == 0) gives -inf
             p.result[seq] = sacc > 0.0 ? (float)(log(sacc) + (double)G * 0.6931471805599453) : -INFINITY;
+            flag_bad_observation(bad_obs, true);
         }
         if (p.write_alpha) {
             float *dst_alpha = ((len & 1) ? p.alpha1 : p.alpha2) + (long long)seq * (kLayers * (long long)K);
@@ -1557,6 +1640,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_split(const FwdPar
         }
         const uint8_t *obs = p.data + static_cast<long long>(seq) * p.maxlen;
         const int T_len = static_cast<int>(len);
+        bool bad_obs = false;   // an observation byte outside the emission table was met
 
         // ---- t = 0: x = exp(initial_prob) * exp(emission), W = 0 ------------------------
         float2 x[kRegLayers][2];
@@ -1564,8 +1648,8 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_split(const FwdPar
         int W = 0;       // exponent shared by this thread's 64 states
         int kt;          // exponent of the largest mantissa (magnitude hint)
         {
-            const int o0 = obs_at(p, obs, 0);
-            o_next = obs_at(p, obs, T_len > 1 ? 1 : 0);
+            const int o0 = obs_at(p, obs, 0, bad_obs);
+            o_next = obs_at(p, obs, T_len > 1 ? 1 : 0, bad_obs);
             const float4 e0 = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o0 * K + g));
             const float el[4] = {fast_exp(e0.x), fast_exp(e0.y), fast_exp(e0.z), fast_exp(e0.w)};
             float m = 0.0f;
@@ -1591,7 +1675,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_split(const FwdPar
         for (int t = 1; t < T_len; ++t) {
             // this step's emission slice (in flight while the exchange completes); the observation after it
             const float4 e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o_next * K + g));
-            o_next = obs_at(p, obs, t + 1 < T_len ? t + 1 : T_len - 1);
+            o_next = obs_at(p, obs, t + 1 < T_len ? t + 1 : T_len - 1, bad_obs);
 
             cluster_wait();
             const unsigned buf = (t & 1) ^ 1u;   // buffer that holds the previous step's layer 0
@@ -1719,6 +1803,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_split(const FwdPar
             for (unsigned r = 0; r < CS; ++r) sacc += (double)s_cl[r];
             // natural log of sum * 2^G; an impossible sequence (sum == 0) gives -inf
             p.result[seq] = sacc > 0.0 ? (float)(log(sacc) + (double)G * 0.6931471805599453) : -INFINITY;
+            flag_bad_observation(bad_obs, true);
         }
         if (p.write_alpha) {
             float *dst_alpha = ((len & 1) ? p.alpha1 : p.alpha2) + (long long)seq * (kLayers * (long long)K);
@@ -1740,13 +1825,349 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_split(const FwdPar
     }
 }
 
+// ---- scaled kernel, layers 8..15 and the transition columns in tensor memory -----------
+// hmm_forward_scaled_split is bound by the shared-memory pipe: per thread and step it reads
+// and writes the eight upper layers (2 x 128 bytes) and reads three transition columns through
+// a pipe that moves 128 bytes per clock and SM. Tensor memory (256 KB per SM, otherwise the
+// accumulator store of the tensor cores) takes their place here: every thread owns 48 of its
+// warp's columns (32 for layers 8..15, 16 for exp(trans1)) and moves them with tcgen05.ld/st,
+// which reach 3.4 x the shared-memory rate for this access pattern. Shared memory then holds
+// only the layer-0 exchange. Arithmetic and results are those of hmm_forward_scaled_split.
+// Bounded wait on a CTA-local mbarrier phase (st.async exchange). False: gave up.
+constexpr int kFwdWaitLimit = 1 << 22;
+__device__ __forceinline__ bool fwd_mbar_wait(unsigned mbar, unsigned parity) {
+    for (int i = 0; i < kFwdWaitLimit; ++i) {
+        unsigned ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                     "selp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(mbar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+// RL: layers kept in registers (4, 6 or 8); the others live in tensor memory. ASYNC (clusters of
+// 2 to 8 CTAs): layer 0 travels with st.async and is counted in by an mbarrier of the consuming
+// CTA (complete_tx), so the sender runs no release fence (the largest stall of the barrier
+// version). A CTA's phase completes on the bytes of the quarter of each producer's threads whose
+// k-mers it consumes, so a CTA can run ahead of threads elsewhere in the cluster; with up to 8
+// CTAs a writer of round r is only ordered after every thread's read of round r - 4, hence four
+// buffers and four mbarriers. Every wait is bounded; one that runs out raises status bit 2.
+template <int RL, bool ASYNC>
+__global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_tmem(const FwdParams p) {
+    static_assert(RL >= 4 && RL <= 8 && RL % 2 == 0, "register layers");
+    extern __shared__ __align__(16) float smem_dyn[];
+    __shared__ int s_seq;
+    __shared__ float s_warp[32];
+    __shared__ int s_warp_i[32];
+    __shared__ float s_cl[16];
+    __shared__ int s_cl_i[16];
+    __shared__ float4 s_A4[kLayers / 4];  // exp(trans2[d]), four layers per 16-byte load
+    __shared__ unsigned s_tmem;           // base address of the CTA's tensor memory
+    __shared__ __align__(8) unsigned long long s_mbar[4];
+
+    const int tid = threadIdx.x;
+    const int NT = blockDim.x;
+    const unsigned rank = cluster_ctarank();
+    const unsigned CS = cluster_nctarank();
+    const int K = p.K;
+    const int Kq = K >> 2;
+    const int M = NT;
+    const int g = (rank * NT + tid) * 4;
+    const int lane = tid & 31, warp = tid >> 5, nwarps = (NT + 31) >> 5;
+
+    constexpr unsigned NB = ASYNC ? 4u : 2u;                          // layer-0 buffers
+    float *a0x = smem_dyn;                                            // [NB][4][M] mantissas
+    int *a0w = reinterpret_cast<int *>(smem_dyn + NB * 4 * M);        // [NB][4][M/4] sender exponents
+
+    // tensor memory: the 8 warps that share a lane quarter take 64 columns each; a thread's
+    // columns 0..31 hold layers 8..15 (4 k-mers each), columns 32..47 exp(trans1) for j = 0..3
+    if (warp == 0) tmem_alloc_all(&s_tmem);
+    tmem_publish();
+    const unsigned tm_all = s_tmem;
+    const unsigned tm = tmem_warp_base(tm_all, warp, 64 * (warp >> 2));
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float4 v = __ldg(reinterpret_cast<const float4 *>(p.trans1) + (j * Kq + (g >> 2)));
+        tmem_st4(tm + 4 * (kLayers - RL) + 4 * j, make_float4(fast_exp(v.x), fast_exp(v.y), fast_exp(v.z), fast_exp(v.w)));
+    }
+    tmem_wait_st();
+    if (tid < kLayers) reinterpret_cast<float *>(s_A4)[tid] = expf(__ldg(p.trans2 + tid));
+    unsigned dstx0, dstw0;
+    {
+        const int dj = g / Kq, rem = g % Kq;
+        const int dr = rem / M, di = rem % M;
+        dstx0 = map_to_rank(smem_u32(a0x) + 4u * (dj * M + di), dr);
+        dstw0 = map_to_rank(smem_u32(a0w) + 4u * (dj * (M >> 2) + (di >> 2)), dr);
+    }
+    const unsigned bufx_bytes = 16u * M, bufw_bytes = 4u * M;
+    const unsigned mbar0 = smem_u32(&s_mbar[0]);
+    unsigned rmbar0 = 0;      // mbarrier 0 of the CTA that consumes my layer 0
+    unsigned phase = 0;       // bit b: parity to wait for on mbarrier b
+    bool dead = false;        // a wait ran out: stop waiting, keep the trip counts
+    if constexpr (ASYNC) {
+        rmbar0 = map_to_rank(mbar0, (unsigned)((g % Kq) / M));
+        if (tid == 0) {
+            for (int b2 = 0; b2 < 4; ++b2)
+                asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(mbar0 + 8u * b2));
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+    }
+    // layer 0 of this thread (4 mantissas and the thread's exponent) to buffer b of its consumer
+    auto send = [&](unsigned b2, float v0, float v1, float v2, float v3, int w) {
+        if constexpr (ASYNC) {
+            if (tid == 0)   // the bytes this CTA will receive in that buffer
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mbar0 + 8u * b2), "r"(20u * M) : "memory");
+            asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];"
+                         ::"r"(dstx0 + b2 * bufx_bytes), "f"(v0), "f"(v1), "f"(v2), "f"(v3), "r"(rmbar0 + 8u * b2) : "memory");
+            asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.s32 [%0], %1, [%2];"
+                         ::"r"(dstw0 + b2 * bufw_bytes), "r"(w), "r"(rmbar0 + 8u * b2) : "memory");
+        } else {
+            st_cluster_v4(dstx0 + b2 * bufx_bytes, v0, v1, v2, v3);
+            st_cluster_s32(dstw0 + b2 * bufw_bytes, w);
+            cluster_arrive();
+        }
+    };
+    // layer 0 of every producer has landed in buffer b
+    auto receive = [&](unsigned b2) {
+        if constexpr (ASYNC) {
+            if (!dead && !fwd_mbar_wait(mbar0 + 8u * b2, (phase >> b2) & 1u)) {
+                dead = true;
+                atomicOr(&g_status, 4u);
+            }
+            phase ^= 1u << b2;
+        } else {
+            cluster_wait();
+        }
+    };
+    const unsigned cl_addr = smem_u32(s_cl);
+    const unsigned cli_addr = smem_u32(s_cl_i);
+
+    first_position(p, CS, tid, &s_seq);
+    for (;;) {
+        const int seq = next_sequence(p, rank, CS, tid, &s_seq);
+        if (seq < 0) break;
+
+        long long len = p.lens[seq];
+        if (len < 1 || len > p.maxlen) {
+            if (tid == 0 && rank == 0) atomicOr(&g_status, 1u);
+            len = len < 1 ? 1 : p.maxlen;
+        }
+        const uint8_t *obs = p.data + static_cast<long long>(seq) * p.maxlen;
+        const int T_len = static_cast<int>(len);
+        bool bad_obs = false;   // an observation byte outside the emission table was met
+
+        // ---- t = 0: x = exp(initial_prob) * exp(emission), W = 0 ------------------------
+        float2 x[RL][2];
+        int o_next;
+        int W = 0;       // exponent shared by this thread's 64 states
+        int kt;          // exponent of the largest mantissa (magnitude hint)
+        {
+            const int o0 = obs_at(p, obs, 0, bad_obs);
+            o_next = obs_at(p, obs, T_len > 1 ? 1 : 0, bad_obs);
+            const float4 e0 = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o0 * K + g));
+            const float el[4] = {fast_exp(e0.x), fast_exp(e0.y), fast_exp(e0.z), fast_exp(e0.w)};
+            float m = 0.0f;
+#pragma unroll
+            for (int d = 0; d < kLayers; ++d) {
+                const float4 v = __ldg(reinterpret_cast<const float4 *>(p.initial_prob + d * K + g));
+                const float4 r = make_float4(fast_exp(v.x) * el[0], fast_exp(v.y) * el[1], fast_exp(v.z) * el[2],
+                                             fast_exp(v.w) * el[3]);
+                m = max3(m, fmaxf(r.x, r.y), fmaxf(r.z, r.w));
+                if (d < RL) {
+                    x[d][0] = make_float2(r.x, r.y);
+                    x[d][1] = make_float2(r.z, r.w);
+                } else {
+                    tmem_st4(tm + 4 * (d - RL), r);
+                }
+            }
+            kt = exponent_of(m);
+            tmem_wait_st();
+        }
+        send(0u, x[0][0].x, x[0][0].y, x[0][1].x, x[0][1].y, W);
+
+        for (int t = 1; t < T_len; ++t) {
+            // this step's emission slice (in flight while the exchange completes); the observation after it
+            const float4 e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o_next * K + g));
+            o_next = obs_at(p, obs, t + 1 < T_len ? t + 1 : T_len - 1, bad_obs);
+            // the transition columns, in flight while the exchange completes
+            float4 t0, t1, t2, t3;
+            tmem_ld4(tm + 4 * (kLayers - RL), t0);
+            tmem_ld4(tm + 4 * (kLayers - RL) + 4, t1);
+            tmem_ld4(tm + 4 * (kLayers - RL) + 8, t2);
+            tmem_ld4(tm + 4 * (kLayers - RL) + 12, t3);
+
+            const unsigned buf = (unsigned)(t - 1) % NB;   // buffer that holds the previous step's layer 0
+            receive(buf);
+            const float *px = a0x + buf * 4 * M + tid;
+            const int *pw = a0w + buf * M + (tid >> 2);
+            const float xa0 = px[0], xa1 = px[M], xa2 = px[2 * M], xa3 = px[3 * M];
+            const int wp0 = pw[0], wp1 = pw[M >> 2], wp2 = pw[2 * (M >> 2)], wp3 = pw[3 * (M >> 2)];
+
+            // magnitude of each incoming value = sender exponent + exponent field of its mantissa;
+            // the new exponent is the largest magnitude this thread is about to combine
+            const int ea0 = xa0 > 0.0f ? wp0 + exponent_of(xa0) : kExpFloor - 200;
+            const int ea1 = xa1 > 0.0f ? wp1 + exponent_of(xa1) : kExpFloor - 200;
+            const int ea2 = xa2 > 0.0f ? wp2 + exponent_of(xa2) : kExpFloor - 200;
+            const int ea3 = xa3 > 0.0f ? wp3 + exponent_of(xa3) : kExpFloor - 200;
+            int Wn = max(max(ea0, ea1), max(ea2, ea3));
+            Wn = max(Wn, W + kt);
+            Wn = max(Wn, kExpFloor);
+            // incoming values relative to 2^Wn (a power-of-two factor: exact); Wn >= wp + exponent, so
+            // the product stays below 2; below 2^-126 it flushes to zero
+            const float2 y0 = dup2(xa0 * pow2_clamped(wp0 - Wn)), y1 = dup2(xa1 * pow2_clamped(wp1 - Wn));
+            const float2 y2 = dup2(xa2 * pow2_clamped(wp2 - Wn)), y3 = dup2(xa3 * pow2_clamped(wp3 - Wn));
+            const float2 own = dup2(pow2_clamped(W - Wn));
+            float2 QE[2], Eo[2];
+            {
+                tmem_wait_ld(t0, t1, t2, t3);
+                const float2 q0 = fma2(make_float2(t3.x, t3.y), y3, fma2(make_float2(t2.x, t2.y), y2,
+                                  fma2(make_float2(t1.x, t1.y), y1, mul2(make_float2(t0.x, t0.y), y0))));
+                const float2 q1 = fma2(make_float2(t3.z, t3.w), y3, fma2(make_float2(t2.z, t2.w), y2,
+                                  fma2(make_float2(t1.z, t1.w), y1, mul2(make_float2(t0.z, t0.w), y0))));
+                const float2 el2[2] = {make_float2(fast_exp(e.x), fast_exp(e.y)), make_float2(fast_exp(e.z), fast_exp(e.w))};
+                QE[0] = mul2(q0, el2[0]);
+                QE[1] = mul2(q1, el2[1]);
+                Eo[0] = mul2(el2[0], own);
+                Eo[1] = mul2(el2[1], own);
+            }
+            // layer 0 first: it is what the other CTAs wait for
+            // exp(trans2) of four layers per shared-memory load (the shared-memory pipe bounds this kernel)
+            float4 a4 = s_A4[0];
+            const auto A_of = [&](int d) { return dup2(d % 4 == 0 ? a4.x : d % 4 == 1 ? a4.y : d % 4 == 2 ? a4.z : a4.w); };
+            {
+                const float2 a = A_of(0);
+                x[0][0] = fma2(a, QE[0], mul2(Eo[0], x[1][0]));
+                x[0][1] = fma2(a, QE[1], mul2(Eo[1], x[1][1]));
+            }
+            send((unsigned)t % NB, x[0][0].x, x[0][0].y, x[0][1].x, x[0][1].y, Wn);
+            float m = max3(fmaxf(x[0][0].x, x[0][0].y), x[0][1].x, x[0][1].y);
+#pragma unroll
+            for (int d = 1; d < RL - 1; ++d) {
+                if (d % 4 == 0) a4 = s_A4[d / 4];
+                const float2 a = A_of(d);
+                x[d][0] = fma2(a, QE[0], mul2(Eo[0], x[d + 1][0]));
+                x[d][1] = fma2(a, QE[1], mul2(Eo[1], x[d + 1][1]));
+                m = max3(m, x[d][0].x, x[d][0].y);
+                m = max3(m, x[d][1].x, x[d][1].y);
+            }
+            float4 nxt, nxt2;   // old values of the next layer, fetched one layer ahead
+            tmem_ld4(tm, nxt);      // layer 8 (old)
+            tmem_wait_ld(nxt);
+            tmem_ld4(tm + 4, nxt2); // layer 9 (old)
+            {
+                const float2 a = A_of(RL - 1);
+                x[RL - 1][0] = fma2(a, QE[0], mul2(Eo[0], make_float2(nxt.x, nxt.y)));
+                x[RL - 1][1] = fma2(a, QE[1], mul2(Eo[1], make_float2(nxt.z, nxt.w)));
+                m = max3(m, x[RL - 1][0].x, x[RL - 1][0].y);
+                m = max3(m, x[RL - 1][1].x, x[RL - 1][1].y);
+            }
+#pragma unroll
+            for (int d = RL; d < kLayers; ++d) {
+                // old value of layer min(d+1, 15); layers 14 and 15 both read old layer 15. Layer d + 1
+                // was requested during layer d - 1; layer d + 2 is requested now, before layer d is
+                // written (a load has completed before anything overwrites its columns).
+                if (d < kLayers - 1) {
+                    float4 &cur = (d & 1) ? nxt : nxt2, &ahead = (d & 1) ? nxt2 : nxt;
+                    tmem_wait_ld(cur);
+                    if (d + 2 < kLayers) tmem_ld4(tm + 4 * (d + 2 - RL), ahead);
+                }
+                const float4 &old = (d < kLayers - 1) ? ((d & 1) ? nxt : nxt2) : ((d & 1) ? nxt2 : nxt);
+                float2 v0 = make_float2(old.x, old.y), v1 = make_float2(old.z, old.w);
+                if (d >= 14) {
+                    const float c = d == 15 ? p.gamma_lin : p.synthetic_lin;
+                    v0.x *= c; v0.y *= c; v1.x *= c; v1.y *= c;
+                }
+                if (d % 4 == 0) a4 = s_A4[d / 4];
+                const float2 a = A_of(d);
+                const float2 r0 = fma2(a, QE[0], mul2(Eo[0], v0));
+                const float2 r1 = fma2(a, QE[1], mul2(Eo[1], v1));
+                tmem_st4(tm + 4 * (d - RL), make_float4(r0.x, r0.y, r1.x, r1.y));
+                m = max3(m, r0.x, r0.y);
+                m = max3(m, r1.x, r1.y);
+            }
+            kt = exponent_of(m);
+            W = Wn;
+            tmem_wait_st();   // the next step reads what this one stored
+        }
+        receive((unsigned)(T_len - 1) % NB);   // the last round is not used, but it must have landed
+
+        // ---- log-likelihood: log(sum of all states) with a common exponent --------------
+        int gexp = W + kt;
+        gexp = __reduce_max_sync(0xffffffffu, gexp);
+        if (lane == 0) s_warp_i[warp] = gexp;
+        __syncthreads();
+        if (tid < (int)CS) {
+            int v = kExpFloor - 200;
+            for (int w = 0; w < nwarps; ++w) v = max(v, s_warp_i[w]);
+            st_cluster_s32(map_to_rank(cli_addr + 4u * rank, tid), v);
+        }
+        cluster_arrive();
+        cluster_wait();
+        int G = kExpFloor - 200;
+        for (unsigned r = 0; r < CS; ++r) G = max(G, s_cl_i[r]);
+        float tsum = 0.0f;
+#pragma unroll
+        for (int d = 0; d < RL; ++d) tsum += (x[d][0].x + x[d][0].y) + (x[d][1].x + x[d][1].y);
+#pragma unroll
+        for (int d = 0; d < kLayers - RL; ++d) {
+            float4 v;
+            tmem_ld4(tm + 4 * d, v);
+            tmem_wait_ld(v);
+            tsum += (v.x + v.y) + (v.z + v.w);
+        }
+        tsum *= pow2_clamped(W - G);
+        tsum = pb::warp_sum(tsum);
+        if (lane == 0) s_warp[warp] = tsum;
+        __syncthreads();
+        if (tid < (int)CS) {
+            float sacc = 0.0f;
+            for (int w = 0; w < nwarps; ++w) sacc += s_warp[w];
+            st_cluster_f32(map_to_rank(cl_addr + 4u * rank, tid), sacc);
+        }
+        cluster_arrive();
+        cluster_wait();
+        if (rank == 0 && tid == 0) {
+            double sacc = 0.0;
+            for (unsigned r = 0; r < CS; ++r) sacc += (double)s_cl[r];
+            // natural log of sum * 2^G; an impossible sequence (sum == 0) gives -inf
+            p.result[seq] = sacc > 0.0 ? (float)(log(sacc) + (double)G * 0.6931471805599453) : -INFINITY;
+            flag_bad_observation(bad_obs, true);
+        }
+        if (p.write_alpha) {
+            float *dst_alpha = ((len & 1) ? p.alpha1 : p.alpha2) + (long long)seq * (kLayers * (long long)K);
+            const float wl = (float)W * kLn2;
+#pragma unroll
+            for (int d = 0; d < kLayers; ++d) {
+                float4 s4 = make_float4(x[d % RL][0].x, x[d % RL][0].y,
+                                        x[d % RL][1].x, x[d % RL][1].y);
+                if (d >= RL) {
+                    tmem_ld4(tm + 4 * (d - RL), s4);
+                    tmem_wait_ld(s4);
+                }
+                float4 v;
+                v.x = fast_log(s4.x) + wl;
+                v.y = fast_log(s4.y) + wl;
+                v.z = fast_log(s4.z) + wl;
+                v.w = fast_log(s4.w) + wl;
+                *reinterpret_cast<float4 *>(dst_alpha + (long long)d * K + g) = v;
+            }
+        }
+        // the next pop starts with a full cluster barrier
+    }
+    tmem_publish();   // every warp is done with its columns
+    if (warp == 0) tmem_free_all(tm_all);
+}
+
 // ---- streaming kernels --------------------------------------------------------
 __global__ void hmm_stream_init(const FwdParams p) {
     const long long N = (long long)kLayers * p.K;
     const long long state = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const int inst = blockIdx.y;
     if (state >= N) return;
-    const int o = obs_at(p, p.data + (long long)inst * p.maxlen, 0);
+    bool bad_obs = false;
+    const int o = obs_at(p, p.data + (long long)inst * p.maxlen, 0, bad_obs);
+    flag_bad_observation(bad_obs, state == 0);
     p.alpha1[inst * N + state] = p.initial_prob[state] + p.output_prob[(long long)o * p.K + state % p.K];
 }
 
@@ -1759,7 +2180,9 @@ __global__ void hmm_stream_step(const FwdParams p, int t) {
     if (t >= p.lens[inst]) return;  // benchmarks/forward.py:113: no write past the end
     const float *src = ((t & 1) ? p.alpha1 : p.alpha2) + inst * N;
     float *dst = ((t & 1) ? p.alpha2 : p.alpha1) + inst * N;
-    const int o = obs_at(p, p.data + (long long)inst * p.maxlen, t);
+    bool bad_obs = false;
+    const int o = obs_at(p, p.data + (long long)inst * p.maxlen, t, bad_obs);
+    flag_bad_observation(bad_obs, state == 0);
     const int s = static_cast<int>(state % K);
     const int d = static_cast<int>(state / K);
     const int Kq = K >> 2;
@@ -1815,6 +2238,7 @@ struct Plan {
     bool split = false;  // layers 8..15 in shared memory, 1024 threads per CTA
     bool scaled = false; // extended-range linear arithmetic instead of log space
     bool cta = false;    // one 256-thread CTA per sequence, packed arithmetic (K = 1024)
+    bool tmem = false;   // scaled split layout with layers 8..15 and transition columns in tensor memory
 };
 
 // Picks (k-mers per thread, threads per CTA, CTAs per cluster) with
@@ -1876,13 +2300,53 @@ bool make_plan(long long K, Plan *pl, bool allow_split, bool need_kpt4 = false) 
 
 using ResidentKernel = void (*)(const FwdParams);
 
+// Completes a plan made by make_plan: where tensor memory takes the place of shared memory.
+// Every entry point calls this, so that the same state space always runs the same kernel.
+// PARPY_B200_FWD_POLY (the scalar-twin comparisons of the tests) selects the kernels that keep
+// layers 8..15 in shared memory; PARPY_B200_FWD_TMEM=0 / PARPY_B200_SCALED_TMEM=0 do so too.
+void finish_plan(Plan *pl, bool five, bool scaled) {
+    pl->scaled = scaled;
+    pl->tmem = false;
+    if (!pl->split || five) return;
+    int packed = 1;
+    if (const char *env = getenv("PARPY_B200_FWD_PACKED")) packed = atoi(env);
+    const char *env = getenv(scaled ? "PARPY_B200_SCALED_TMEM" : "PARPY_B200_FWD_TMEM");
+    pl->tmem = (env == nullptr || atoi(env) != 0) && (scaled || (packed && getenv("PARPY_B200_FWD_POLY") == nullptr));
+}
+
 ResidentKernel pick_kernel(const Plan &pl, bool five) {
     const int kpt = pl.kpt;
+    int rl = 0;   // layers kept in registers by the tensor-memory kernels (0: the kernel's default)
+    if (const char *env = getenv("PARPY_B200_FWD_REGLAYERS")) rl = atoi(env);
+    if (pl.scaled && pl.tmem) {
+        // Measured on the benchmark workload (state-steps/s), layers in registers / exchange:
+        // 6 / st.async 4.76e12, 4 / st.async 4.65e12, 8 / st.async 4.46e12, 6 / barrier 4.44e12,
+        // 4 / barrier 4.22e12, 8 / barrier 4.14e12; shared memory instead of tensor memory 3.77e12.
+        bool async_x = pl.cs >= 2 && pl.cs <= 8;
+        if (const char *env = getenv("PARPY_B200_SCALED_ASYNC")) async_x = async_x && atoi(env) != 0;
+        if (async_x) return rl == 4 ? hmm_forward_scaled_tmem<4, true> : rl == 8 ? hmm_forward_scaled_tmem<8, true> : hmm_forward_scaled_tmem<6, true>;
+        return rl == 4 ? hmm_forward_scaled_tmem<4, false> : rl == 8 ? hmm_forward_scaled_tmem<8, false> : hmm_forward_scaled_tmem<6, false>;
+    }
     if (pl.scaled) return pl.split ? hmm_forward_scaled_split : hmm_forward_scaled;
     if (pl.cta && !five) {
-        int npoly = 8;   // measured on 100 sequences x 2000 steps: 8 -> 2.67 ms, 10 -> 2.69, 12 -> 2.81
-
-        if (const char *env = getenv("PARPY_B200_FWD_POLY")) npoly = atoi(env);
+        if (const char *mk = getenv("PARPY_B200_FWD_MASKS")) {
+            unsigned ex = 0, lg = 0;
+            if (sscanf(mk, "%x:%x", &ex, &lg) == 2) {
+#define PB_MASKS(E, L) if (ex == E && lg == L) return hmm_forward_packed_cta<E, L>
+                PB_MASKS(0x0000u, 0xEEECu);
+                PB_MASKS(0x0000u, 0xFFFEu);
+                PB_MASKS(0xAAAAu, 0x5554u);
+                PB_MASKS(0xAAAAu, 0x5555u);
+                PB_MASKS(0x0000u, 0xAAAAu);
+                PB_MASKS(0x8888u, 0x7776u);
+#undef PB_MASKS
+            }
+        }
+        // Measured on 100 sequences x 2000 steps: logarithm of 11 layers as polynomial (mask 0xEEEC, all
+        // exponentials on the MUFU pipe) 2.64 ms; of the odd layers 2.71; of all but layer 0 2.69;
+        // exponential of the odd layers as polynomial (the earlier default) 2.72; both kinds mixed 2.84-2.93.
+        if (getenv("PARPY_B200_FWD_POLY") == nullptr) return hmm_forward_packed_cta<0x0000u, 0xEEECu>;
+        const int npoly = atoi(getenv("PARPY_B200_FWD_POLY"));   // exponential masks only
         switch (npoly) {
             case 0: return hmm_forward_packed_cta<0x0000u>;
             case 5: return hmm_forward_packed_cta<0x2492u>;
@@ -1895,40 +2359,60 @@ ResidentKernel pick_kernel(const Plan &pl, bool five) {
         }
     }
     if (pl.split && !five) {
-        // how many of the 16 layers take the polynomial exponential
-        int npoly = 5;
-        if (const char *env = getenv("PARPY_B200_FWD_POLY")) npoly = atoi(env);
         int packed = 1;
         if (const char *env = getenv("PARPY_B200_FWD_PACKED")) packed = atoi(env);
+        // "PARPY_B200_FWD_MASKS=<exp mask>:<log mask>" (hex) picks, among the compiled combinations,
+        // which layers take their exponential / their logarithm on the FMA pipe
+        unsigned ex = 0, lg = 0;
+        bool masks = false;
+        if (const char *mk = getenv("PARPY_B200_FWD_MASKS")) masks = sscanf(mk, "%x:%x", &ex, &lg) == 2;
+        if (packed && pl.tmem) {
+            // Default for 4096 k-mers and more. Measured on the benchmark workload (state-steps/s):
+            // logarithm of layers 2,3,5,6,7,9,10,11,13,14,15 as polynomial, 4 layers in registers
+            // 1.911e12; same with 8 in registers 1.905e12, 6: 1.891e12; layers 1,2,3,5,... (12) 1.897e12;
+            // exponential of the even layers but 0 as polynomial and no logarithm (the earlier
+            // default) 1.835e12 in tensor memory, 1.817e12 in shared memory.
+            if (masks) {
+                if (ex == 0x0000u && lg == 0xEEEEu) return rl == 8 ? hmm_forward_packed<0x0000u, 0xEEEEu, true, 8> : hmm_forward_packed<0x0000u, 0xEEEEu, true, 4>;
+                if (ex == 0x5554u && lg == 0x0000u) return rl == 4 ? hmm_forward_packed<0x5554u, 0x0000u, true, 4> : hmm_forward_packed<0x5554u, 0x0000u, true, 8>;
+            }
+            return rl == 8 ? hmm_forward_packed<0x0000u, 0xEEECu, true, 8>
+                 : rl == 6 ? hmm_forward_packed<0x0000u, 0xEEECu, true, 6> : hmm_forward_packed<0x0000u, 0xEEECu, true, 4>;
+        }
         if (packed) {
-            // layer 0 stays on the MUFU pipe in every mask: it is on the path to the exchange.
-            // Measured on the benchmark workload (state-steps/s): even layers but 0 (7 layers) 1.799e12,
-            // layers 1..8 1.793e12, odd layers 1.764e12, 9 layers 1.747e12, 10 layers 1.751e12,
-            // 11 layers 1.712e12, layers 8..15 1.707e12.
-            if (!getenv("PARPY_B200_FWD_POLY")) npoly = 7;
-            // experiment: logarithms of N layers on the FMA pipe (exponentials all on the MUFU pipe)
-            if (const char *lg = getenv("PARPY_B200_FWD_LG")) {
-                switch (atoi(lg)) {
-                    case 12: return hmm_forward_packed<0x0000u, 0xEEEEu>;
-                    case 13: return hmm_forward_packed<0x0000u, 0xFBFAu>;
-                    case 14: return hmm_forward_packed<0x0000u, 0xFEFEu>;
-                    case 15: return hmm_forward_packed<0x0000u, 0xFFFEu>;
-                    case 16: return hmm_forward_packed<0x0000u, 0xFFFFu>;
-                    case 114: return hmm_forward_packed<0x0100u, 0xFEFEu>;
-                    default: break;
+            // layers 8..15 in shared memory. Measured (state-steps/s), logarithm masks with all
+            // exponentials on the MUFU pipe: 0xEEEC 1.888e12, 0x6EEE 1.881e12, 0x3FFC 1.876e12, 0xEEEE
+            // 1.870e12, 0xFEFE 1.863e12, 0xFFF0 1.862e12, 0xAAAA 1.859e12, 0x7FFE 1.858e12, 0xFFFE 1.845e12,
+            // 0xFFFF 1.841e12; with exponentials as well: 0x1110:0xEEEE 1.785e12, 0x5554:0xAAAA 1.724e12.
+            // Exponential masks alone: even layers but 0 (7 layers) 1.817e12, layers 1..8 1.793e12, odd
+            // layers 1.764e12, 9 layers 1.747e12, 10 layers 1.751e12, 11 layers 1.712e12.
+            if (masks) {
+#define PB_MASKS(E, L) if (ex == E && lg == L) return hmm_forward_packed<E, L>
+                PB_MASKS(0x0000u, 0xEEEEu);
+                PB_MASKS(0x0000u, 0xFEFEu);
+                PB_MASKS(0x0000u, 0xFFFEu);
+                PB_MASKS(0x0000u, 0xFFFFu);
+                PB_MASKS(0x5554u, 0xAAAAu);
+                PB_MASKS(0x0000u, 0xAAAAu);
+                PB_MASKS(0x0000u, 0x6EEEu);
+#undef PB_MASKS
+            }
+            if (const char *env = getenv("PARPY_B200_FWD_POLY")) {
+                switch (atoi(env)) {   // exponential masks only: the scalar kernel's twins
+                    case 0: return hmm_forward_packed<0x0000u>;
+                    case 5: return hmm_forward_packed<0x2492u>;   // layers 1,4,7,10,13
+                    case 8: return hmm_forward_packed<0xAAAAu>;   // odd layers
+                    case 9: return hmm_forward_packed<0xAD5Au>;   // all but 0,2,5,7,9,12,14
+                    case 10: return hmm_forward_packed<0x6DB6u>;  // all but 0,3,6,9,12,15
+                    case 11: return hmm_forward_packed<0xDB6Eu>;  // all but 0,4,7,10,13
+                    case 12: return hmm_forward_packed<0xEEEEu>;  // all but 0,4,8,12
+                    default: return hmm_forward_packed<0x5554u>;  // 7: even layers but 0
                 }
             }
-            switch (npoly) {
-                case 0: return hmm_forward_packed<0x0000u>;
-                case 5: return hmm_forward_packed<0x2492u>;   // layers 1,4,7,10,13
-                case 8: return hmm_forward_packed<0xAAAAu>;   // odd layers
-                case 9: return hmm_forward_packed<0xAD5Au>;   // all but 0,2,5,7,9,12,14
-                case 10: return hmm_forward_packed<0x6DB6u>;  // all but 0,3,6,9,12,15
-                case 11: return hmm_forward_packed<0xDB6Eu>;  // all but 0,4,7,10,13
-                case 12: return hmm_forward_packed<0xEEEEu>;  // all but 0,4,8,12
-                default: return hmm_forward_packed<0x5554u>;  // 7: even layers but 0
-            }
+            return hmm_forward_packed<0x0000u, 0xEEECu>;
         }
+        int npoly = 5;   // how many of the 16 layers take the polynomial exponential
+        if (const char *env = getenv("PARPY_B200_FWD_POLY")) npoly = atoi(env);
         switch (npoly) {
             case 0: return hmm_forward_split<0x0000u>;
             case 4: return hmm_forward_split<0x2222u>;   // layers 1,5,9,13
@@ -1946,10 +2430,12 @@ int32_t resident_config(const Plan &pl, bool five, cudaLaunchConfig_t *cfg,
     ResidentKernel k = pick_kernel(pl, five);
     size_t smem = size_t(2) * 4 * (size_t(pl.nt) * pl.kpt / 4) * sizeof(float);
     if (pl.cta && !five && !pl.scaled) smem = 0;  // static shared memory only
+    else if (pl.scaled && pl.tmem)    // the exchange only: mantissas + sender exponents, up to four buffers
+        smem = size_t(20) * pl.nt * sizeof(float);
     else if (pl.scaled && pl.split)   // mantissas + sender exponents, 3 transition columns, layers 8..15
         smem = size_t(10) * pl.nt * sizeof(float) + size_t(3 + 8) * pl.nt * sizeof(float4);
     else if (pl.scaled) smem *= 2;  // mantissas + exponents
-    else if (pl.split && !five) smem += size_t(4 + 8) * pl.nt * sizeof(float4);  // transition columns + layers 8..15
+    else if (pl.split && !five && !pl.tmem) smem += size_t(4 + 8) * pl.nt * sizeof(float4);  // transition columns + layers 8..15
     if (pl.cs > 8) PB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
     PB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     memset(cfg, 0, sizeof(*cfg));
@@ -2052,7 +2538,7 @@ int32_t forward_impl(float gamma, const float *initial_prob, int64_t num_states,
     const bool resident = !streaming_forced && make_plan(K, &pl, !five, scaled);
     PB_REQUIRE(!scaled || (resident && pl.kpt == 4),
                "forward: the scaled kernel needs at least 1024 k-mers (num_states=%lld)", (long long)num_states);
-    pl.scaled = scaled;
+    if (resident) finish_plan(&pl, five, scaled);
     if (resident) {
         PB_REQUIRE(pl.kpt == 1 || (pb::aligned16(initial_prob) && pb::aligned16(output_prob) &&
                                    pb::aligned16(trans1) &&
@@ -2149,6 +2635,7 @@ int32_t parpy_b200_forward_plan(int64_t num_states, int64_t num_instances, int32
         pb::set_error("forward_plan: num_states=%lld has no resident mapping", (long long)num_states);
         return PB_ERR_UNSUPPORTED;
     }
+    finish_plan(&pl, false, false);
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[1];
     int max_clusters = 0;
@@ -2240,6 +2727,7 @@ extern "C" int32_t parpy_b200_forward_noalloc(float gamma, const float *initial_
     PB_REQUIRE(make_plan(K, &pl, true),
                "forward_noalloc: num_states=%lld has no resident mapping (the streaming kernel needs "
                "caller scratch: use parpy_b200_forward)", (long long)num_states);
+    finish_plan(&pl, false, false);
     PB_REQUIRE(pl.kpt == 1 || (pb::aligned16(initial_prob) && pb::aligned16(output_prob) && pb::aligned16(trans1)),
                "forward_noalloc: tables must be 16-byte aligned");
     pb::DeviceInfo dev;

@@ -250,6 +250,97 @@ __global__ void __launch_bounds__(256) sddmm_nnz(const float *__restrict__ A, co
 }
 
 
+// Long dot products (K = 256 .. 1024, a multiple of 128): with 4 lanes per non-zero the A row
+// of a non-zero is read again for every non-zero of that row, and both operands go through the
+// L1 data pipe, which is what bounds sddmm_nnz at K = 1024 (87 % busy). Here a warp walks a
+// contiguous run of non-zeros (CSR order: runs of equal rows) and keeps the current A row in
+// registers, K / 32 elements per lane, so that only the gathered row of B^T moves per non-zero;
+// U non-zeros are in flight at once (all loads before the math), each reduced with a butterfly.
+template <int NV, int U>   // NV = K / 128 float4 per lane and operand row
+__global__ void __launch_bounds__(256) sddmm_rowcache(const float *__restrict__ A, const float *__restrict__ Bt,
+                                                      const int64_t *__restrict__ rows,
+                                                      const int64_t *__restrict__ cols,
+                                                      const float *__restrict__ cvalues, float *__restrict__ D,
+                                                      long long nnz, float alpha, float beta) {
+    constexpr int K = 128 * NV;
+    const int lane = threadIdx.x & 31;
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    long long per = (nnz + nwarps - 1) / nwarps;
+    per = (per + U - 1) / U * U;
+    const long long lo = warp * per, hi = pb::ll_min(nnz, lo + per);
+    float4 ar[NV];
+    long long cur = -1;
+    for (long long i = lo; i < hi; i += U) {
+        long long r[U], c[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long long j = i + u < hi ? i + u : hi - 1;   // clamp: harmless duplicate work
+            r[u] = __ldg(rows + j);
+            c[u] = __ldg(cols + j);
+        }
+        bool same = true;
+#pragma unroll
+        for (int u = 1; u < U; ++u) same = same && r[u] == r[0];
+        float acc[U];
+        if (same) {
+            if (r[0] != cur) {
+                cur = r[0];
+#pragma unroll
+                for (int v = 0; v < NV; ++v)
+                    ar[v] = __ldg(reinterpret_cast<const float4 *>(A + cur * K + 4 * lane + 128 * v));
+            }
+            float4 q[U][NV];
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+                for (int v = 0; v < NV; ++v)
+                    q[u][v] = __ldg(reinterpret_cast<const float4 *>(Bt + c[u] * K + 4 * lane + 128 * v));
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                float a = 0.0f;
+#pragma unroll
+                for (int v = 0; v < NV; ++v) {
+                    a = fmaf(ar[v].x, q[u][v].x, a);
+                    a = fmaf(ar[v].y, q[u][v].y, a);
+                    a = fmaf(ar[v].z, q[u][v].z, a);
+                    a = fmaf(ar[v].w, q[u][v].w, a);
+                }
+                acc[u] = a;
+            }
+        } else {
+            // the group straddles a row boundary: one non-zero at a time
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (r[u] != cur) {
+                    cur = r[u];
+#pragma unroll
+                    for (int v = 0; v < NV; ++v)
+                        ar[v] = __ldg(reinterpret_cast<const float4 *>(A + cur * K + 4 * lane + 128 * v));
+                }
+                float a = 0.0f;
+#pragma unroll
+                for (int v = 0; v < NV; ++v) {
+                    const float4 qv = __ldg(reinterpret_cast<const float4 *>(Bt + c[u] * K + 4 * lane + 128 * v));
+                    a = fmaf(ar[v].x, qv.x, a);
+                    a = fmaf(ar[v].y, qv.y, a);
+                    a = fmaf(ar[v].z, qv.z, a);
+                    a = fmaf(ar[v].w, qv.w, a);
+                }
+                acc[u] = a;
+            }
+        }
+        float mine = 0.0f;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], o);
+            if (lane == u) mine = acc[u];
+        }
+        if (lane < U && i + lane < hi) D[i + lane] = alpha * mine + beta * __ldg(cvalues + i + lane);
+    }
+}
+
 // ------------------------------------------------------------------- SpMM ----
 // C[i, j] += sum over the non-zeros a of row i of values[a] * B[cols[a], j]
 // (test/test_spmm.py:16-24). The reference gives every cell (i, j) its own
@@ -323,10 +414,24 @@ int32_t sddmm_common(const float *A, const float *B, const int64_t *crows, int64
     } while (0)
     // measured at 8192 x 8192, 1 %, K = 64: <4,2,2> 38.9 us for the whole call, <8,4,2> 40.0,
     // <8,8,1> 46, <16,8,1> 73 (the old half-warp-per-non-zero kernel: 64)
-    if (!vec) PB_SDDMM(false, 8, 4, 1);
+#define PB_SDDMM_ROWS(NV, U)                                                                                  \
+    do {                                                                                                      \
+        int per_sm = 0;                                                                                       \
+        PB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, sddmm_rowcache<NV, U>, 256, 0));       \
+        const long long blocks = std::max<long long>(                                                         \
+            1, std::min<long long>((nnz + 8 * U - 1) / (8 * U), (long long)std::max(per_sm, 1) * dev.sm_count)); \
+        sddmm_rowcache<NV, U><<<(unsigned)blocks, 256, 0, stream>>>(A, Bt, rows, cols, cvalues, D, nnz,       \
+                                                                    (float)alpha, (float)beta);               \
+    } while (0)
+    // long dot products: the A row stays in registers (0.29 -> see the kernel's comment); cfg 2 keeps the gather kernel
+    if (vec && cfg != 2 && K == 1024) PB_SDDMM_ROWS(8, 2);
+    else if (vec && cfg != 2 && K == 512) PB_SDDMM_ROWS(4, 4);
+    else if (vec && cfg != 2 && K == 256) PB_SDDMM_ROWS(2, 8);
+    else if (!vec) PB_SDDMM(false, 8, 4, 1);
     else if (cfg == 1) PB_SDDMM(true, 8, 4, 2);
     else PB_SDDMM(true, 4, 2, 2);
 #undef PB_SDDMM
+#undef PB_SDDMM_ROWS
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }

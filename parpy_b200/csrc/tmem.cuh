@@ -1,0 +1,53 @@
+// Tensor memory (TMEM, 512 columns x 128 lanes x 32 bit per SM on sm_100a) used as per-thread
+// scratch: tcgen05.alloc / dealloc, and the 32x32b load/store shapes that move N consecutive
+// columns of the warp's own 32 lanes to or from N registers of each thread. Warp w of a CTA may
+// only touch lanes 32 * (w % 4) .. 32 * (w % 4) + 31. Measured on B200 with 1024 threads each
+// reading and writing 8 x 16 bytes per iteration: 568 cycles per iteration against 1926 through
+// shared memory (128 bytes per clock), results identical.
+#pragma once
+
+namespace {
+
+// Allocates all 512 columns for this CTA (warp 0 calls it, all 32 lanes) and leaves the base
+// address in *slot (shared memory). Every thread reads *slot after tmem_publish().
+__device__ __forceinline__ void tmem_alloc_all(unsigned *slot) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;"
+                 ::"r"(static_cast<unsigned>(__cvta_generic_to_shared(slot))) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+// CTA-wide barrier that also orders tensor-memory operations before and after it.
+__device__ __forceinline__ void tmem_publish() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+// Frees the allocation (warp 0, all 32 lanes, after every warp's last access: call tmem_publish first).
+__device__ __forceinline__ void tmem_free_all(unsigned base) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(base) : "memory");
+}
+// Address of column `col` in the calling warp's lane quarter.
+__device__ __forceinline__ unsigned tmem_warp_base(unsigned base, int warp, int col) {
+    return base + (static_cast<unsigned>(32 * (warp & 3)) << 16) + static_cast<unsigned>(col);
+}
+__device__ __forceinline__ void tmem_ld4(unsigned taddr, float4 &v) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st4(unsigned taddr, const float4 &v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};"
+                 ::"r"(taddr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+// All earlier loads (stores) of the calling thread have completed. The overloads name the
+// registers a load filled, so that no use of them can be scheduled ahead of the wait.
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_ld(float4 &a) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" : "+f"(a.x), "+f"(a.y), "+f"(a.z), "+f"(a.w)::"memory");
+}
+__device__ __forceinline__ void tmem_wait_ld(float4 &a, float4 &b, float4 &c, float4 &d) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+f"(a.x), "+f"(a.y), "+f"(a.z), "+f"(a.w), "+f"(b.x), "+f"(b.y), "+f"(b.z), "+f"(b.w),
+                   "+f"(c.x), "+f"(c.y), "+f"(c.z), "+f"(c.w), "+f"(d.x), "+f"(d.y), "+f"(d.z), "+f"(d.w)::"memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+}  // namespace

@@ -159,14 +159,17 @@ def forward_schedule(lens, clusters):
 
 def forward_status():
     """Reads and clears the forward kernels' device status word (synchronises the
-    device). Returns ``{"length_clamped": bool, "observation_clamped": bool}``:
-    a sequence length outside [1, maxlen], or an observation byte that is not a
-    row of ``output_prob``, was met (and clamped) by a call since the last read."""
+    device). Returns ``{"length_clamped": bool, "observation_clamped": bool,
+    "wait_timed_out": bool}``: a sequence length outside [1, maxlen], or an
+    observation byte that is not a row of ``output_prob``, was met (and clamped)
+    by a call since the last read; or a bounded wait for another CTA's values ran
+    out inside a kernel, in which case the results of those calls are not valid."""
     import ctypes
     from . import _native
     st = ctypes.c_uint32(0)
     _native.check(_native.lib().parpy_b200_forward_status(ctypes.byref(st)), "forward_status")
-    return {"length_clamped": bool(st.value & 1), "observation_clamped": bool(st.value & 2)}
+    return {"length_clamped": bool(st.value & 1), "observation_clamped": bool(st.value & 2),
+            "wait_timed_out": bool(st.value & 4)}
 
 
 def viterbi_status():

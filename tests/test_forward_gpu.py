@@ -199,9 +199,18 @@ def test_kernel_layout_variants_agree_with_oracle(native, oracle_mod, monkeypatc
     dh, ds = to_dev(hmm), to_dev(seqs)
     settings = ([{"PARPY_B200_FWD_SPLIT": "0"}]
                 + [{"PARPY_B200_FWD_PACKED": "0", "PARPY_B200_FWD_POLY": str(n)} for n in (0, 4, 5, 6, 8)]
-                + [{"PARPY_B200_FWD_POLY": str(n)} for n in (0, 5, 8, 9, 10, 11, 12)])
+                + [{"PARPY_B200_FWD_POLY": str(n)} for n in (0, 5, 8, 9, 10, 11, 12)]
+                # default layout (upper layers and transition columns in tensor memory, logarithm of 11
+                # layers as polynomial) with 4 (default), 6 and 8 layers in registers; other masks; the same
+                # kernels with shared memory in place of tensor memory
+                + [{}, {"PARPY_B200_FWD_REGLAYERS": "6"}, {"PARPY_B200_FWD_REGLAYERS": "8"},
+                   {"PARPY_B200_FWD_MASKS": "0:EEEE"}, {"PARPY_B200_FWD_MASKS": "5554:0", "PARPY_B200_FWD_REGLAYERS": "4"},
+                   {"PARPY_B200_FWD_TMEM": "0"}, {"PARPY_B200_FWD_TMEM": "0", "PARPY_B200_FWD_MASKS": "0:FFFF"},
+                   {"PARPY_B200_FWD_TMEM": "0", "PARPY_B200_FWD_MASKS": "5554:AAAA"}])
+    knobs = ("PARPY_B200_FWD_SPLIT", "PARPY_B200_FWD_POLY", "PARPY_B200_FWD_PACKED", "PARPY_B200_FWD_TMEM",
+             "PARPY_B200_FWD_MASKS", "PARPY_B200_FWD_REGLAYERS")
     for env in settings:
-        for k in ("PARPY_B200_FWD_SPLIT", "PARPY_B200_FWD_POLY", "PARPY_B200_FWD_PACKED"):
+        for k in knobs:
             monkeypatch.delenv(k, raising=False)
         for k, v in env.items():
             monkeypatch.setenv(k, v)
@@ -216,8 +225,9 @@ def test_kernel_layout_variants_agree_with_oracle(native, oracle_mod, monkeypatc
     seqs = synthetic.hmm_sequences(9, 2, 120, seed=8)
     exp, exp_alpha = oracle_mod.forward(hmm, seqs, want_alpha=True)
     dh, ds = to_dev(hmm), to_dev(seqs)
-    for env in [{"PARPY_B200_FWD_PACKED": "0"}] + [{"PARPY_B200_FWD_POLY": str(n)} for n in (0, 5, 8, 10, 12, 14, 16)]:
-        for k in ("PARPY_B200_FWD_SPLIT", "PARPY_B200_FWD_POLY", "PARPY_B200_FWD_PACKED"):
+    for env in ([{"PARPY_B200_FWD_PACKED": "0"}] + [{"PARPY_B200_FWD_POLY": str(n)} for n in (0, 5, 8, 10, 12, 14, 16)]
+                + [{"PARPY_B200_FWD_MASKS": m} for m in ("0:EEEC", "0:FFFE", "AAAA:5554", "AAAA:5555", "0:AAAA", "8888:7776")]):
+        for k in knobs:
             monkeypatch.delenv(k, raising=False)
         for k, v in env.items():
             monkeypatch.setenv(k, v)
@@ -291,23 +301,33 @@ def test_scaled_variant_against_golden_oracle_and_log_space(native, oracle_mod):
 
 @pytest.mark.parametrize("k,nseq,lo,hi", [(7, 40, 30, 400), (6, 50, 1, 300)])
 def test_scaled_layouts_agree_bit_for_bit(native, monkeypatch, k, nseq, lo, hi):
-    # The scaled kernel in its two layouts: clusters of 512-thread CTAs with all 16 layers in registers
-    # (PARPY_B200_SCALED_SPLIT=0), and 1024-thread CTAs with layers 8..15 in shared memory and one
-    # exponent per sending thread in the exchange (default from 4096 k-mers). Every scaling is by a
-    # power of two, so the two must produce the same bits, final alpha included.
+    # The scaled kernel in its layouts: clusters of 512-thread CTAs with all 16 layers in
+    # registers (PARPY_B200_SCALED_SPLIT=0); 1024-thread CTAs with layers 8..15 and the transition
+    # columns in shared memory and one exponent per sending thread in the exchange
+    # (PARPY_B200_SCALED_TMEM=0); the same with those values in tensor memory (default from 4096
+    # k-mers). Every scaling is by a power of two and the operations are the same in the same order,
+    # so all three must produce the same bits, final alpha included.
     from parpy_b200 import synthetic
     hmm = synthetic.hmm_model(k, seed=20 + k)
     seqs = synthetic.hmm_sequences(nseq, lo, hi, seed=30 + k)
     dh, ds = to_dev(hmm), to_dev(seqs)
-    out = {}
-    for split in ("0", "1"):
+    out = []
+    for split, tmem, async_x, rl in (("0", "0", "0", "8"), ("1", "0", "0", "8"), ("1", "1", "0", "8"), ("1", "1", "1", "8"),
+                                     ("1", "1", "1", "6"), ("1", "1", "1", "4"), ("1", "1", "0", "4")):
         monkeypatch.setenv("PARPY_B200_SCALED_SPLIT", split)
+        monkeypatch.setenv("PARPY_B200_SCALED_TMEM", tmem)
+        monkeypatch.setenv("PARPY_B200_SCALED_ASYNC", async_x)     # layer 0 by st.async + mbarriers
+        monkeypatch.setenv("PARPY_B200_FWD_REGLAYERS", rl)         # layers kept in registers
         rc, res, a1, a2 = cabi_forward(native, dh, ds, FLAGS["scaled"] | 2, alpha=True)
         assert rc == 0, native.error_message()
-        out[split] = (res.cpu().numpy().copy(), a1.cpu().numpy().copy(), a2.cpu().numpy().copy())
-    assert np.isfinite(out["1"][0]).all()
-    assert np.array_equal(out["0"][0], out["1"][0])
-    assert np.array_equal(out["0"][1], out["1"][1]) and np.array_equal(out["0"][2], out["1"][2])
+        out.append((res.cpu().numpy().copy(), a1.cpu().numpy().copy(), a2.cpu().numpy().copy()))
+        # twice in a row: tensor memory is released and taken again
+        rc, res2, _, _ = cabi_forward(native, dh, ds, FLAGS["scaled"])
+        assert rc == 0 and np.array_equal(res2.cpu().numpy(), out[-1][0])
+    assert np.isfinite(out[0][0]).all()
+    for other in out[1:]:
+        assert np.array_equal(out[0][0], other[0])
+        assert np.array_equal(out[0][1], other[1]) and np.array_equal(out[0][2], other[2])
 
 
 def test_8mer_runs_on_a_16_cta_cluster(native, oracle_mod):
@@ -663,12 +683,12 @@ def test_out_of_range_observations_are_clamped_and_flagged(native):
         opts = parpy.par({"inst": parpy.threads(5)})
         want = torch.zeros(5)
         hmm_mod.forward_kernel(hmm, good, want, None, None, opts=opts)
-        assert hmm_mod.forward_status() == {"length_clamped": False, "observation_clamped": False}
+        assert hmm_mod.forward_status() == {"length_clamped": False, "observation_clamped": False, "wait_timed_out": False}
         got = torch.zeros(5)
         hmm_mod.forward_kernel(hmm, bad, got, None, None, opts=opts)
-        assert hmm_mod.forward_status() == {"length_clamped": False, "observation_clamped": True}
+        assert hmm_mod.forward_status() == {"length_clamped": False, "observation_clamped": True, "wait_timed_out": False}
         assert torch.equal(got, want)
-        assert hmm_mod.forward_status() == {"length_clamped": False, "observation_clamped": False}
+        assert hmm_mod.forward_status() == {"length_clamped": False, "observation_clamped": False, "wait_timed_out": False}
     # Viterbi: same rule, its own status word
     hmm = hmm_mod.to_device(synthetic.hmm_model(5, seed=9))
     good = hmm_mod.to_device(good)

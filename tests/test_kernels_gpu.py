@@ -229,7 +229,8 @@ def test_spmv_reference_shaped_entry(native, oracle_mod):
 
 # ---- SDDMM ------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("alpha,beta", [(1.0, 0.0), (1.5, 2.0)])
-@pytest.mark.parametrize("N,ncols,K,density", [(512, 768, 64, 0.02), (100, 333, 30, 0.05), (64, 64, 1024, 0.1)])
+@pytest.mark.parametrize("N,ncols,K,density", [(512, 768, 64, 0.02), (100, 333, 30, 0.05), (64, 64, 1024, 0.1),
+                                               (128, 200, 256, 0.05), (96, 150, 512, 0.07), (300, 4000, 1024, 0.01)])
 def test_sddmm_csr_and_coo_against_oracle(oracle_mod, alpha, beta, N, ncols, K, density):
     # benchmarks/sddmm.py:43-61,72-84 call shapes; validation rule of :86-103 is atol=rtol=1e-5
     C = synthetic.uniform_csr(N, ncols, density, seed=N + K)
@@ -253,6 +254,14 @@ def test_sddmm_csr_and_coo_against_oracle(oracle_mod, alpha, beta, N, ncols, K, 
     Dh = np.zeros(nnz, dtype=np.float32)
     kernels.parpy_sddmm_coo_kernel(A.numpy(), B.numpy(), Ch, Dh, alpha, beta, opts=parpy.par({"nnz": parpy.threads(nnz)}))
     assert np.array_equal(Dh, got)
+    # COO entries in any order (the long-dot-product kernel caches the A row of a run of equal rows,
+    # and must not depend on the runs being long)
+    perm = np.random.default_rng(N).permutation(nnz)
+    Cp = {"rows": exp_rows[perm].copy(), "cols": C["cols"].numpy()[perm].copy(), "values": C["values"].numpy()[perm].copy(),
+          "nnz": nnz}
+    Dp = np.zeros(nnz, dtype=np.float32)
+    kernels.parpy_sddmm_coo_kernel(A.numpy(), B.numpy(), Cp, Dp, alpha, beta, opts=parpy.par({"nnz": parpy.threads(nnz)}))
+    assert np.array_equal(Dp, got[perm])
 
 
 def test_sddmm_decompress_entry(native, oracle_mod):
