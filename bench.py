@@ -167,6 +167,15 @@ def run_reference_arm(args, rank, world):
                                                          synthetic.state_steps(hmm, seqs))
     except Exception as exc:     # the CPU line above is the arm's result; this is a side note
         line["reference_cuda"] = {"unavailable": str(exc)[:200]}
+    # Second side note: the CUDA program ParPy's compiler emits for forward_kernel (hand transcription
+    # of its code-generation rules, oracle/parpy_emitted.cu), called the way forward_parpy calls it.
+    try:
+        import torch
+        if torch.cuda.is_available() and oracle.parpy_emitted_available():
+            torch.cuda.set_device(0)
+            line["parpy_emitted_cuda"] = time_parpy_emitted(args, hmm, seqs, synthetic.state_steps(hmm, seqs))
+    except Exception as exc:
+        line["parpy_emitted_cuda"] = {"unavailable": str(exc)[:200]}
     print(json.dumps(line), flush=True)
 
 
@@ -461,6 +470,33 @@ def ncu_traffic_bytes(args, input_bytes):
     if args.variant != "auto" or args.kmer != 7:
         return None
     return NCU_DRAM_BYTES_PER_INPUT_BYTE * input_bytes
+
+
+def time_parpy_emitted(args, hmm, seqs, work):
+    """What ParPy's own compiler would run for this benchmark (benchmarks/forward.py:189-218): the
+    emitted one-launch-per-time-step program with result and alpha zero-filled inside the call, for
+    the 'state' thread counts its tuner tries above one block; the best is kept (ParPyTuned)."""
+    import torch
+    from oracle import oracle
+    n = int(hmm["num_states"])
+    dev = lambda d: {k: (v.cuda() if isinstance(v, torch.Tensor) and v.dim() > 0 else v) for k, v in d.items()}
+    dh, ds = dev(hmm), dev(seqs)
+    batch = int(seqs["num_instances"])
+    alpha = (torch.empty((batch, n), device="cuda"), torch.empty((batch, n), device="cuda"))
+    small = {"data": ds["data"][:2, :8].contiguous(), "lens": torch.clamp(ds["lens"][:2], max=8)}
+    best = None
+    for nthreads in (n, n // 4, n // 16):
+        if nthreads <= 1024:
+            continue
+        oracle.parpy_emitted_forward(dh, small, nthreads)      # load the module
+        t0 = time.perf_counter()
+        oracle.parpy_emitted_forward(dh, ds, nthreads, alpha=alpha)
+        dt = time.perf_counter() - t0
+        if best is None or dt < best[0]:
+            best = (dt, nthreads)
+    return {"value": work / best[0], "unit": UNIT, "seconds": best[0], "state_threads": best[1],
+            "what": "hand transcription of the CUDA ParPy emits for forward_kernel (one launch per time step, "
+                    "two-kernel reductions, zero fill of alpha inside the call), best of three thread counts"}
 
 
 def time_reference_cuda(args, hmm, seqs, ours, work):

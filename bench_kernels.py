@@ -2,7 +2,7 @@
 """Timing of the kernels that surround the headline path, on the configurations
 the reference's tests and benchmarks use (seeded synthetic inputs):
 
-    python bench_kernels.py [--quick] [--only softmax,reduce,spmv,sddmm,forward5,viterbi]
+    python bench_kernels.py [--quick] [--only softmax,reduce,spmv,sddmm,spmm,forward5,viterbi]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         --master-port P bench_kernels.py --gpus N        # row-block / slice sharded kernels
 
@@ -218,8 +218,25 @@ def bench_viterbi(r):
     return lines
 
 
+def bench_spmm(r):
+    # CSR SpMM (test/test_spmm.py:16-24 shape family, larger): C += A @ B, A 65536 x 65536 with 32
+    # non-zeros per row on average, B dense [65536, 64]
+    n, k = 1 << 16, 64
+    A = synthetic.zipf_csr(n, n, mean_nnz=32, cap=1024, seed=1234)
+    d = {key: t.cuda() for key, t in A.items() if isinstance(t, torch.Tensor)}
+    B = torch.randn(n, k, generator=r.g).cuda()
+    C = torch.zeros(n, k, device="cuda")
+    nnz = d["values"].numel()
+    ms = r.timed(lambda: _native.check(r.lib.parpy_b200_spmm(P(d["values"].data_ptr()), P(d["rows"].data_ptr()),
+                                                             P(d["cols"].data_ptr()), n, P(B.data_ptr()), k,
+                                                             P(C.data_ptr()), stream())))
+    # value + column per non-zero, row pointers, B once, C read-modify-write
+    nbytes = nnz * 12 + n * 8 + 4 * n * k + 8 * n * k
+    return [report(f"spmm[{n}x{n}, nnz={nnz}, B {n}x{k}]", ms, nbytes, {"nnz": nnz, "gathered_bytes": nnz * k * 4})]
+
+
 SECTIONS = {"softmax": bench_softmax, "reduce": bench_reductions, "spmv": bench_spmv, "sddmm": bench_sddmm,
-            "forward5": bench_forward5, "viterbi": bench_viterbi}
+            "spmm": bench_spmm, "forward5": bench_forward5, "viterbi": bench_viterbi}
 
 
 def surrounding(reps=5):

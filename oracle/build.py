@@ -4,6 +4,8 @@ the reference's own CUDA implementation of the HMM forward algorithm.
 TEST INFRASTRUCTURE ONLY. Outputs:
 
   oracle/liboracle.so        gcc -O2 -fopenmp build of the C restatements
+  oracle/libparpy_emitted.so nvcc build of parpy_emitted.cu: the CUDA program ParPy's compiler
+                             emits for forward_kernel, written out by hand from its rules
   oracle/_ref/trellis_5mer.so, oracle/_ref/trellis_7mer.so
                              nvcc build of benchmarks/{5,7}mer/hmm.cu, compiled
                              from the reference sources where they lie (nothing
@@ -50,6 +52,22 @@ def build_oracle(force=False):
     return LIB
 
 
+EMITTED = os.path.join(HERE, "libparpy_emitted.so")
+
+
+def build_emitted(force=False):
+    """Compiles the hand transcription of ParPy's emitted forward program (needs
+    nvcc; returns None without it)."""
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    src = os.path.join(HERE, "parpy_emitted.cu")
+    if not os.path.exists(nvcc):
+        return None
+    if force or not os.path.exists(EMITTED) or os.path.getmtime(src) > os.path.getmtime(EMITTED):
+        _run([nvcc, "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC", "--shared", src,
+              "-o", EMITTED])
+    return EMITTED
+
+
 def build_reference(ref_root, force=False):
     """Compiles the reference-shipped CUDA (Trellis-generated) forward/Viterbi
     libraries. Returns the list of built files (empty if the checkout or nvcc is
@@ -73,5 +91,6 @@ def build_reference(ref_root, force=False):
 
 if __name__ == "__main__":
     print(build_oracle(force=True))
+    print(build_emitted(force=True))
     for f in build_reference(sys.argv[1] if len(sys.argv) > 1 else reference_root(), force=True):
         print(f)

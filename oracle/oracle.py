@@ -148,6 +148,43 @@ def trellis_forward(k, hmm, seqs):
     return res
 
 
+def parpy_emitted_available():
+    return os.path.exists(_build.EMITTED)
+
+
+def parpy_emitted_forward(hmm, seqs, nthreads, zero_fill=True, alpha=None):
+    """The CUDA program ParPy's compiler emits for benchmarks/forward.py
+    ``forward_kernel`` with ``state: threads(nthreads)``, nthreads > 1024 (hand
+    transcription in parpy_emitted.cu), on CUDA tensors, the way
+    ``forward_parpy`` (benchmarks/forward.py:189-198) calls it: result and the two
+    alpha matrices are allocated here and zero-filled by the call. Asynchronous;
+    returns the result tensor. ``alpha`` may pass preallocated matrices."""
+    import torch
+    lib = ctypes.CDLL(_build.EMITTED)
+    fn = lib.parpy_emitted_forward_kernel
+    fn.restype = ctypes.c_int32
+    fn.argtypes = [ctypes.c_float, _P, ctypes.c_int64, _P, ctypes.c_float, _P, _P, _P, _P, ctypes.c_int64,
+                   ctypes.c_int64, _P, _P, _P, ctypes.c_int64, ctypes.c_int32]
+    n = int(hmm["num_states"])
+    batch, maxlen = seqs["data"].shape
+    dev = lambda t: t if t.is_cuda else t.cuda()
+    tables = {k: dev(hmm[k]) for k in ("initial_prob", "output_prob", "trans1", "trans2")}
+    data, lens = dev(seqs["data"]).contiguous(), dev(seqs["lens"]).to(torch.int64).contiguous()
+    result = torch.empty(batch, dtype=torch.float32, device="cuda")
+    a1, a2 = alpha if alpha is not None else (torch.empty((batch, n), dtype=torch.float32, device="cuda"),
+                                              torch.empty((batch, n), dtype=torch.float32, device="cuda"))
+    # the generated code runs on the legacy default stream: order it after torch's current stream
+    torch.cuda.current_stream().synchronize()
+    rc = fn(float(hmm["gamma"]), tables["initial_prob"].data_ptr(), n, tables["output_prob"].data_ptr(),
+            float(hmm["synthetic_248"]), tables["trans1"].data_ptr(), tables["trans2"].data_ptr(), data.data_ptr(),
+            lens.data_ptr(), maxlen, batch, result.data_ptr(), a1.data_ptr(), a2.data_ptr(), int(nthreads),
+            1 if zero_fill else 0)
+    if rc != 0:
+        raise RuntimeError(f"parpy_emitted_forward_kernel failed (code={rc})")
+    torch.cuda.synchronize()
+    return result
+
+
 # ---- surrounding kernels ------------------------------------------------------------
 def _f32(a):
     return _np(a, np.float32)

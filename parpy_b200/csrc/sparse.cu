@@ -250,133 +250,78 @@ __global__ void __launch_bounds__(256) sddmm_nnz(const float *__restrict__ A, co
 }
 
 
-// Long dot products (K = 256 .. 1024, a multiple of 128): with 4 lanes per non-zero the A row
-// of a non-zero is read again for every non-zero of that row, and both operands go through the
-// L1 data pipe, which is what bounds sddmm_nnz at K = 1024 (87 % busy). Here a warp walks a
-// contiguous run of non-zeros (CSR order: runs of equal rows) and keeps the current A row in
-// registers, K / 32 elements per lane, so that only the gathered row of B^T moves per non-zero;
-// U non-zeros are in flight at once (all loads before the math), each reduced with a butterfly.
-template <int NV, int U>   // NV = K / 128 float4 per lane and operand row
-__global__ void __launch_bounds__(256) sddmm_rowcache(const float *__restrict__ A, const float *__restrict__ Bt,
-                                                      const int64_t *__restrict__ rows,
-                                                      const int64_t *__restrict__ cols,
-                                                      const float *__restrict__ cvalues, float *__restrict__ D,
-                                                      long long nnz, float alpha, float beta) {
-    constexpr int K = 128 * NV;
-    const int lane = threadIdx.x & 31;
-    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
-    long long per = (nnz + nwarps - 1) / nwarps;
-    per = (per + U - 1) / U * U;
-    const long long lo = warp * per, hi = pb::ll_min(nnz, lo + per);
-    float4 ar[NV];
-    long long cur = -1;
-    for (long long i = lo; i < hi; i += U) {
-        long long r[U], c[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const long long j = i + u < hi ? i + u : hi - 1;   // clamp: harmless duplicate work
-            r[u] = __ldg(rows + j);
-            c[u] = __ldg(cols + j);
-        }
-        bool same = true;
-#pragma unroll
-        for (int u = 1; u < U; ++u) same = same && r[u] == r[0];
-        float acc[U];
-        if (same) {
-            if (r[0] != cur) {
-                cur = r[0];
-#pragma unroll
-                for (int v = 0; v < NV; ++v)
-                    ar[v] = __ldg(reinterpret_cast<const float4 *>(A + cur * K + 4 * lane + 128 * v));
-            }
-            float4 q[U][NV];
-#pragma unroll
-            for (int u = 0; u < U; ++u)
-#pragma unroll
-                for (int v = 0; v < NV; ++v)
-                    q[u][v] = __ldg(reinterpret_cast<const float4 *>(Bt + c[u] * K + 4 * lane + 128 * v));
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                float a = 0.0f;
-#pragma unroll
-                for (int v = 0; v < NV; ++v) {
-                    a = fmaf(ar[v].x, q[u][v].x, a);
-                    a = fmaf(ar[v].y, q[u][v].y, a);
-                    a = fmaf(ar[v].z, q[u][v].z, a);
-                    a = fmaf(ar[v].w, q[u][v].w, a);
-                }
-                acc[u] = a;
-            }
-        } else {
-            // the group straddles a row boundary: one non-zero at a time
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                if (r[u] != cur) {
-                    cur = r[u];
-#pragma unroll
-                    for (int v = 0; v < NV; ++v)
-                        ar[v] = __ldg(reinterpret_cast<const float4 *>(A + cur * K + 4 * lane + 128 * v));
-                }
-                float a = 0.0f;
-#pragma unroll
-                for (int v = 0; v < NV; ++v) {
-                    const float4 qv = __ldg(reinterpret_cast<const float4 *>(Bt + c[u] * K + 4 * lane + 128 * v));
-                    a = fmaf(ar[v].x, qv.x, a);
-                    a = fmaf(ar[v].y, qv.y, a);
-                    a = fmaf(ar[v].z, qv.z, a);
-                    a = fmaf(ar[v].w, qv.w, a);
-                }
-                acc[u] = a;
-            }
-        }
-        float mine = 0.0f;
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], o);
-            if (lane == u) mine = acc[u];
-        }
-        if (lane < U && i + lane < hi) D[i + lane] = alpha * mine + beta * __ldg(cvalues + i + lane);
-    }
-}
-
 // ------------------------------------------------------------------- SpMM ----
 // C[i, j] += sum over the non-zeros a of row i of values[a] * B[cols[a], j]
 // (test/test_spmm.py:16-24). The reference gives every cell (i, j) its own
-// 32-thread block; here a CTA covers one row and a contiguous run of columns, so
-// every non-zero turns into one coalesced read of a B row segment.
-template <bool VEC>
-__global__ void __launch_bounds__(128) spmm_rows(const float *__restrict__ values,
-                                                 const int64_t *__restrict__ rows,
-                                                 const int64_t *__restrict__ cols,
-                                                 const float *__restrict__ B, long long K,
-                                                 float *__restrict__ C) {
-    const long long i = blockIdx.y;
+// 32-thread block. Here a warp owns one row and a run of up to 128 columns: LPR
+// lanes cover the run with one float4 each, so every non-zero is one coalesced
+// read of a B row segment, and the 32 / LPR lane groups take different non-zeros
+// of the row at the same time (narrow B: all lanes busy, several gathers in
+// flight); the groups' partial sums meet in a shuffle butterfly and group 0
+// updates C once.
+template <int LPR>
+__global__ void __launch_bounds__(256) spmm_warp_rows(const float *__restrict__ values,
+                                                      const int64_t *__restrict__ rows,
+                                                      const int64_t *__restrict__ cols,
+                                                      const float *__restrict__ B, long long nrows,
+                                                      long long K, int chunks, float *__restrict__ C) {
+    constexpr int G = 32 / LPR;   // non-zeros in flight per warp and trip
+    const int lane = threadIdx.x & 31, sub = lane % LPR, grp = lane / LPR;
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long i = warp / chunks;
+    if (i >= nrows) return;
+    const long long j = (warp % chunks) * (4 * LPR) + 4 * sub;
+    const bool live = j < K;   // K % 4 == 0: a float4 is inside or outside as a whole
     const long long a0 = __ldg(rows + i), a1 = __ldg(rows + i + 1);
-    if (VEC) {
-        const long long j = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
-        if (j >= K) return;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (long long a = a0; a < a1; ++a) {
-            const float v = __ldg(values + a);
-            const float4 b = __ldg(reinterpret_cast<const float4 *>(B + __ldg(cols + a) * K + j));
-            acc.x = fmaf(v, b.x, acc.x);
-            acc.y = fmaf(v, b.y, acc.y);
-            acc.z = fmaf(v, b.z, acc.z);
-            acc.w = fmaf(v, b.w, acc.w);
+    float4 acc0 = make_float4(0.f, 0.f, 0.f, 0.f), acc1 = acc0;
+    long long a = a0 + grp;
+    for (; a + G < a1; a += 2 * G) {   // two non-zeros per group in flight
+        const float v0 = __ldg(values + a), v1 = __ldg(values + a + G);
+        const long long c0 = __ldg(cols + a), c1 = __ldg(cols + a + G);
+        if (live) {
+            const float4 b0 = __ldg(reinterpret_cast<const float4 *>(B + c0 * K + j));
+            const float4 b1 = __ldg(reinterpret_cast<const float4 *>(B + c1 * K + j));
+            acc0.x = fmaf(v0, b0.x, acc0.x); acc0.y = fmaf(v0, b0.y, acc0.y);
+            acc0.z = fmaf(v0, b0.z, acc0.z); acc0.w = fmaf(v0, b0.w, acc0.w);
+            acc1.x = fmaf(v1, b1.x, acc1.x); acc1.y = fmaf(v1, b1.y, acc1.y);
+            acc1.z = fmaf(v1, b1.z, acc1.z); acc1.w = fmaf(v1, b1.w, acc1.w);
         }
+    }
+    if (a < a1 && live) {
+        const float v0 = __ldg(values + a);
+        const float4 b0 = __ldg(reinterpret_cast<const float4 *>(B + __ldg(cols + a) * K + j));
+        acc0.x = fmaf(v0, b0.x, acc0.x); acc0.y = fmaf(v0, b0.y, acc0.y);
+        acc0.z = fmaf(v0, b0.z, acc0.z); acc0.w = fmaf(v0, b0.w, acc0.w);
+    }
+    acc0.x += acc1.x; acc0.y += acc1.y; acc0.z += acc1.z; acc0.w += acc1.w;
+#pragma unroll
+    for (int o = LPR; o < 32; o <<= 1) {   // across the lane groups
+        acc0.x += __shfl_xor_sync(0xffffffffu, acc0.x, o);
+        acc0.y += __shfl_xor_sync(0xffffffffu, acc0.y, o);
+        acc0.z += __shfl_xor_sync(0xffffffffu, acc0.z, o);
+        acc0.w += __shfl_xor_sync(0xffffffffu, acc0.w, o);
+    }
+    if (grp == 0 && live) {
         float4 *dst = reinterpret_cast<float4 *>(C + i * K + j);
         float4 c = *dst;
-        c.x += acc.x; c.y += acc.y; c.z += acc.z; c.w += acc.w;
+        c.x += acc0.x; c.y += acc0.y; c.z += acc0.z; c.w += acc0.w;
         *dst = c;
-    } else {
-        const long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-        if (j >= K) return;
-        float acc = 0.f;
-        for (long long a = a0; a < a1; ++a) acc = fmaf(__ldg(values + a), __ldg(B + __ldg(cols + a) * K + j), acc);
-        C[i * K + j] += acc;
     }
+}
+
+// Any width and alignment: one thread per cell of a row's column run.
+__global__ void __launch_bounds__(128) spmm_rows_scalar(const float *__restrict__ values,
+                                                        const int64_t *__restrict__ rows,
+                                                        const int64_t *__restrict__ cols,
+                                                        const float *__restrict__ B, long long K, int chunks,
+                                                        float *__restrict__ C) {
+    const long long i = blockIdx.x / chunks;
+    const long long j = (long long)(blockIdx.x % chunks) * blockDim.x + threadIdx.x;
+    if (j >= K) return;
+    const long long a0 = __ldg(rows + i), a1 = __ldg(rows + i + 1);
+    float acc = 0.f;
+    for (long long a = a0; a < a1; ++a) acc = fmaf(__ldg(values + a), __ldg(B + __ldg(cols + a) * K + j), acc);
+    C[i * K + j] += acc;
 }
 
 int32_t sddmm_common(const float *A, const float *B, const int64_t *crows, int64_t N, const int64_t *rows,
@@ -414,24 +359,13 @@ int32_t sddmm_common(const float *A, const float *B, const int64_t *crows, int64
     } while (0)
     // measured at 8192 x 8192, 1 %, K = 64: <4,2,2> 38.9 us for the whole call, <8,4,2> 40.0,
     // <8,8,1> 46, <16,8,1> 73 (the old half-warp-per-non-zero kernel: 64)
-#define PB_SDDMM_ROWS(NV, U)                                                                                  \
-    do {                                                                                                      \
-        int per_sm = 0;                                                                                       \
-        PB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, sddmm_rowcache<NV, U>, 256, 0));       \
-        const long long blocks = std::max<long long>(                                                         \
-            1, std::min<long long>((nnz + 8 * U - 1) / (8 * U), (long long)std::max(per_sm, 1) * dev.sm_count)); \
-        sddmm_rowcache<NV, U><<<(unsigned)blocks, 256, 0, stream>>>(A, Bt, rows, cols, cvalues, D, nnz,       \
-                                                                    (float)alpha, (float)beta);               \
-    } while (0)
-    // long dot products: the A row stays in registers (0.29 -> see the kernel's comment); cfg 2 keeps the gather kernel
-    if (vec && cfg != 2 && K == 1024) PB_SDDMM_ROWS(8, 2);
-    else if (vec && cfg != 2 && K == 512) PB_SDDMM_ROWS(4, 4);
-    else if (vec && cfg != 2 && K == 256) PB_SDDMM_ROWS(2, 8);
-    else if (!vec) PB_SDDMM(false, 8, 4, 1);
+    // K = 1024 (the reference's other inner size, benchmarks/bench.py:206-244): 0.29 ms, i.e. 2.75 GB of
+    // gathered B^T rows at 9.5 TB/s out of the L2. A variant that keeps the A row of a run of non-zeros in
+    // registers (one warp per run, only B^T rows move) measured 0.284 ms and was not kept.
+    if (!vec) PB_SDDMM(false, 8, 4, 1);
     else if (cfg == 1) PB_SDDMM(true, 8, 4, 2);
     else PB_SDDMM(true, 4, 2, 2);
 #undef PB_SDDMM
-#undef PB_SDDMM_ROWS
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }
@@ -488,12 +422,23 @@ int32_t parpy_b200_spmm(const float *values, const int64_t *rows, const int64_t 
     PB_REQUIRE(nrows >= 0 && ncols >= 0, "spmm: negative size");
     if (nrows == 0 || ncols == 0) return PB_OK;
     PB_REQUIRE(values && rows && cols && B && C, "spmm: null pointer");
-    PB_REQUIRE(nrows <= 65535, "spmm: more than 65535 rows are not supported");
     const bool vec = (ncols % 4 == 0) && pb::aligned16(B) && pb::aligned16(C);
-    const long long per_block = vec ? 128 * 4 : 128;
-    dim3 grid((unsigned)((ncols + per_block - 1) / per_block), (unsigned)nrows, 1);
-    if (vec) spmm_rows<true><<<grid, 128, 0, stream>>>(values, rows, cols, B, ncols, C);
-    else spmm_rows<false><<<grid, 128, 0, stream>>>(values, rows, cols, B, ncols, C);
+    if (vec) {
+        // lanes per column run: as many as the row of B needs, up to a full warp
+        const int lpr = ncols >= 128 ? 32 : ncols > 32 ? 16 : ncols > 16 ? 8 : 4;
+        const long long chunks = (ncols + 4 * lpr - 1) / (4 * lpr);
+        const long long warps = nrows * chunks;
+        const long long blocks = (warps + 7) / 8;
+        PB_REQUIRE(blocks <= 0x7fffffffLL, "spmm: %lld rows x %lld columns is too large", (long long)nrows, (long long)ncols);
+        if (lpr == 32) spmm_warp_rows<32><<<(unsigned)blocks, 256, 0, stream>>>(values, rows, cols, B, nrows, ncols, (int)chunks, C);
+        else if (lpr == 16) spmm_warp_rows<16><<<(unsigned)blocks, 256, 0, stream>>>(values, rows, cols, B, nrows, ncols, (int)chunks, C);
+        else if (lpr == 8) spmm_warp_rows<8><<<(unsigned)blocks, 256, 0, stream>>>(values, rows, cols, B, nrows, ncols, (int)chunks, C);
+        else spmm_warp_rows<4><<<(unsigned)blocks, 256, 0, stream>>>(values, rows, cols, B, nrows, ncols, (int)chunks, C);
+    } else {
+        const long long chunks = (ncols + 127) / 128;
+        PB_REQUIRE(nrows * chunks <= 0x7fffffffLL, "spmm: %lld rows x %lld columns is too large", (long long)nrows, (long long)ncols);
+        spmm_rows_scalar<<<(unsigned)(nrows * chunks), 128, 0, stream>>>(values, rows, cols, B, ncols, (int)chunks, C);
+    }
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }

@@ -699,3 +699,21 @@ def test_out_of_range_observations_are_clamped_and_flagged(native):
     got, _ = hmm_mod.viterbi(hmm, bad, 32, 8, check=False)
     assert hmm_mod.viterbi_status() == {"wait_timed_out": False, "observation_clamped": True}
     assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("k,nthreads", [(4, 2048), (4, 4096), (5, 2048), (5, 16384)])
+def test_transcription_of_the_emitted_cuda_agrees_with_the_oracle(native, oracle_mod, k, nthreads):
+    # oracle/parpy_emitted.cu: the program ParPy's compiler emits for forward_kernel with
+    # 'state': threads(nthreads) > 1024 (one launch per time step, two-kernel reductions), written
+    # out by hand; it is the benchmark's "ParPy-generated CUDA" arm, so it has to compute the same
+    # thing: against the CPU oracle, and against this library's kernel on the same inputs.
+    from parpy_b200 import synthetic
+    if not oracle_mod.parpy_emitted_available():
+        pytest.skip("oracle/libparpy_emitted.so not built")
+    hmm = synthetic.hmm_model(k, seed=40 + k)
+    seqs = synthetic.hmm_sequences(9, 1, 70, seed=50 + k, pad_value=0)
+    exp = oracle_mod.forward(hmm, seqs)
+    got = oracle_mod.parpy_emitted_forward(to_dev(hmm), to_dev(seqs), nthreads).cpu().numpy()
+    assert max_rel(got, exp) <= REL_ORACLE
+    rc, res, _, _ = cabi_forward(native, to_dev(hmm), to_dev(seqs))
+    assert rc == 0 and max_rel(res.cpu().numpy(), got) <= REL_ORACLE

@@ -304,7 +304,8 @@ def test_sum_exp_3d_like_reference_test(oracle_mod, dims):
     assert max_rel(x.reshape(N * M, K), ref_x) <= 1e-5          # x was exponentiated in place
 
 
-@pytest.mark.parametrize("N,M,K", [(1024, 256, 512), (100, 77, 33), (5, 9, 4)])
+@pytest.mark.parametrize("N,M,K", [(1024, 256, 512), (100, 77, 33), (5, 9, 4), (300, 500, 64), (257, 300, 100),
+                                   (70000, 900, 16), (64, 200, 8), (33, 100, 32)])
 def test_spmm_like_reference_test(native, oracle_mod, N, M, K):
     # test/test_spmm.py:53-87: uniform random CSR at 1 % (denser for the tiny cases), dense B
     A = synthetic.zipf_csr(N, M, mean_nnz=max(2, M // 100), cap=M, seed=N)
