@@ -253,7 +253,7 @@ hmm_schedule(const int64_t *__restrict__ lens, int B, int C, int *__restrict__ o
     }
     __syncthreads();
 
-    // repair of the fullest bin; the number of rounds is bounded by half the steps it could save
+    // repair of the fullest bin, for a bounded number of rounds
     long long total = 0;
     if (C > 1 && B > C) {
         for (int c = 0; c < C; ++c) total += s_load[c];
@@ -262,8 +262,10 @@ hmm_schedule(const int64_t *__restrict__ lens, int B, int C, int *__restrict__ o
     if (C > 1 && B > C) {
         long long top = 0;
         for (int c = 0; c < C; ++c) top = s_load[c] > top ? s_load[c] : top;
+        // a round costs about as much as a time step of a small model: spend at most an eighth of
+        // the steps that perfect balance could save
         const long long gap = top - total / C;
-        budget = static_cast<int>(gap / 2 < 4096 ? gap / 2 : 4096);
+        budget = static_cast<int>(gap / 8 < 512 ? gap / 8 : 512);
     }
     for (int it = 0; it < budget; ++it) {
         if (warp == 0) {
