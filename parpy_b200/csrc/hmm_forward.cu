@@ -836,6 +836,16 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_split(const FwdParams p) 
 }
 
 
+// log 0 inside the kernels that run with `finite` arithmetic: every -inf that enters (tables,
+// emissions, initial distribution) becomes this value, sums of a few of them stay finite for
+// any sequence length an int can hold, anything below kLogZeroTest leaves the kernel as -inf.
+constexpr float kLogZero = -1e25f;
+constexpr float kLogZeroTest = -1e24f;
+__device__ __forceinline__ float4 clamp_log_zero(float4 v) {
+    return make_float4(fmaxf(v.x, kLogZero), fmaxf(v.y, kLogZero), fmaxf(v.z, kLogZero), fmaxf(v.w, kLogZero));
+}
+__device__ __forceinline__ float restore_log_zero(float x) { return x < kLogZeroTest ? -INFINITY : x; }
+
 // ---- resident kernel, register/shared split, packed arithmetic ---------------------
 // hmm_forward_split with its additions, multiplications and multiply-adds issued as packed
 // pairs (add/sub/mul/fma .f32x2: one issue slot for the same operation on two k-mers of the
@@ -894,7 +904,9 @@ __device__ __forceinline__ float2 log1p_poly2_times(float2 x) {
 
 // log(exp(u) + exp(v)) for two states, every half rounded exactly like lse2_sel;
 // (-inf, -inf) gives -inf. `lgpoly`: the logarithm is the polynomial above.
-__device__ __forceinline__ float2 lse2_pair(bool poly, float2 u, float2 v, bool lgpoly = false) {
+// `finite`: the caller guarantees finite operands (log 0 is kept as a large negative number, see
+// kLogZero), so (-inf) - (-inf) cannot occur and the NaN clamp is dropped.
+__device__ __forceinline__ float2 lse2_pair(bool poly, float2 u, float2 v, bool lgpoly = false, bool finite = false) {
     const float2 mx = max2(u, v);
     const float2 t = mul2(sub2(u, v), dup2(kLog2e));   // |t| = |u - v| * log2(e)
     float2 ex;
@@ -902,16 +914,16 @@ __device__ __forceinline__ float2 lse2_pair(bool poly, float2 u, float2 v, bool 
     else ex = make_float2(pb::ex2_approx(-fabsf(t.x)), pb::ex2_approx(-fabsf(t.y)));
     if (lgpoly) {
         const float2 r = fma2(ex, log1p_poly2_times(ex), mx);
-        return poly ? r : make_float2(fmaxf(r.x, -INFINITY), fmaxf(r.y, -INFINITY));
+        return (poly || finite) ? r : make_float2(fmaxf(r.x, -INFINITY), fmaxf(r.y, -INFINITY));
     }
     const float2 s = add2(ex, dup2(1.0f));
     const float2 r = fma2(make_float2(pb::lg2_approx(s.x), pb::lg2_approx(s.y)), dup2(kLn2), mx);
     // the polynomial path maps the NaN of (-inf) - (-inf) to a zero term by itself
-    return poly ? r : make_float2(fmaxf(r.x, -INFINITY), fmaxf(r.y, -INFINITY));
+    return (poly || finite) ? r : make_float2(fmaxf(r.x, -INFINITY), fmaxf(r.y, -INFINITY));
 }
 
 // log of the sum of four exponentials, terms added in the order j = 0..3 (lse4 on pairs).
-__device__ __forceinline__ float2 lse4_pair(float2 p0, float2 p1, float2 p2, float2 p3) {
+__device__ __forceinline__ float2 lse4_pair(float2 p0, float2 p1, float2 p2, float2 p3, bool finite = false) {
     const float2 m = max2(max2(p0, p1), max2(p2, p3));
     const float2 l2e = dup2(kLog2e);
     const float2 d0 = mul2(sub2(p0, m), l2e), d1 = mul2(sub2(p1, m), l2e);
@@ -921,13 +933,14 @@ __device__ __forceinline__ float2 lse4_pair(float2 p0, float2 p1, float2 p2, flo
     sum = add2(sum, make_float2(pb::ex2_approx(d2.x), pb::ex2_approx(d2.y)));
     sum = add2(sum, make_float2(pb::ex2_approx(d3.x), pb::ex2_approx(d3.y)));
     const float2 r = fma2(make_float2(pb::lg2_approx(sum.x), pb::lg2_approx(sum.y)), dup2(kLn2), m);
-    return make_float2(fmaxf(r.x, -INFINITY), fmaxf(r.y, -INFINITY));
+    return finite ? r : make_float2(fmaxf(r.x, -INFINITY), fmaxf(r.y, -INFINITY));
 }
 
 // POLY_MASK bit d: layer d evaluates its exponential on the FMA pipe; LG_MASK bit d: its logarithm.
 // TMEM: layers RL..15 and the transition columns live in tensor memory instead of shared memory
 // (RL = layers kept in registers; the shared-memory layout is fixed at 8).
-template <unsigned POLY_MASK, unsigned LG_MASK = 0u, bool TMEM = false, int RL = kRegLayers>
+// FIN: finite arithmetic (kLogZero in place of -inf inside the kernel; no NaN clamps).
+template <unsigned POLY_MASK, unsigned LG_MASK = 0u, bool TMEM = false, int RL = kRegLayers, bool FIN = false>
 __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p) {
     static_assert(TMEM ? (RL >= 4 && RL <= 8 && RL % 2 == 0) : RL == kRegLayers, "register layers");
     extern __shared__ __align__(16) float smem_dyn[];
@@ -961,13 +974,14 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
     }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-        const float4 v = __ldg(reinterpret_cast<const float4 *>(p.trans1) + (j * Kq + (g >> 2)));
+        float4 v = __ldg(reinterpret_cast<const float4 *>(p.trans1) + (j * Kq + (g >> 2)));
+        if constexpr (FIN) v = clamp_log_zero(v);
         if constexpr (TMEM) tmem_st4(tm + 4 * (kLayers - RL) + 4 * j, v);
         else Ts[j * NT + tid] = v;
     }
     if constexpr (TMEM) tmem_wait_st();
-    if (tid < kLayers) s_t2[tid] = dup2(__ldg(p.trans2 + tid));
-    const float gamma2 = p.gamma, syn2 = p.synthetic;
+    if (tid < kLayers) s_t2[tid] = dup2(FIN ? fmaxf(__ldg(p.trans2 + tid), kLogZero) : __ldg(p.trans2 + tid));
+    const float gamma2 = FIN ? fmaxf(p.gamma, kLogZero) : p.gamma, syn2 = FIN ? fmaxf(p.synthetic, kLogZero) : p.synthetic;
 
     const unsigned a0_base = smem_u32(a0s);
     unsigned dst0;
@@ -1002,9 +1016,11 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
             const int o0 = obs_at(p, obs, 0, bad_obs);
             o_next = obs_at(p, obs, T_len > 1 ? 1 : 0, bad_obs);
             e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o0 * K + g));
+            if constexpr (FIN) e = clamp_log_zero(e);
 #pragma unroll
             for (int d = 0; d < kLayers; ++d) {
-                const float4 v = __ldg(reinterpret_cast<const float4 *>(p.initial_prob + d * K + g));
+                float4 v = __ldg(reinterpret_cast<const float4 *>(p.initial_prob + d * K + g));
+                if constexpr (FIN) v = clamp_log_zero(v);
                 const float2 lo = make_float2(v.x + e.x, v.y + e.y);
                 const float2 hi = make_float2(v.z + e.z, v.w + e.w);
                 if (d < RL) { a[d][0] = lo; a[d][1] = hi; }
@@ -1021,6 +1037,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
             // this step's emission slice; the observation after it
             e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o_next * K + g));
             o_next = obs_at(p, obs, t + 1 < T_len ? t + 1 : T_len - 1, bad_obs);
+            if constexpr (FIN) e = clamp_log_zero(e);
             const float2 ev[2] = {make_float2(e.x, e.y), make_float2(e.z, e.w)};
             float4 t0, t1, t2, t3;   // transition columns
             if constexpr (TMEM) {    // in flight while the exchange completes
@@ -1043,15 +1060,15 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
                     t0 = Ts[tid], t1 = Ts[NT + tid], t2 = Ts[2 * NT + tid], t3 = Ts[3 * NT + tid];
                 }
                 q[0] = lse4_pair(add2(make_float2(t0.x, t0.y), a0), add2(make_float2(t1.x, t1.y), a1),
-                                 add2(make_float2(t2.x, t2.y), a2), add2(make_float2(t3.x, t3.y), a3));
+                                 add2(make_float2(t2.x, t2.y), a2), add2(make_float2(t3.x, t3.y), a3), FIN);
                 q[1] = lse4_pair(add2(make_float2(t0.z, t0.w), a0), add2(make_float2(t1.z, t1.w), a1),
-                                 add2(make_float2(t2.z, t2.w), a2), add2(make_float2(t3.z, t3.w), a3));
+                                 add2(make_float2(t2.z, t2.w), a2), add2(make_float2(t3.z, t3.w), a3), FIN);
             }
             {
                 const float2 w = s_t2[0];
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
-                    a[0][h] = add2(lse2_pair((POLY_MASK & 1u) != 0, add2(w, q[h]), a[1][h], (LG_MASK & 1u) != 0), ev[h]);
+                    a[0][h] = add2(lse2_pair((POLY_MASK & 1u) != 0, add2(w, q[h]), a[1][h], (LG_MASK & 1u) != 0, FIN), ev[h]);
             }
             st_cluster_v4(dst, a[0][0].x, a[0][0].y, a[0][1].x, a[0][1].y);
             cluster_arrive();
@@ -1060,7 +1077,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
                 const float2 w = s_t2[d];
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
-                    a[d][h] = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[h]), a[d + 1][h], ((LG_MASK >> d) & 1u) != 0), ev[h]);
+                    a[d][h] = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[h]), a[d + 1][h], ((LG_MASK >> d) & 1u) != 0, FIN), ev[h]);
             }
             // layers 7..15: the "next layer" operand comes from shared memory
             float4 nxt, nxt2;   // TMEM: old values of the next layer, requested one layer ahead
@@ -1074,9 +1091,9 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
             {
                 const float2 w = s_t2[RL - 1];
                 a[RL - 1][0] = add2(lse2_pair(((POLY_MASK >> (RL - 1)) & 1u) != 0, add2(w, q[0]),
-                                                      make_float2(nxt.x, nxt.y), ((LG_MASK >> (RL - 1)) & 1u) != 0), ev[0]);
+                                                      make_float2(nxt.x, nxt.y), ((LG_MASK >> (RL - 1)) & 1u) != 0, FIN), ev[0]);
                 a[RL - 1][1] = add2(lse2_pair(((POLY_MASK >> (RL - 1)) & 1u) != 0, add2(w, q[1]),
-                                                      make_float2(nxt.z, nxt.w), ((LG_MASK >> (RL - 1)) & 1u) != 0), ev[1]);
+                                                      make_float2(nxt.z, nxt.w), ((LG_MASK >> (RL - 1)) & 1u) != 0, FIN), ev[1]);
             }
 #pragma unroll
             for (int d = RL; d < kLayers; ++d) {
@@ -1099,8 +1116,8 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
                     v0.x += c; v0.y += c; v1.x += c; v1.y += c;
                 }
                 const float2 w = s_t2[d];
-                const float2 r0 = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[0]), v0, ((LG_MASK >> d) & 1u) != 0), ev[0]);
-                const float2 r1 = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[1]), v1, ((LG_MASK >> d) & 1u) != 0), ev[1]);
+                const float2 r0 = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[0]), v0, ((LG_MASK >> d) & 1u) != 0, FIN), ev[0]);
+                const float2 r1 = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[1]), v1, ((LG_MASK >> d) & 1u) != 0, FIN), ev[1]);
                 if constexpr (TMEM) tmem_st4(tm + 4 * (d - RL), make_float4(r0.x, r0.y, r1.x, r1.y));
                 else As[(d - RL) * NT + tid] = make_float4(r0.x, r0.y, r1.x, r1.y);
             }
@@ -1168,7 +1185,9 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
         if (rank == 0 && tid == 0) {
             float sacc = 0.0f;
             for (unsigned r = 0; r < CS; ++r) sacc += s_cl[r];
-            p.result[seq] = gmax + fast_log(sacc);
+            // an impossible sequence (every state at log 0) scores NaN, as the reference's
+            // (-inf) - (-inf) in forward_lse_inst does (benchmarks/forward.py:168-173)
+            p.result[seq] = (FIN && gmax < kLogZeroTest) ? __int_as_float(0x7fc00000) : gmax + fast_log(sacc);
             flag_bad_observation(bad_obs, true);
         }
         if (p.write_alpha) {
@@ -1185,6 +1204,8 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
                         v = As[(d - RL) * NT + tid];
                     }
                 }
+                if constexpr (FIN)
+                    v = make_float4(restore_log_zero(v.x), restore_log_zero(v.y), restore_log_zero(v.z), restore_log_zero(v.w));
                 *reinterpret_cast<float4 *>(dst_alpha + (long long)d * K + g) = v;
             }
         }
@@ -1202,7 +1223,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
 // exponential on the layers of POLY_MASK). Layer 0 is exchanged
 // through the CTA's own shared memory, so a time step costs one __syncthreads instead of
 // a cluster barrier, which is what bounds the step time of small state spaces.
-template <unsigned POLY_MASK, unsigned LG_MASK = 0u>
+template <unsigned POLY_MASK, unsigned LG_MASK = 0u, bool FIN = false>
 __global__ void __launch_bounds__(256, 1) hmm_forward_packed_cta(const FwdParams p) {
     __shared__ __align__(16) float a0s[2][1024];   // layer 0 of all k-mers, double buffered
     __shared__ int s_seq;
@@ -1219,12 +1240,13 @@ __global__ void __launch_bounds__(256, 1) hmm_forward_packed_cta(const FwdParams
     float2 T[4][2];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-        const float4 v = __ldg(reinterpret_cast<const float4 *>(p.trans1) + (j * Kq + tid));
+        float4 v = __ldg(reinterpret_cast<const float4 *>(p.trans1) + (j * Kq + tid));
+        if constexpr (FIN) v = clamp_log_zero(v);
         T[j][0] = make_float2(v.x, v.y);
         T[j][1] = make_float2(v.z, v.w);
     }
-    if (tid < kLayers) s_t2[tid] = dup2(__ldg(p.trans2 + tid));
-    const float gamma2 = p.gamma, syn2 = p.synthetic;
+    if (tid < kLayers) s_t2[tid] = dup2(FIN ? fmaxf(__ldg(p.trans2 + tid), kLogZero) : __ldg(p.trans2 + tid));
+    const float gamma2 = FIN ? fmaxf(p.gamma, kLogZero) : p.gamma, syn2 = FIN ? fmaxf(p.synthetic, kLogZero) : p.synthetic;
 
     if (p.seg != nullptr && tid == 0) s_seq = p.seg[blockIdx.x];   // position in this CTA's part of the schedule
     for (;;) {
@@ -1261,9 +1283,11 @@ __global__ void __launch_bounds__(256, 1) hmm_forward_packed_cta(const FwdParams
             const int o0 = obs_at(p, obs, 0, bad_obs);
             o_next = obs_at(p, obs, T_len > 1 ? 1 : 0, bad_obs);
             e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o0 * K + g));
+            if constexpr (FIN) e = clamp_log_zero(e);
 #pragma unroll
             for (int d = 0; d < kLayers; ++d) {
-                const float4 v = __ldg(reinterpret_cast<const float4 *>(p.initial_prob + d * K + g));
+                float4 v = __ldg(reinterpret_cast<const float4 *>(p.initial_prob + d * K + g));
+                if constexpr (FIN) v = clamp_log_zero(v);
                 a[d][0] = make_float2(v.x + e.x, v.y + e.y);
                 a[d][1] = make_float2(v.z + e.z, v.w + e.w);
             }
@@ -1273,6 +1297,7 @@ __global__ void __launch_bounds__(256, 1) hmm_forward_packed_cta(const FwdParams
 
         for (int t = 1; t < T_len; ++t) {
             e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o_next * K + g));
+            if constexpr (FIN) e = clamp_log_zero(e);
             o_next = obs_at(p, obs, t + 1 < T_len ? t + 1 : T_len - 1, bad_obs);
             const float2 ev[2] = {make_float2(e.x, e.y), make_float2(e.z, e.w)};
 
@@ -1282,7 +1307,7 @@ __global__ void __launch_bounds__(256, 1) hmm_forward_packed_cta(const FwdParams
             float2 q[2];
 #pragma unroll
             for (int h = 0; h < 2; ++h)
-                q[h] = lse4_pair(add2(T[0][h], a0), add2(T[1][h], a1), add2(T[2][h], a2), add2(T[3][h], a3));
+                q[h] = lse4_pair(add2(T[0][h], a0), add2(T[1][h], a1), add2(T[2][h], a2), add2(T[3][h], a3), FIN);
 #pragma unroll
             for (int d = 0; d < kLayers; ++d) {
                 const float2 w = s_t2[d];
@@ -1294,7 +1319,7 @@ __global__ void __launch_bounds__(256, 1) hmm_forward_packed_cta(const FwdParams
                         v.x += c;
                         v.y += c;
                     }
-                    a[d][h] = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[h]), v, ((LG_MASK >> d) & 1u) != 0), ev[h]);
+                    a[d][h] = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[h]), v, ((LG_MASK >> d) & 1u) != 0, FIN), ev[h]);
                 }
                 if (d == 0)
                     *reinterpret_cast<float4 *>(&a0s[buf ^ 1u][g]) =
@@ -1325,15 +1350,19 @@ __global__ void __launch_bounds__(256, 1) hmm_forward_packed_cta(const FwdParams
         if (tid == 0) {
             float sacc = 0.0f;
             for (int w = 0; w < nwarps; ++w) sacc += s_warp[w];
-            p.result[seq] = gmax + fast_log(sacc);
+            // an impossible sequence scores NaN like the reference's (-inf) - (-inf)
+            p.result[seq] = (FIN && gmax < kLogZeroTest) ? __int_as_float(0x7fc00000) : gmax + fast_log(sacc);
             flag_bad_observation(bad_obs, true);
         }
         if (p.write_alpha) {
             float *dst_alpha = ((len & 1) ? p.alpha1 : p.alpha2) + (long long)seq * (kLayers * (long long)K);
 #pragma unroll
-            for (int d = 0; d < kLayers; ++d)
-                *reinterpret_cast<float4 *>(dst_alpha + (long long)d * K + g) =
-                    make_float4(a[d][0].x, a[d][0].y, a[d][1].x, a[d][1].y);
+            for (int d = 0; d < kLayers; ++d) {
+                float4 v = make_float4(a[d][0].x, a[d][0].y, a[d][1].x, a[d][1].y);
+                if constexpr (FIN)
+                    v = make_float4(restore_log_zero(v.x), restore_log_zero(v.y), restore_log_zero(v.z), restore_log_zero(v.w));
+                *reinterpret_cast<float4 *>(dst_alpha + (long long)d * K + g) = v;
+            }
         }
     }
 }
@@ -1552,8 +1581,8 @@ __global__ void __launch_bounds__(512, 1) hmm_forward_scaled(const FwdParams p) 
         if (rank == 0 && tid == 0) {
             double sacc = 0.0;
             for (unsigned r = 0; r < CS; ++r) sacc += (double)s_cl[r];
-            // natural log of sum * 2^G; an impossible sequence (sum == 0) gives -inf
-            p.result[seq] = sacc > 0.0 ? (float)(log(sacc) + (double)G * 0.6931471805599453) : -INFINITY;
+            // natural log of sum * 2^G; an impossible sequence (sum == 0) gives NaN like the reference's (-inf) - (-inf)
+            p.result[seq] = sacc > 0.0 ? (float)(log(sacc) + (double)G * 0.6931471805599453) : __int_as_float(0x7fc00000);
             flag_bad_observation(bad_obs, true);
         }
         if (p.write_alpha) {
@@ -1803,8 +1832,8 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_split(const FwdPar
         if (rank == 0 && tid == 0) {
             double sacc = 0.0;
             for (unsigned r = 0; r < CS; ++r) sacc += (double)s_cl[r];
-            // natural log of sum * 2^G; an impossible sequence (sum == 0) gives -inf
-            p.result[seq] = sacc > 0.0 ? (float)(log(sacc) + (double)G * 0.6931471805599453) : -INFINITY;
+            // natural log of sum * 2^G; an impossible sequence (sum == 0) gives NaN like the reference's (-inf) - (-inf)
+            p.result[seq] = sacc > 0.0 ? (float)(log(sacc) + (double)G * 0.6931471805599453) : __int_as_float(0x7fc00000);
             flag_bad_observation(bad_obs, true);
         }
         if (p.write_alpha) {
@@ -2132,8 +2161,8 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_tmem(const FwdPara
         if (rank == 0 && tid == 0) {
             double sacc = 0.0;
             for (unsigned r = 0; r < CS; ++r) sacc += (double)s_cl[r];
-            // natural log of sum * 2^G; an impossible sequence (sum == 0) gives -inf
-            p.result[seq] = sacc > 0.0 ? (float)(log(sacc) + (double)G * 0.6931471805599453) : -INFINITY;
+            // natural log of sum * 2^G; an impossible sequence (sum == 0) gives NaN like the reference's (-inf) - (-inf)
+            p.result[seq] = sacc > 0.0 ? (float)(log(sacc) + (double)G * 0.6931471805599453) : __int_as_float(0x7fc00000);
             flag_bad_observation(bad_obs, true);
         }
         if (p.write_alpha) {
@@ -2347,7 +2376,11 @@ ResidentKernel pick_kernel(const Plan &pl, bool five) {
         // Measured on 100 sequences x 2000 steps: logarithm of 11 layers as polynomial (mask 0xEEEC, all
         // exponentials on the MUFU pipe) 2.64 ms; of the odd layers 2.71; of all but layer 0 2.69;
         // exponential of the odd layers as polynomial (the earlier default) 2.72; both kinds mixed 2.84-2.93.
-        if (getenv("PARPY_B200_FWD_POLY") == nullptr) return hmm_forward_packed_cta<0x0000u, 0xEEECu>;
+        if (getenv("PARPY_B200_FWD_POLY") == nullptr) {
+            const char *fin = getenv("PARPY_B200_FWD_FINITE");   // finite arithmetic unless set to 0
+            if (fin && atoi(fin) == 0) return hmm_forward_packed_cta<0x0000u, 0xEEECu>;
+            return hmm_forward_packed_cta<0x0000u, 0xEEECu, true>;
+        }
         const int npoly = atoi(getenv("PARPY_B200_FWD_POLY"));   // exponential masks only
         switch (npoly) {
             case 0: return hmm_forward_packed_cta<0x0000u>;
@@ -2374,10 +2407,24 @@ ResidentKernel pick_kernel(const Plan &pl, bool five) {
             // 1.911e12; same with 8 in registers 1.905e12, 6: 1.891e12; layers 1,2,3,5,... (12) 1.897e12;
             // exponential of the even layers but 0 as polynomial and no logarithm (the earlier
             // default) 1.835e12 in tensor memory, 1.817e12 in shared memory.
+            // Finite arithmetic (log 0 kept as -1e25 inside the kernel, -inf again in what it writes)
+            // drops the NaN clamps of every log-sum-exp: 1.999e12 against 1.923e12 state-steps/s.
+            // PARPY_B200_FWD_FINITE=0 selects the kernel that computes on -inf itself.
+            const char *fin = getenv("PARPY_B200_FWD_FINITE");
+            if (masks && !(fin && atoi(fin) == 0)) {
+#define PB_FIN(E, L) if (ex == E && lg == L) return hmm_forward_packed<E, L, true, 4, true>
+                PB_FIN(0x0000u, 0xEEEEu);
+                PB_FIN(0x0000u, 0xFEFEu);
+                PB_FIN(0x0000u, 0xFFFEu);
+                PB_FIN(0x0000u, 0xEEE8u);
+                PB_FIN(0x0000u, 0xAAAAu);
+#undef PB_FIN
+            }
             if (masks) {
                 if (ex == 0x0000u && lg == 0xEEEEu) return rl == 8 ? hmm_forward_packed<0x0000u, 0xEEEEu, true, 8> : hmm_forward_packed<0x0000u, 0xEEEEu, true, 4>;
                 if (ex == 0x5554u && lg == 0x0000u) return rl == 4 ? hmm_forward_packed<0x5554u, 0x0000u, true, 4> : hmm_forward_packed<0x5554u, 0x0000u, true, 8>;
             }
+            if ((rl == 0 || rl == 4) && !(fin && atoi(fin) == 0)) return hmm_forward_packed<0x0000u, 0xEEECu, true, 4, true>;
             return rl == 8 ? hmm_forward_packed<0x0000u, 0xEEECu, true, 8>
                  : rl == 6 ? hmm_forward_packed<0x0000u, 0xEEECu, true, 6> : hmm_forward_packed<0x0000u, 0xEEECu, true, 4>;
         }

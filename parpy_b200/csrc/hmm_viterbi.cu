@@ -20,6 +20,7 @@
 #include "../../include/parpy_b200.h"
 #include "common.cuh"
 #include "cluster.cuh"
+#include "tmem.cuh"
 
 namespace {
 
@@ -168,14 +169,12 @@ __device__ __forceinline__ bool vit_mbar_wait(unsigned mbar, unsigned parity, in
     return false;
 }
 
-// Observation byte t of a sequence, kept inside the emission table.
-__device__ __forceinline__ int vit_obs(const VitParams &p, const uint8_t *obs, int t) {
-    int o = obs[t];
-    if (o > p.obs_max) {
-        if (threadIdx.x == 0) atomicOr(&g_vit_status, 2u);
-        o = p.obs_max;
-    }
-    return o;
+// Observation byte t of a sequence, kept inside the emission table (no branch in the time loop:
+// `bad` is raised into the status word once per sequence).
+__device__ __forceinline__ int vit_obs(const VitParams &p, const uint8_t *obs, int t, bool &bad) {
+    const int o = obs[t];
+    bad = bad || o > p.obs_max;
+    return min(o, p.obs_max);
 }
 
 // One CTA waits, with the kernel's bounded wait, on an mbarrier that nothing ever completes:
@@ -210,10 +209,19 @@ __device__ __forceinline__ void vit_send_layer0(unsigned dst, unsigned rmbar, un
     }
 }
 
-template <bool ASYNC>
-__global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p) {
+// TM (4096 k-mers and more): 1024 threads per CTA; a thread keeps layers 0..3 of its four k-mers in
+// registers and layers 4..15 in tensor memory (48 of its warp's columns, one float2 per k-mer pair
+// and layer, moved with tcgen05.ld/st), its transition values and decision slack in shared memory.
+// A 7-mer sequence then takes a cluster of 4 CTAs instead of 8 (33 clusters on 132 SMs instead of
+// 15 on 120) with 8 warps per scheduler instead of 4. Same arithmetic, same paths.
+// MAXT: the largest CTA the instantiation is launched with (256 for the one-CTA 5-mer layout, which
+// then has 255 registers per thread to work with and keeps everything in them).
+template <bool ASYNC, bool TM, int MAXT = (TM ? 1024 : 512)>
+__global__ void __launch_bounds__(MAXT, 1) hmm_viterbi_resident(const VitParams p) {
     constexpr unsigned NB = ASYNC ? 4u : 2u;      // layer-0 buffers
-    extern __shared__ __align__(16) float a0s[];  // [NB][4][M] layer-0 values this CTA consumes
+    constexpr int RL = TM ? 4 : kLayers;          // layers kept in registers
+    extern __shared__ __align__(16) float a0s[];  // [NB][4][M] layer-0 values this CTA consumes; TM: + Ts, slack
+    __shared__ unsigned s_tmem;                   // TM: base address of the CTA's tensor memory
     __shared__ __align__(8) unsigned long long s_mbar[4];
     __shared__ float2 s_t2[kLayers];   // (trans2[d], trans2[d])
     __shared__ int s_seq;
@@ -241,12 +249,22 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
     uint4 *codes = p.codes + (long long)(blockIdx.x / CS) * p.codes_per_cluster;
 
     if (tid < kLayers) s_t2[tid] = vdup2(__ldg(p.trans2 + tid));
+    float4 *Ts = reinterpret_cast<float4 *>(a0s + NB * 4 * M);   // TM: [4][NT] transition values
+    float4 *Ss = Ts + 4 * NT;                                    // TM: [NT] decision slack
+    unsigned tm_all = 0, tm = 0;
+    if constexpr (TM) {
+        if (warp == 0) tmem_alloc_all(&s_tmem);
+        tmem_publish();
+        tm_all = s_tmem;
+        tm = tmem_warp_base(tm_all, warp, 64 * (warp >> 2));
+    }
     float2 T[4][2];   // transition log-probabilities into the thread's two k-mer pairs
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         const float4 v = __ldg(reinterpret_cast<const float4 *>(p.trans1) + (j * Kq + (g >> 2)));
         T[j][0] = make_float2(v.x, v.y);
         T[j][1] = make_float2(v.z, v.w);
+        if constexpr (TM) Ts[j * NT + tid] = v;
     }
     // Tmax + 2 t2max per k-mer of the thread (see decide4); infinite when a table holds -inf
     float slack[4];
@@ -265,6 +283,7 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
             slack[2 * h] = mx + 2.0f * t2max;
             slack[2 * h + 1] = my + 2.0f * t2max;
         }
+        if constexpr (TM) Ss[tid] = make_float4(slack[0], slack[1], slack[2], slack[3]);
     }
     const unsigned a0_base = smem_u32(a0s);
     unsigned dst0;
@@ -306,6 +325,7 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
         const int len = static_cast<int>(len64);
         const uint8_t *obs = p.data + (long long)seq * p.maxlen;
         uint32_t *res = p.out + (long long)seq * p.out_stride;
+        bool bad_obs = false;   // an observation byte outside the emission table was met
 
         for (int t = 0; t < len; t += bos) {
             const int L = min(len - t, p.batch);        // positions of this window that exist
@@ -314,26 +334,44 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
             const int karg = (L == p.batch && ((p.batch - 1) & 1)) ? p.batch - 2 : L - 1;
 
             // ---- window start (hmm.cu:352-376) ------------------------------------------
-            float chi[kLayers][4];
+            float chi[RL][4];   // TM: layers RL..15 live in tensor memory
             float e[4];
+            // layer d of this thread's four k-mers, wherever it lives (d is a constant after unrolling)
+            auto put_layer = [&](const int d, const float4 v) {
+                if (d < RL) { chi[d % RL][0] = v.x; chi[d % RL][1] = v.y; chi[d % RL][2] = v.z; chi[d % RL][3] = v.w; }
+                else if constexpr (TM) tmem_st4(tm + 4 * (d - RL), v);
+            };
+            auto get_layer = [&](const int d) {
+                float4 v = make_float4(chi[d % RL][0], chi[d % RL][1], chi[d % RL][2], chi[d % RL][3]);
+                if constexpr (TM) {
+                    if (d >= RL) {
+                        tmem_ld4(tm + 4 * (d - RL), v);
+                        tmem_wait_ld(v);
+                    }
+                }
+                return v;
+            };
             {
-                const float4 v = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)vit_obs(p, obs, t) * K + g));
+                const float4 v = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)vit_obs(p, obs, t, bad_obs) * K + g));
                 e[0] = v.x; e[1] = v.y; e[2] = v.z; e[3] = v.w;
             }
             if (t == 0) {
 #pragma unroll
                 for (int d = 0; d < kLayers; ++d) {
                     const float4 v = __ldg(reinterpret_cast<const float4 *>(p.initial_prob + d * K + g));
-                    chi[d][0] = v.x + e[0]; chi[d][1] = v.y + e[1]; chi[d][2] = v.z + e[2]; chi[d][3] = v.w + e[3];
+                    put_layer(d, make_float4(v.x + e[0], v.y + e[1], v.z + e[2], v.w + e[3]));
                 }
             } else {
                 const unsigned last = s_last;
 #pragma unroll
-                for (int d = 0; d < kLayers; ++d)
+                for (int d = 0; d < kLayers; ++d) {
+                    float w[4];
 #pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        chi[d][c] = (unsigned)(d * K + g + c) == last ? e[c] : -INFINITY;
+                    for (int c = 0; c < 4; ++c) w[c] = (unsigned)(d * K + g + c) == last ? e[c] : -INFINITY;
+                    put_layer(d, make_float4(w[0], w[1], w[2], w[3]));
+                }
             }
+            if constexpr (TM) tmem_wait_st();
             unsigned buf = 0;   // buffer that holds the previous step's layer 0
             vit_send_layer0<ASYNC>(dst0, rmbar0, mbar0, tid == 0, 16u * M, chi[0][0], chi[0][1], chi[0][2], chi[0][3]);
             if (!ASYNC) arrive();
@@ -346,9 +384,12 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
                 float v = chi[0][0];
                 unsigned i = (unsigned)g;
 #pragma unroll
-                for (int d = 0; d < kLayers; ++d)
+                for (int d = 0; d < kLayers; ++d) {
+                    const float4 l4 = get_layer(d);
+                    const float w[4] = {l4.x, l4.y, l4.z, l4.w};
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) argmax_combine(v, i, chi[d][c], (unsigned)(d * K + g + c));
+                    for (int c = 0; c < 4; ++c) argmax_combine(v, i, w[c], (unsigned)(d * K + g + c));
+                }
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) {
                     const float ov = __shfl_xor_sync(0xffffffffu, v, o);
@@ -385,7 +426,7 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
             // ---- forward steps with back pointers (hmm.cu:116-176, 378-412) ----------------
             for (int k = 1; k < L; ++k) {
                 {
-                    const float4 v = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)vit_obs(p, obs, t + k) * K + g));
+                    const float4 v = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)vit_obs(p, obs, t + k, bad_obs) * K + g));
                     e[0] = v.x; e[1] = v.y; e[2] = v.z; e[3] = v.w;
                 }
                 if (ASYNC) {
@@ -407,30 +448,92 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
                 // the short path when it is safe for both in every lane of the warp
                 Decide4 dec[4];
                 bool fast[2];
+                // TM: the transition values come out of shared memory for the decision and the winner's
+                // selection only (the rare all-candidates path fetches them again)
+                float2 Tq[4][2];
+                float sl[4];
+                if constexpr (TM) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float4 v = Ts[j * NT + tid];
+                        Tq[j][0] = make_float2(v.x, v.y);
+                        Tq[j][1] = make_float2(v.z, v.w);
+                    }
+                    const float4 s4 = Ss[tid];
+                    sl[0] = s4.x; sl[1] = s4.y; sl[2] = s4.z; sl[3] = s4.w;
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) { Tq[j][0] = T[j][0]; Tq[j][1] = T[j][1]; }
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) sl[c] = slack[c];
+                }
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     float2 sj[4];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) sj[j] = vadd2(T[j][h], a[j]);
-                    dec[2 * h] = decide4(sj[0].x, sj[1].x, sj[2].x, sj[3].x, slack[2 * h]);
-                    dec[2 * h + 1] = decide4(sj[0].y, sj[1].y, sj[2].y, sj[3].y, slack[2 * h + 1]);
+                    for (int j = 0; j < 4; ++j) sj[j] = vadd2(Tq[j][h], a[j]);
+                    dec[2 * h] = decide4(sj[0].x, sj[1].x, sj[2].x, sj[3].x, sl[2 * h]);
+                    dec[2 * h + 1] = decide4(sj[0].y, sj[1].y, sj[2].y, sj[3].y, sl[2 * h + 1]);
                     fast[h] = __all_sync(0xffffffffu, dec[2 * h].safe && dec[2 * h + 1].safe);
+                }
+                // the winner's transition value and layer-0 value of each k-mer pair, chosen here so that
+                // the four candidates' values are dead before the layers start
+                float2 Tw[2], aw[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const unsigned jx = dec[2 * h].j, jy = dec[2 * h + 1].j;
+                    Tw[h] = make_float2(sel4(jx, Tq[0][h].x, Tq[1][h].x, Tq[2][h].x, Tq[3][h].x),
+                                        sel4(jy, Tq[0][h].y, Tq[1][h].y, Tq[2][h].y, Tq[3][h].y));
+                    aw[h] = make_float2(sel4(jx, a[0].x, a[1].x, a[2].x, a[3].x),
+                                        sel4(jy, a[0].x, a[1].x, a[2].x, a[3].x));
                 }
                 // layers [d_lo, d_hi) of pair h, ascending (a layer reads the old value of the next)
                 auto layers = [&](const int h, const int d_lo, const int d_hi) {
+                    // TM: old values of the layers above the register layers, requested one layer ahead
+                    // (pair h of layer d sits in columns 4 (d - RL) + 2 h, 2 h + 1)
+                    float2 nA = make_float2(0.f, 0.f), nB = nA;
+                    if constexpr (TM) {
+                        if (d_hi > RL - 1) tmem_ld2(tm + 2 * h, nA);   // layer RL
+                    }
+                    // old value of layer min(d + 1, 15) for pair h; called once per d, in ascending order
+                    auto old_next = [&](const int d) {
+                        if constexpr (!TM) {
+                            return make_float2(chi[(d + 1 < kLayers ? d + 1 : 15) % RL][2 * h],
+                                               chi[(d + 1 < kLayers ? d + 1 : 15) % RL][2 * h + 1]);
+                        } else {
+                            if (d + 1 < RL) return make_float2(chi[(d + 1) % RL][2 * h], chi[(d + 1) % RL][2 * h + 1]);
+                            if (d == RL - 1) {
+                                tmem_wait_ld(nA);
+                                tmem_ld2(tm + 4 + 2 * h, nB);   // layer RL + 1
+                                return nA;
+                            }
+                            if (d < kLayers - 1) {
+                                float2 &cur = (d & 1) ? nA : nB, &ahead = (d & 1) ? nB : nA;
+                                tmem_wait_ld(cur);
+                                // requested before layer d is written: a load has completed before
+                                // anything overwrites its columns
+                                if (d + 2 < kLayers) tmem_ld2(tm + 4 * (d + 2 - RL) + 2 * h, ahead);
+                                return cur;
+                            }
+                            return (d & 1) ? nB : nA;   // layer 15 reads its own old value, fetched for layer 14
+                        }
+                    };
+                    auto put_pair = [&](const int d, const float2 r) {
+                        if (d < RL) {
+                            chi[d % RL][2 * h] = r.x;
+                            chi[d % RL][2 * h + 1] = r.y;
+                        } else if constexpr (TM) {
+                            tmem_st2(tm + 4 * (d - RL) + 2 * h, r);
+                        }
+                    };
                     if (fast[h]) {
                         const unsigned jx = dec[2 * h].j, jy = dec[2 * h + 1].j;
-                        const float2 Tw = make_float2(sel4(jx, T[0][h].x, T[1][h].x, T[2][h].x, T[3][h].x),
-                                                      sel4(jy, T[0][h].y, T[1][h].y, T[2][h].y, T[3][h].y));
-                        const float2 aw = make_float2(sel4(jx, a[0].x, a[1].x, a[2].x, a[3].x),
-                                                      sel4(jy, a[0].x, a[1].x, a[2].x, a[3].x));
                         const unsigned ex = jx << (8 * h), ey = jy << (8 * h + 4);     // even layers
                         const unsigned ox = ex << 16, oy = ey << 16;                     // odd layers
 #pragma unroll
                         for (int d = d_lo; d < d_hi; ++d) {
-                            const float2 val = vadd2(vadd2(Tw, s_t2[d]), aw);
-                            const float2 nx = make_float2(chi[d + 1 < kLayers ? d + 1 : 15][2 * h],
-                                                          chi[d + 1 < kLayers ? d + 1 : 15][2 * h + 1]);
+                            const float2 val = vadd2(vadd2(Tw[h], s_t2[d]), aw[h]);
+                            const float2 nx = old_next(d);
                             const float2 p5 = d == 15 ? vadd2(vdup2(p.gamma), nx)
                                             : d == 14 ? vadd2(vdup2(p.synthetic), nx) : nx;
                             const unsigned sh = 8 * h + 16 * (d & 1);
@@ -438,8 +541,7 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
                             const unsigned cy = p5.y > val.y ? (4u << (sh + 4)) : ((d & 1) ? oy : ey);
                             const float2 r = vadd2(make_float2(fmaxf(val.x, p5.x), fmaxf(val.y, p5.y)),
                                                    make_float2(e[2 * h], e[2 * h + 1]));
-                            chi[d][2 * h] = r.x;
-                            chi[d][2 * h + 1] = r.y;
+                            put_pair(d, r);
                             words[d >> 1] |= cx | cy;
                         }
                     } else {
@@ -449,9 +551,15 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
                             // all four k-mer candidates: (T + t2) + a, as the reference adds them
                             float2 cand[4];
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) cand[j] = vadd2(vadd2(T[j][h], t2), a[j]);
-                            const float2 nx = make_float2(chi[d + 1 < kLayers ? d + 1 : 15][2 * h],
-                                                          chi[d + 1 < kLayers ? d + 1 : 15][2 * h + 1]);
+                            for (int j = 0; j < 4; ++j) {
+                                float2 Tj = T[j][h];
+                                if constexpr (TM) {
+                                    const float4 v = Ts[j * NT + tid];
+                                    Tj = h == 0 ? make_float2(v.x, v.y) : make_float2(v.z, v.w);
+                                }
+                                cand[j] = vadd2(vadd2(Tj, t2), a[j]);
+                            }
+                            const float2 nx = old_next(d);
                             // duration-chain candidate; below layer 14 its log-probability is 0
                             const float2 p5 = d == 15 ? vadd2(vdup2(p.gamma), nx)
                                             : d == 14 ? vadd2(vdup2(p.synthetic), nx) : nx;
@@ -475,8 +583,7 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
                                 }
                             }
                             const float2 r = vadd2(make_float2(bx, by), make_float2(e[2 * h], e[2 * h + 1]));
-                            chi[d][2 * h] = r.x;
-                            chi[d][2 * h + 1] = r.y;
+                            put_pair(d, r);
                             words[d >> 1] |= cx | cy;
                         }
                     }
@@ -489,6 +596,7 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
                 if (!ASYNC) arrive();
                 layers(0, 1, kLayers);
                 layers(1, 1, kLayers);
+                if constexpr (TM) tmem_wait_st();   // the next step (and the arg-max) read what this one stored
                 uint4 *slot = codes + ((long long)(k - 1) * Kq + gthread) * 2;
                 __stcg(slot, make_uint4(words[0], words[1], words[2], words[3]));
                 __stcg(slot + 1, make_uint4(words[4], words[5], words[6], words[7]));
@@ -574,11 +682,17 @@ __global__ void __launch_bounds__(512, 1) hmm_viterbi_resident(const VitParams p
             arrive();
             wait();
         }
+        if (bad_obs && tid == 0) atomicOr(&g_vit_status, 2u);
+    }
+    if constexpr (TM) {
+        tmem_publish();   // every warp is done with its columns
+        if (warp == 0) tmem_free_all(tm_all);
     }
 }
 
 struct VitPlan {
     int nt = 0, cs = 0;
+    bool tm = false;   // 1024-thread CTAs with the upper layers in tensor memory
 };
 
 bool vit_plan(long long K, VitPlan *pl) {
@@ -591,10 +705,16 @@ bool vit_plan(long long K, VitPlan *pl) {
         const long long v = atoll(env);
         if (v >= 32 && v <= 512 && (v & (v - 1)) == 0 && v <= threads) nt = v;
     }
+    // 4096 k-mers and more: 1024 threads per CTA, layers 4..15 in tensor memory (7-mer: clusters of 4 on
+    // 132 SMs instead of clusters of 8 on 120, twice the warps per scheduler)
+    bool tm = threads >= 1024 && getenv("PARPY_B200_VIT_NT") == nullptr;
+    if (const char *env = getenv("PARPY_B200_VIT_TMEM")) tm = tm && atoi(env) != 0;
+    if (tm) nt = 1024;
     long long cs = threads / nt;
     if (cs > 16) return false;
     pl->nt = (int)nt;
     pl->cs = (int)cs;
+    pl->tm = tm;
     return true;
 }
 
@@ -633,8 +753,14 @@ static int32_t viterbi_impl(float gamma, const float *initial_prob, int64_t num_
     bool async_x = true;
     if (const char *env = getenv("PARPY_B200_VIT_ASYNC")) async_x = atoi(env) != 0;
     async_x = async_x && pl.cs >= 2 && pl.cs <= 8;
-    void (*kernel)(const VitParams) = async_x ? hmm_viterbi_resident<true> : hmm_viterbi_resident<false>;
-    const size_t smem = size_t(async_x ? 4 : 2) * 4 * pl.nt * sizeof(float);
+    void (*kernel)(const VitParams) = pl.tm ? (async_x ? hmm_viterbi_resident<true, true> : hmm_viterbi_resident<false, true>)
+                                            : (async_x ? hmm_viterbi_resident<true, false> : hmm_viterbi_resident<false, false>);
+    // One CTA of at most 256 threads per sequence: with no more sequences than SMs every CTA has an SM to
+    // itself, and the instantiation bounded to 256 threads keeps all 64 values and the transition
+    // table in its 253 registers (no spills); larger batches keep the 128-register one, two CTAs per SM.
+    if (!pl.tm && !async_x && pl.nt <= 256 && num_instances <= dev.sm_count) kernel = hmm_viterbi_resident<false, false, 256>;
+    // layer-0 buffers; with tensor memory also the transition values and the decision slack of every thread
+    const size_t smem = size_t(async_x ? 4 : 2) * 4 * pl.nt * sizeof(float) + (pl.tm ? size_t(5) * pl.nt * sizeof(float4) : 0);
     if (pl.cs > 8) PB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
     PB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     cudaLaunchConfig_t cfg;
@@ -655,9 +781,9 @@ static int32_t viterbi_impl(float gamma, const float *initial_prob, int64_t num_
     PB_REQUIRE(max_clusters >= 1, "viterbi: no cluster of %d CTAs x %d threads fits this device", pl.cs, pl.nt);
 
     // back-pointer nibbles: (batch - 1) steps x K/4 threads x 32 bytes per resident cluster,
-    // at most ~3 GiB in total
+    // at most ~6 GiB in total (33 clusters of a 7-mer model with 1024-step windows: 4.4 GB)
     const long long per_cluster = (batch_size - 1) * (K / 4) * 2;   // uint4 elements
-    const long long budget = (3LL << 30) / (per_cluster * (long long)sizeof(uint4));
+    const long long budget = (6LL << 30) / (per_cluster * (long long)sizeof(uint4));
     long long clusters = std::min<long long>(std::min<long long>(max_clusters, num_instances), std::max<long long>(budget, 1));
     void *ws_codes = nullptr, *ws = nullptr;
     rc = pb::workspace((size_t)clusters * (size_t)per_cluster * sizeof(uint4), &ws_codes, stream, 4);

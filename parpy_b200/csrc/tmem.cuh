@@ -37,9 +37,18 @@ __device__ __forceinline__ void tmem_st4(unsigned taddr, const float4 &v) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};"
                  ::"r"(taddr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
+__device__ __forceinline__ void tmem_ld2(unsigned taddr, float2 &v) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st2(unsigned taddr, const float2 &v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x2.b32 [%0], {%1, %2};" ::"r"(taddr), "f"(v.x), "f"(v.y) : "memory");
+}
 // All earlier loads (stores) of the calling thread have completed. The overloads name the
 // registers a load filled, so that no use of them can be scheduled ahead of the wait.
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_ld(float2 &a) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" : "+f"(a.x), "+f"(a.y)::"memory");
+}
 __device__ __forceinline__ void tmem_wait_ld(float4 &a) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" : "+f"(a.x), "+f"(a.y), "+f"(a.z), "+f"(a.w)::"memory");
 }

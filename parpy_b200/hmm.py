@@ -193,7 +193,7 @@ def viterbi(hmm, seqs, batch_size=1024, batch_overlap=128, check=True):
     arrays. With ``check`` (default) the call waits for the kernel and raises
     ``RuntimeError`` if one of its bounded waits ran out, in which case the paths
     are not valid; ``check=False`` leaves the call asynchronous and the status to
-    :func:`viterbi_status`. Back-pointer scratch of up to 3 GiB per (device,
+    :func:`viterbi_status`. Back-pointer scratch of up to 6 GiB per (device,
     stream) is kept by the library between calls."""
     import torch
     from . import _native

@@ -285,14 +285,18 @@ def test_scaled_variant_against_golden_oracle_and_log_space(native, oracle_mod):
     for i in range(6):
         a = (a1 if int(seqs7["lens"][i]) & 1 else a2)[i].cpu().numpy()
         assert max_rel(a, exp_alpha[i]) <= REL_ORACLE
-    # zero-probability emissions: dead states are exactly -inf, an impossible sequence gives -inf
+    # zero-probability emissions: an impossible sequence scores NaN, as it does in the reference's
+    # final reduction ((-inf) - (-inf), benchmarks/forward.py:168-173) and in the oracle
     dead = dict(hmm7)
     dead_tbl = hmm7["output_prob"].clone()
     last = int(seqs7["data"][2, int(seqs7["lens"][2]) - 1].item()) & 0xFF
     dead_tbl[last, :] = -np.inf
     dead["output_prob"] = dead_tbl
     rc, res, _, _ = cabi_forward(native, to_dev(dead), to_dev(seqs7), FLAGS["scaled"])
-    assert rc == 0 and np.isneginf(res.cpu().numpy()[2])
+    exp_dead = oracle_mod.forward(dead, seqs7)
+    got_dead = res.cpu().numpy()
+    assert rc == 0 and np.isnan(got_dead[2]) and np.array_equal(np.isnan(got_dead), np.isnan(exp_dead))
+    assert max_rel(got_dead[~np.isnan(exp_dead)], exp_dead[~np.isnan(exp_dead)]) <= REL_ORACLE
     # small state spaces are refused rather than silently run in log space
     rc, _, _, _ = cabi_forward(native, to_dev(load_model("3mer")), to_dev(load_signals(shortest_reads(2))),
                                FLAGS["scaled"])
@@ -717,3 +721,36 @@ def test_transcription_of_the_emitted_cuda_agrees_with_the_oracle(native, oracle
     assert max_rel(got, exp) <= REL_ORACLE
     rc, res, _, _ = cabi_forward(native, to_dev(hmm), to_dev(seqs))
     assert rc == 0 and max_rel(res.cpu().numpy(), got) <= REL_ORACLE
+
+
+@pytest.mark.parametrize("finite", ["0", "1"])
+def test_7mer_zero_probabilities_in_every_table(native, oracle_mod, monkeypatch, finite):
+    # -inf log-probabilities in the emission table (whole rows and single k-mers), in the transition
+    # table and in the duration table: dead states stay exactly -inf and no alpha turns into NaN; an
+    # impossible sequence scores NaN, the (-inf) - (-inf) of the reference's final reduction
+    # (benchmarks/forward.py:168-173). PARPY_B200_FWD_FINITE=1 runs the variant that keeps log 0 as a
+    # large negative number inside the kernel and must give the same answers.
+    from parpy_b200 import synthetic
+    monkeypatch.setenv("PARPY_B200_FWD_FINITE", finite)
+    hmm = synthetic.hmm_model(7, seed=61)
+    seqs = synthetic.hmm_sequences(6, 3, 60, seed=62, pad_value=0)
+    hmm["output_prob"] = hmm["output_prob"].clone()
+    hmm["trans1"] = hmm["trans1"].clone()
+    hmm["trans2"] = hmm["trans2"].clone()
+    last = int(seqs["data"][2, int(seqs["lens"][2]) - 1].item())
+    hmm["output_prob"][last, :] = -np.inf                     # sequence 2 becomes impossible at its last step
+    hmm["output_prob"][:, 5::97] = -np.inf                    # some k-mers never emit anything
+    hmm["trans1"][3::11, 1] = -np.inf                         # some k-mer transitions are impossible
+    hmm["trans2"][9] = -np.inf                                # one duration never starts
+    exp, exp_alpha = oracle_mod.forward(hmm, seqs, want_alpha=True)
+    rc, res, a1, a2 = cabi_forward(native, to_dev(hmm), to_dev(seqs), 2, alpha=True)
+    assert rc == 0, native.error_message()
+    got = res.cpu().numpy()
+    dead = np.isnan(exp)
+    assert dead[2] and not dead.all() and np.array_equal(np.isnan(got), dead)
+    assert max_rel(got[~dead], exp[~dead]) <= REL_ORACLE
+    for i in range(6):
+        a = (a1 if int(seqs["lens"][i]) & 1 else a2)[i].cpu().numpy()
+        assert not np.isnan(a).any()
+        assert np.array_equal(np.isneginf(a), np.isneginf(exp_alpha[i]))
+        assert max_rel(a, exp_alpha[i]) <= REL_ORACLE

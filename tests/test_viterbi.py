@@ -181,6 +181,14 @@ def test_layer0_exchange_variants_agree_at_scale(monkeypatch, k, nseq, lo, hi):
         got = hmm_mod.viterbi_paths(dh, ds)
         for i, (a, b) in enumerate(zip(got, ref)):
             assert np.array_equal(a, b), (rep, i, int(np.argmax(a != b)))
+    # the layout with all 16 layers in registers (512-thread CTAs, twice the CTAs per sequence) against
+    # the default one for these sizes (1024-thread CTAs, layers 4..15 in tensor memory), both exchanges
+    monkeypatch.setenv("PARPY_B200_VIT_TMEM", "0")
+    for async_x in ("0", "1"):
+        monkeypatch.setenv("PARPY_B200_VIT_ASYNC", async_x)
+        got = hmm_mod.viterbi_paths(dh, ds)
+        for i, (a, b) in enumerate(zip(got, ref)):
+            assert np.array_equal(a, b), (async_x, i, int(np.argmax(a != b)))
 
 
 @pytest.mark.gpu
