@@ -56,7 +56,9 @@ int32_t parpy_b200_device_summary(int32_t *sm_count, int32_t *cc_major, int32_t 
  * num_instances). Layouts: initial_prob f32[num_states]; output_prob
  * f32[n_obs, K] with K = num_states/16; trans1 f32[K,4]; trans2 f32[16];
  * data int8/uint8 [num_instances, maxlen] with values < n_obs at t < lens[i];
- * lens i64[num_instances]; result f32[num_instances].
+ * lens i64[num_instances]; result f32[num_instances]. Log 0 is -inf in every
+ * table; a sequence the model cannot produce scores NaN, the (-inf) - (-inf)
+ * of the reference's final reduction (benchmarks/forward.py:168-173).
  * alpha1/alpha2 f32[num_instances, num_states] are the reference's scratch.
  * The resident kernel keeps alpha on chip and leaves them untouched (they may
  * be NULL); the streaming kernel (state spaces the resident kernel does not

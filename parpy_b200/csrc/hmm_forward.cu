@@ -891,7 +891,18 @@ __device__ __forceinline__ float2 ex2_poly2_negabs(float2 t2) {
 // absolute error 3.3e-7 evaluated in fp32; lg2.approx is specified to 2.4e-7). Folded into the
 // final multiply-add of the log-sum-exp, it costs five packed instructions more than the
 // MUFU form and takes two MUFU operations per pair off the pipe that bounds the kernel.
-__device__ __forceinline__ float2 log1p_poly2_times(float2 x) {
+// `short6`: the same with P of degree 5 (max absolute error 1.5e-6, mean error 3e-9): one packed
+// instruction less per pair; still far below the rounding of an alpha value of magnitude 100 and more.
+__device__ __forceinline__ float2 log1p_poly2_times(float2 x, bool short6 = false) {
+    if (short6) {
+        float2 p = dup2(-0.01833890751004219f);
+        p = fma2(p, x, dup2(0.08557005226612091f));
+        p = fma2(p, x, dup2(-0.19376108050346375f));
+        p = fma2(p, x, dup2(0.31764912605285645f));
+        p = fma2(p, x, dup2(-0.4978750944137573f));
+        p = fma2(p, x, dup2(0.9999016523361206f));
+        return p;
+    }
     float2 p = dup2(0.01076451875269413f);
     p = fma2(p, x, dup2(-0.05514521896839142f));
     p = fma2(p, x, dup2(0.1346745640039444f));
@@ -906,14 +917,15 @@ __device__ __forceinline__ float2 log1p_poly2_times(float2 x) {
 // (-inf, -inf) gives -inf. `lgpoly`: the logarithm is the polynomial above.
 // `finite`: the caller guarantees finite operands (log 0 is kept as a large negative number, see
 // kLogZero), so (-inf) - (-inf) cannot occur and the NaN clamp is dropped.
-__device__ __forceinline__ float2 lse2_pair(bool poly, float2 u, float2 v, bool lgpoly = false, bool finite = false) {
+__device__ __forceinline__ float2 lse2_pair(bool poly, float2 u, float2 v, bool lgpoly = false, bool finite = false,
+                                            bool short6 = false) {
     const float2 mx = max2(u, v);
     const float2 t = mul2(sub2(u, v), dup2(kLog2e));   // |t| = |u - v| * log2(e)
     float2 ex;
     if (poly) ex = ex2_poly2_negabs(t);
     else ex = make_float2(pb::ex2_approx(-fabsf(t.x)), pb::ex2_approx(-fabsf(t.y)));
     if (lgpoly) {
-        const float2 r = fma2(ex, log1p_poly2_times(ex), mx);
+        const float2 r = fma2(ex, log1p_poly2_times(ex, short6), mx);
         return (poly || finite) ? r : make_float2(fmaxf(r.x, -INFINITY), fmaxf(r.y, -INFINITY));
     }
     const float2 s = add2(ex, dup2(1.0f));
@@ -940,7 +952,7 @@ __device__ __forceinline__ float2 lse4_pair(float2 p0, float2 p1, float2 p2, flo
 // TMEM: layers RL..15 and the transition columns live in tensor memory instead of shared memory
 // (RL = layers kept in registers; the shared-memory layout is fixed at 8).
 // FIN: finite arithmetic (kLogZero in place of -inf inside the kernel; no NaN clamps).
-template <unsigned POLY_MASK, unsigned LG_MASK = 0u, bool TMEM = false, int RL = kRegLayers, bool FIN = false>
+template <unsigned POLY_MASK, unsigned LG_MASK = 0u, bool TMEM = false, int RL = kRegLayers, bool FIN = false, bool LG6 = false>
 __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p) {
     static_assert(TMEM ? (RL >= 4 && RL <= 8 && RL % 2 == 0) : RL == kRegLayers, "register layers");
     extern __shared__ __align__(16) float smem_dyn[];
@@ -1068,7 +1080,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
                 const float2 w = s_t2[0];
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
-                    a[0][h] = add2(lse2_pair((POLY_MASK & 1u) != 0, add2(w, q[h]), a[1][h], (LG_MASK & 1u) != 0, FIN), ev[h]);
+                    a[0][h] = add2(lse2_pair((POLY_MASK & 1u) != 0, add2(w, q[h]), a[1][h], (LG_MASK & 1u) != 0, FIN, LG6), ev[h]);
             }
             st_cluster_v4(dst, a[0][0].x, a[0][0].y, a[0][1].x, a[0][1].y);
             cluster_arrive();
@@ -1077,7 +1089,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
                 const float2 w = s_t2[d];
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
-                    a[d][h] = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[h]), a[d + 1][h], ((LG_MASK >> d) & 1u) != 0, FIN), ev[h]);
+                    a[d][h] = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[h]), a[d + 1][h], ((LG_MASK >> d) & 1u) != 0, FIN, LG6), ev[h]);
             }
             // layers 7..15: the "next layer" operand comes from shared memory
             float4 nxt, nxt2;   // TMEM: old values of the next layer, requested one layer ahead
@@ -1091,9 +1103,9 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
             {
                 const float2 w = s_t2[RL - 1];
                 a[RL - 1][0] = add2(lse2_pair(((POLY_MASK >> (RL - 1)) & 1u) != 0, add2(w, q[0]),
-                                                      make_float2(nxt.x, nxt.y), ((LG_MASK >> (RL - 1)) & 1u) != 0, FIN), ev[0]);
+                                                      make_float2(nxt.x, nxt.y), ((LG_MASK >> (RL - 1)) & 1u) != 0, FIN, LG6), ev[0]);
                 a[RL - 1][1] = add2(lse2_pair(((POLY_MASK >> (RL - 1)) & 1u) != 0, add2(w, q[1]),
-                                                      make_float2(nxt.z, nxt.w), ((LG_MASK >> (RL - 1)) & 1u) != 0, FIN), ev[1]);
+                                                      make_float2(nxt.z, nxt.w), ((LG_MASK >> (RL - 1)) & 1u) != 0, FIN, LG6), ev[1]);
             }
 #pragma unroll
             for (int d = RL; d < kLayers; ++d) {
@@ -1116,8 +1128,8 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
                     v0.x += c; v0.y += c; v1.x += c; v1.y += c;
                 }
                 const float2 w = s_t2[d];
-                const float2 r0 = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[0]), v0, ((LG_MASK >> d) & 1u) != 0, FIN), ev[0]);
-                const float2 r1 = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[1]), v1, ((LG_MASK >> d) & 1u) != 0, FIN), ev[1]);
+                const float2 r0 = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[0]), v0, ((LG_MASK >> d) & 1u) != 0, FIN, LG6), ev[0]);
+                const float2 r1 = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[1]), v1, ((LG_MASK >> d) & 1u) != 0, FIN, LG6), ev[1]);
                 if constexpr (TMEM) tmem_st4(tm + 4 * (d - RL), make_float4(r0.x, r0.y, r1.x, r1.y));
                 else As[(d - RL) * NT + tid] = make_float4(r0.x, r0.y, r1.x, r1.y);
             }
@@ -1223,7 +1235,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
 // exponential on the layers of POLY_MASK). Layer 0 is exchanged
 // through the CTA's own shared memory, so a time step costs one __syncthreads instead of
 // a cluster barrier, which is what bounds the step time of small state spaces.
-template <unsigned POLY_MASK, unsigned LG_MASK = 0u, bool FIN = false>
+template <unsigned POLY_MASK, unsigned LG_MASK = 0u, bool FIN = false, bool LG6 = false>
 __global__ void __launch_bounds__(256, 1) hmm_forward_packed_cta(const FwdParams p) {
     __shared__ __align__(16) float a0s[2][1024];   // layer 0 of all k-mers, double buffered
     __shared__ int s_seq;
@@ -1319,7 +1331,7 @@ __global__ void __launch_bounds__(256, 1) hmm_forward_packed_cta(const FwdParams
                         v.x += c;
                         v.y += c;
                     }
-                    a[d][h] = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[h]), v, ((LG_MASK >> d) & 1u) != 0, FIN), ev[h]);
+                    a[d][h] = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[h]), v, ((LG_MASK >> d) & 1u) != 0, FIN, LG6), ev[h]);
                 }
                 if (d == 0)
                     *reinterpret_cast<float4 *>(&a0s[buf ^ 1u][g]) =
@@ -2379,7 +2391,12 @@ ResidentKernel pick_kernel(const Plan &pl, bool five) {
         if (getenv("PARPY_B200_FWD_POLY") == nullptr) {
             const char *fin = getenv("PARPY_B200_FWD_FINITE");   // finite arithmetic unless set to 0
             if (fin && atoi(fin) == 0) return hmm_forward_packed_cta<0x0000u, 0xEEECu>;
-            return hmm_forward_packed_cta<0x0000u, 0xEEECu, true>;
+            // finite arithmetic 2.54 -> 2.48 ms, degree-5 logarithm polynomial 2.42 ms (with 13 layers: 2.44)
+            if (const char *l6 = getenv("PARPY_B200_FWD_LG6")) {
+                if (atoi(l6) == 0) return hmm_forward_packed_cta<0x0000u, 0xEEECu, true>;
+                if (atoi(l6) == 2) return hmm_forward_packed_cta<0x0000u, 0xFEFCu, true, true>;
+            }
+            return hmm_forward_packed_cta<0x0000u, 0xEEECu, true, true>;
         }
         const int npoly = atoi(getenv("PARPY_B200_FWD_POLY"));   // exponential masks only
         switch (npoly) {
@@ -2412,8 +2429,21 @@ ResidentKernel pick_kernel(const Plan &pl, bool five) {
             // PARPY_B200_FWD_FINITE=0 selects the kernel that computes on -inf itself.
             const char *fin = getenv("PARPY_B200_FWD_FINITE");
             if (masks && !(fin && atoi(fin) == 0)) {
+                if (const char *l6 = getenv("PARPY_B200_FWD_LG6"))
+                    if (atoi(l6) != 0) {
+                        if (ex == 0 && lg == 0xEEECu) return hmm_forward_packed<0x0000u, 0xEEECu, true, 4, true, true>;
+                        if (ex == 0 && lg == 0xFEFCu) return hmm_forward_packed<0x0000u, 0xFEFCu, true, 4, true, true>;
+                        if (ex == 0 && lg == 0xFFFEu) return hmm_forward_packed<0x0000u, 0xFFFEu, true, 4, true, true>;
+                        if (ex == 0 && lg == 0xFEFEu) return hmm_forward_packed<0x0000u, 0xFEFEu, true, 4, true, true>;
+                        if (ex == 0 && lg == 0xFFFCu) return hmm_forward_packed<0x0000u, 0xFFFCu, true, 4, true, true>;
+                        if (ex == 0 && lg == 0xFCFCu) return hmm_forward_packed<0x0000u, 0xFCFCu, true, 4, true, true>;
+                        if (ex == 0 && lg == 0xFEECu) return hmm_forward_packed<0x0000u, 0xFEECu, true, 4, true, true>;
+                        if (ex == 0 && lg == 0xEEFCu) return hmm_forward_packed<0x0000u, 0xEEFCu, true, 4, true, true>;
+                    }
 #define PB_FIN(E, L) if (ex == E && lg == L) return hmm_forward_packed<E, L, true, 4, true>
                 PB_FIN(0x0000u, 0xEEEEu);
+                PB_FIN(0x0000u, 0xEEC8u);
+                PB_FIN(0x0000u, 0xECC8u);
                 PB_FIN(0x0000u, 0xFEFEu);
                 PB_FIN(0x0000u, 0xFFFEu);
                 PB_FIN(0x0000u, 0xEEE8u);
@@ -2424,7 +2454,14 @@ ResidentKernel pick_kernel(const Plan &pl, bool five) {
                 if (ex == 0x0000u && lg == 0xEEEEu) return rl == 8 ? hmm_forward_packed<0x0000u, 0xEEEEu, true, 8> : hmm_forward_packed<0x0000u, 0xEEEEu, true, 4>;
                 if (ex == 0x5554u && lg == 0x0000u) return rl == 4 ? hmm_forward_packed<0x5554u, 0x0000u, true, 4> : hmm_forward_packed<0x5554u, 0x0000u, true, 8>;
             }
-            if ((rl == 0 || rl == 4) && !(fin && atoi(fin) == 0)) return hmm_forward_packed<0x0000u, 0xEEECu, true, 4, true>;
+            if ((rl == 0 || rl == 4) && !(fin && atoi(fin) == 0)) {
+                // With the shorter logarithm polynomial (degree 5) 13 layers take it: 2.050e12; the same
+                // masks measured with it: 0xFEFE 2.049e12, 0xFFFC 2.047e12, 0xEEFC 2.041e12, 0xFFFE 2.037e12,
+                // 0xFCFC 2.037e12, 0xFEEC 2.032e12, 0xEEEC 2.025e12. PARPY_B200_FWD_LG6=0: degree 6, 11 layers.
+                const char *l6 = getenv("PARPY_B200_FWD_LG6");
+                if (l6 && atoi(l6) == 0) return hmm_forward_packed<0x0000u, 0xEEECu, true, 4, true>;
+                return hmm_forward_packed<0x0000u, 0xFEFCu, true, 4, true, true>;
+            }
             return rl == 8 ? hmm_forward_packed<0x0000u, 0xEEECu, true, 8>
                  : rl == 6 ? hmm_forward_packed<0x0000u, 0xEEECu, true, 6> : hmm_forward_packed<0x0000u, 0xEEECu, true, 4>;
         }

@@ -200,15 +200,17 @@ def test_kernel_layout_variants_agree_with_oracle(native, oracle_mod, monkeypatc
     settings = ([{"PARPY_B200_FWD_SPLIT": "0"}]
                 + [{"PARPY_B200_FWD_PACKED": "0", "PARPY_B200_FWD_POLY": str(n)} for n in (0, 4, 5, 6, 8)]
                 + [{"PARPY_B200_FWD_POLY": str(n)} for n in (0, 5, 8, 9, 10, 11, 12)]
-                # default layout (upper layers and transition columns in tensor memory, logarithm of 11
-                # layers as polynomial) with 4 (default), 6 and 8 layers in registers; other masks; the same
-                # kernels with shared memory in place of tensor memory
-                + [{}, {"PARPY_B200_FWD_REGLAYERS": "6"}, {"PARPY_B200_FWD_REGLAYERS": "8"},
+                # default layout (upper layers and transition columns in tensor memory, finite arithmetic,
+                # logarithm of 13 layers as degree-5 polynomial); the degree-6 polynomial on 11 layers; the
+                # kernels that compute on -inf itself with 4, 6 and 8 layers in registers; other masks; the
+                # same kernels with shared memory in place of tensor memory
+                + [{}, {"PARPY_B200_FWD_LG6": "0"}, {"PARPY_B200_FWD_LG6": "1", "PARPY_B200_FWD_MASKS": "0:FFFE"},
+                   {"PARPY_B200_FWD_FINITE": "0"}, {"PARPY_B200_FWD_MASKS": "0:AAAA"}, {"PARPY_B200_FWD_REGLAYERS": "6"}, {"PARPY_B200_FWD_REGLAYERS": "8"},
                    {"PARPY_B200_FWD_MASKS": "0:EEEE"}, {"PARPY_B200_FWD_MASKS": "5554:0", "PARPY_B200_FWD_REGLAYERS": "4"},
                    {"PARPY_B200_FWD_TMEM": "0"}, {"PARPY_B200_FWD_TMEM": "0", "PARPY_B200_FWD_MASKS": "0:FFFF"},
                    {"PARPY_B200_FWD_TMEM": "0", "PARPY_B200_FWD_MASKS": "5554:AAAA"}])
     knobs = ("PARPY_B200_FWD_SPLIT", "PARPY_B200_FWD_POLY", "PARPY_B200_FWD_PACKED", "PARPY_B200_FWD_TMEM",
-             "PARPY_B200_FWD_MASKS", "PARPY_B200_FWD_REGLAYERS")
+             "PARPY_B200_FWD_MASKS", "PARPY_B200_FWD_REGLAYERS", "PARPY_B200_FWD_LG6", "PARPY_B200_FWD_FINITE")
     for env in settings:
         for k in knobs:
             monkeypatch.delenv(k, raising=False)
@@ -225,7 +227,8 @@ def test_kernel_layout_variants_agree_with_oracle(native, oracle_mod, monkeypatc
     seqs = synthetic.hmm_sequences(9, 2, 120, seed=8)
     exp, exp_alpha = oracle_mod.forward(hmm, seqs, want_alpha=True)
     dh, ds = to_dev(hmm), to_dev(seqs)
-    for env in ([{"PARPY_B200_FWD_PACKED": "0"}] + [{"PARPY_B200_FWD_POLY": str(n)} for n in (0, 5, 8, 10, 12, 14, 16)]
+    for env in ([{}, {"PARPY_B200_FWD_LG6": "0"}, {"PARPY_B200_FWD_LG6": "2"}, {"PARPY_B200_FWD_FINITE": "0"},
+                 {"PARPY_B200_FWD_PACKED": "0"}] + [{"PARPY_B200_FWD_POLY": str(n)} for n in (0, 5, 8, 10, 12, 14, 16)]
                 + [{"PARPY_B200_FWD_MASKS": m} for m in ("0:EEEC", "0:FFFE", "AAAA:5554", "AAAA:5555", "0:AAAA", "8888:7776")]):
         for k in knobs:
             monkeypatch.delenv(k, raising=False)
