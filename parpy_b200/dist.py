@@ -77,18 +77,106 @@ def balanced_partition(lens, world, clusters_per_rank):
     return [np.array(sorted(b), dtype=np.int64) for b in bins]
 
 
+def pack_bins(lens, nbins, rounds=4000):
+    """Packs sequences into ``nbins`` bins so that the fullest bin is as low as a
+    local search gets it: longest-first greedy packing, then repeatedly the
+    fullest bin gives one sequence to, or exchanges one with, another bin,
+    whichever lowers the larger of the two bins most, until no such step
+    exists. This is the model of what a rank's device-side schedule does with
+    its shard (greedy + repair of the fullest bin) and, over ``world *
+    clusters`` bins, the packing the partition is cut from. Deterministic.
+    Returns (bin index of every sequence, per-bin totals)."""
+    lens, order = _longest_first(lens)
+    n = len(lens)
+    nbins = max(1, int(nbins))
+    load = np.zeros(nbins, dtype=np.int64)
+    where = np.zeros(n, dtype=np.int64)
+    heap = [(0, b) for b in range(nbins)]
+    for i in order:
+        t, b = heapq.heappop(heap)
+        where[i] = b
+        load[b] = t + int(lens[i])
+        heapq.heappush(heap, (int(load[b]), b))
+    if n == 0 or nbins == 1:
+        return where, load
+    floor = max(int(lens.max()), -(-int(lens.sum()) // nbins))   # no packing is lower than this
+    for _ in range(rounds):
+        b = int(np.argmax(load))
+        top = int(load[b])
+        if top <= floor:
+            break
+        best = (top, -1, -1)   # (larger of the two bins afterwards, sequence leaving b, sequence entering b or -1)
+        mine = np.nonzero(where == b)[0]
+        other = np.nonzero(where != b)[0]
+        c_min = int(np.argmin(np.where(np.arange(nbins) == b, np.iinfo(np.int64).max, load)))
+        for i in mine:
+            li = int(lens[i])
+            moved = max(top - li, int(load[c_min]) + li)
+            if moved < best[0]:
+                best = (moved, int(i), -1)
+            if len(other):
+                lj = lens[other]
+                after = np.maximum(top - li + lj, load[where[other]] + li - lj)
+                k = int(np.argmin(after))
+                if int(after[k]) < best[0]:
+                    best = (int(after[k]), int(i), int(other[k]))
+        if best[1] < 0:
+            break
+        i, j = best[1], best[2]
+        c = c_min if j < 0 else int(where[j])
+        load[b] -= lens[i]
+        load[c] += lens[i]
+        where[i] = c
+        if j >= 0:
+            load[c] -= lens[j]
+            load[b] += lens[j]
+            where[j] = b
+    return where, load
+
+
+def packed_partition(lens, world, clusters_per_rank):
+    """Partition cut from one packing of all sequences into ``world *
+    clusters_per_rank`` bins (:func:`pack_bins`): the bins, fullest first, are
+    dealt to the ranks in serpentine order, and a rank's shard is the union of
+    its bins. Every rank's own schedule can then reproduce bins no fuller than
+    the global packing's fullest. Returns ``world`` sorted int64 index arrays."""
+    lens = np.asarray(lens, dtype=np.int64)
+    nbins = world * int(clusters_per_rank)
+    where, load = pack_bins(lens, nbins)
+    by_load = np.lexsort((np.arange(nbins), -load))
+    rank_of_bin = np.zeros(nbins, dtype=np.int64)
+    for pos, b in enumerate(by_load):
+        lap, k = divmod(pos, world)
+        rank_of_bin[b] = k if lap % 2 == 0 else world - 1 - k
+    owner = rank_of_bin[where] if len(lens) else np.zeros(0, dtype=np.int64)
+    return [np.nonzero(owner == r)[0].astype(np.int64) for r in range(world)]
+
+
+def rank_makespan(lens, clusters):
+    """Fullest bin of :func:`pack_bins` over one rank's sequences: the number of
+    time steps its busiest resident cluster runs."""
+    lens = np.asarray(lens, dtype=np.int64)
+    if len(lens) == 0:
+        return 0
+    return int(pack_bins(lens, min(int(clusters), len(lens)))[1].max())
+
+
 def partition(lens, world, clusters_per_rank=None):
     """The sequence partition every rank derives: :func:`lpt_partition`, or, when
-    the number of resident clusters per rank is given, whichever of it and
-    :func:`balanced_partition` has the smaller largest per-cluster total over
-    all ranks (ties: LPT)."""
+    the number of resident clusters per rank is given, whichever of it,
+    :func:`balanced_partition` and :func:`packed_partition` leaves the busiest
+    cluster of any rank with the fewest time steps (ties: in that order)."""
     parts = lpt_partition(lens, world)
     if clusters_per_rank is None or world == 1:
         return parts
     lens = np.asarray(lens, dtype=np.int64)
-    alt = balanced_partition(lens, world, clusters_per_rank)
-    height = lambda ps: max(cluster_balance(lens[p], clusters_per_rank)[0] for p in ps)
-    return alt if height(alt) < height(parts) else parts
+    height = lambda ps: max(rank_makespan(lens[p], clusters_per_rank) for p in ps)
+    best, best_h = parts, height(parts)
+    for alt in (balanced_partition(lens, world, clusters_per_rank), packed_partition(lens, world, clusters_per_rank)):
+        h = height(alt)
+        if h < best_h:
+            best, best_h = alt, h
+    return best
 
 
 def shard_sequences(seqs, rank, world, clusters_per_rank=None):

@@ -57,14 +57,27 @@ def test_cluster_aware_partition_is_a_partition_and_never_worse():
     for world in (2, 4, 8):
         parts = dist.partition(lens, world, 33)
         assert sorted(np.concatenate(parts).tolist()) == list(range(500))
-        tall = lambda ps: max(dist.cluster_balance(lens[p], 33)[0] for p in ps)
-        assert tall(parts) <= tall(dist.lpt_partition(lens, world))
+        tall = lambda ps: max(dist.rank_makespan(lens[p], 33) for p in ps)
+        for other in (dist.lpt_partition(lens, world), dist.balanced_partition(lens, world, 33),
+                      dist.packed_partition(lens, world, 33)):
+            assert sorted(np.concatenate(other).tolist()) == list(range(500))
+            assert tall(parts) <= tall(other)
         # the per-cluster total cannot be below the mean, nor below the longest sequence
         assert tall(parts) >= max(lens.sum() / (33 * world), lens.max())
     # one rank: the schedule of the kernel's own queue (longest first, next free cluster)
     load = dist.cluster_schedule(np.array([5, 9, 2, 7, 3]), 2)
     assert sorted(load.tolist()) == [12, 14]          # 9+3+2 | 7+5
     assert dist.partition(lens, 1, 33)[0].tolist() == list(range(500))
+    # the packing model: greedy + repair of the fullest bin never ends above the greedy packing, keeps
+    # every sequence in exactly one bin, and reaches the floor when the floor is reachable
+    where, load = dist.pack_bins(lens, 33)
+    assert load.sum() == lens.sum() and np.array_equal(np.bincount(where, weights=lens, minlength=33), load)
+    assert load.max() <= dist.cluster_schedule(lens, 33).max()
+    where, load = dist.pack_bins(np.array([5, 9, 2, 7, 3]), 2)
+    assert sorted(load.tolist()) == [12, 14]          # no subset sums to 13
+    where, load = dist.pack_bins(np.array([8, 7, 6, 5, 4]), 2)
+    assert sorted(load.tolist()) == [15, 15]          # greedy gives 17 | 13 (8+5+4 | 7+6); one exchange evens it
+    assert dist.pack_bins(np.array([], dtype=np.int64), 4)[1].tolist() == [0, 0, 0, 0]
 
 
 def _sparse_worker(rank, world, port, out_path):
