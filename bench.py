@@ -22,7 +22,8 @@ inside the timed step.
             the CPU restatement of the reference algorithm (oracle/) on the
             host cores, on a bounded sample of the same workload
   schedule  how evenly rank 0's sequences pack onto its resident clusters
-  variants  the opt-in scaled kernel on the same batch (N = 1)
+  variants  the log-space kernel (opts.b200['forward'] = 'log_space') and the
+            explicitly requested scaled kernel on the same batch (N = 1)
   surrounding
             softmax, sum+max, CSR SpMV and SDDMM on their benchmark shapes, once
             each after the timed region (N = 1; see bench_kernels.py)
@@ -59,13 +60,13 @@ def parse_args():
     ap.add_argument("--scaling", choices=["weak", "strong"], default="strong",
                     help="strong (default): the 500-sequence batch sharded over the GPUs; "
                          "weak: 500 sequences per GPU")
-    ap.add_argument("--variant", choices=["auto", "five_term", "scaled", "streaming"], default="auto")
+    ap.add_argument("--variant", choices=["auto", "five_term", "log_space", "scaled", "streaming"], default="auto")
     ap.add_argument("--ref-cuda", action="store_true",
                     help="also time the reference's own CUDA implementation (oracle/_ref), once")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-surrounding", action="store_true",
                     help="skip the surrounding kernels (softmax, sum+max, SpMV, SDDMM) after the timed region")
-    ap.add_argument("--no-variants", action="store_true", help="skip the opt-in scaled kernel")
+    ap.add_argument("--no-variants", action="store_true", help="skip the extra runs of the log-space and scaled kernels")
     ap.add_argument("--batch", type=int, default=BATCH, help=argparse.SUPPRESS)
     ap.add_argument("--kmer", type=int, default=KMER, help=argparse.SUPPRESS)
     ap.add_argument("--min-len", type=int, default=MIN_LEN, help=argparse.SUPPRESS)
@@ -380,6 +381,9 @@ def main():
         return m["total_ms"], m["e2e_s"], float(m["work"]), float(m["bytes"])
 
     head = measure(args.scaling, args.variant, with_e2e=True)
+    status = hmm_mod.forward_status()            # read-and-clear: clamps met, bounded waits that ran out
+    if status["wait_timed_out"]:
+        raise SystemExit("a bounded wait inside the forward kernel ran out: the results are not valid")
     total_ms, e2e_s, work, nbytes = reduce_ranks(head)
     weak = None
     if world > 1 and args.scaling == "strong":
@@ -419,6 +423,10 @@ def main():
                          "note": "algorithmic bytes (8.25 B/state-step) per launch over the measured "
                                  "launch duration; alpha stays on chip, so DRAM traffic is far lower"},
             "step_ms": head["step_ms"],
+            "arithmetic": (args.variant if args.variant != "auto" else
+                           "scaled (what a call without options runs on 4096 k-mers and more)" if args.kmer >= 6
+                           else "log_space"),
+            "status": status,
             # rank 0's share on its persistent clusters: the launch lasts as long as the busiest
             # cluster's step total, the work done is the mean
             "schedule": {"resident_clusters": clusters, "sequences_rank0": head["batch"],
@@ -428,12 +436,17 @@ def main():
         if weak is not None:
             line["weak"] = weak
         if world == 1 and args.variant == "auto" and not args.no_variants:
-            sc = measure("strong", "scaled", with_e2e=False)
-            a, b = sc["result"].cpu().numpy(), head["result"].cpu().numpy()
-            line["variants"] = {"scaled": {
-                "value": sc["work"] * args.steps / (sc["total_ms"] * 1e-3), "ms_per_step": sc["total_ms"] / args.steps,
-                "max_rel_vs_default": float(abs((a - b) / b).max()),
-                "what": "opt-in linear-domain kernel (opts.b200['forward'] = 'scaled'), same batch"}}
+            b = head["result"].cpu().numpy()
+            line["variants"] = {}
+            for name, what in (("log_space", "log-space kernel (opts.b200['forward'] = 'log_space'), same batch"),
+                               ("scaled", "linear-domain kernel requested explicitly (opts.b200['forward'] = "
+                                          "'scaled'; what a call without options runs on this state space)")):
+                sc = measure("strong", name, with_e2e=False)
+                a = sc["result"].cpu().numpy()
+                line["variants"][name] = {
+                    "value": sc["work"] * args.steps / (sc["total_ms"] * 1e-3),
+                    "ms_per_step": sc["total_ms"] / args.steps,
+                    "max_rel_vs_default": float(abs((a - b) / b).max()), "what": what}
         if world == 1 and not args.no_cpu_baseline:
             cores = host_cores()
             sub, desc = cpu_sample(hmm, all_seqs, cores)
@@ -456,18 +469,18 @@ def main():
         td.destroy_process_group()
 
 
-# One ncu capture of hmm_forward_packed<0x5554> (66 sequences of 200-400 steps, --set full,
-# summary under profiles/) measured dram__bytes_read.sum = 7,994,000 B and
-# dram__bytes_write.sum = 0 B for 7,956,782 B of inputs (tables + observations + lengths): the
-# kernel reads its inputs from DRAM once and keeps alpha on chip, so DRAM traffic follows the
-# input size, not the step count.
-NCU_DRAM_BYTES_PER_INPUT_BYTE = 7994000.0 / 7956782.0
+# ncu captures (--set full, 66 sequences of 200-400 steps) of the resident kernels measured
+# dram__bytes_read.sum = 8.00 MB and dram__bytes_write.sum = 0 B per launch for 7,956,782 B of inputs
+# (tables + observations + lengths), the same for the scaled and the log-space kernel: a launch reads
+# its inputs from DRAM once and keeps alpha on chip, so DRAM traffic follows the input size, not
+# the step count.
+NCU_DRAM_BYTES_PER_INPUT_BYTE = 8000000.0 / 7956782.0
 
 
 def ncu_traffic_bytes(args, input_bytes):
     """DRAM bytes per launch of the resident kernel, scaled from the committed
     ncu capture by input bytes; None for variants that were not captured."""
-    if args.variant != "auto" or args.kmer != 7:
+    if args.variant not in ("auto", "scaled", "log_space") or args.kmer != 7:
         return None
     return NCU_DRAM_BYTES_PER_INPUT_BYTE * input_bytes
 

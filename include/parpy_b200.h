@@ -80,7 +80,13 @@ int32_t forward_kernel_scratch_first(float gamma, float *initial_prob, int64_t n
                                      int64_t num_instances, float *alpha1,
                                      float *alpha2, float *result);
 
-/* Option flags of parpy_b200_forward. */
+/* Option flags of parpy_b200_forward. Without SCALED, LOG_SPACE, FIVE_TERM,
+ * STREAMING or WRITE_ALPHA the library picks the arithmetic by state space:
+ * scaled for 4096 k-mers and more (6-mer and up), log space below that, where
+ * the reference ships golden vectors that its own test compares at rtol 1e-5
+ * with fp32 log-space results. forward_kernel and
+ * forward_kernel_scratch_first follow the same rule. The environment variable
+ * PARPY_B200_FWD_DEFAULT=log makes log space the rule everywhere. */
 #define PARPY_B200_FWD_AUTO 0u
 /* Force the streaming kernel: alpha ping-pongs through alpha1/alpha2 in global
  * memory, one launch per time step, the reference's five-term log-sum-exp in
@@ -99,8 +105,15 @@ int32_t forward_kernel_scratch_first(float gamma, float *initial_prob, int64_t n
  * with a per-thread base-2 exponent (extended-range linear arithmetic) instead of
  * on log-probabilities. Mathematically the same quantity; rounding differs: this
  * form agrees with a float64 evaluation to ~1e-8 relative, while fp32 log space
- * (the reference's arithmetic) is itself 1e-6..1e-4 away from float64. */
+ * (the reference's arithmetic) is itself 1e-6..1e-4 away from float64. States
+ * more than 2^-126 below the largest of their thread's 64 states count as log 0
+ * (visible only in alpha written with WRITE_ALPHA). Its layer-0 exchange waits on
+ * mbarriers with a bounded number of polls; a wait that runs out raises bit 2 of
+ * the status word (parpy_b200_forward_status). */
 #define PARPY_B200_FWD_SCALED 8u
+/* Resident kernel: evaluate on log-probabilities (the factored log-sum-exp form)
+ * whatever the library's default for the state space is. */
+#define PARPY_B200_FWD_LOG_SPACE 16u
 
 /* Same computation as forward_kernel with explicit options. `trans2` is a
  * DEVICE pointer to 16 floats like everywhere else. `stream` is a
@@ -164,7 +177,8 @@ int32_t parpy_b200_forward_status(uint32_t *status);
  * a plugin host that forbids allocation inside its execute callback.
  * parpy_b200_forward may grow the library's scheduling scratch with cudaMalloc
  * on its first call or when the batch grows; this entry never does. It computes
- * the same result[] (resident kernel, factored log-sum-exp, alpha kept on chip)
+ * result[] with the resident log-space kernel (factored log-sum-exp, alpha kept on
+ * chip: what parpy_b200_forward runs with PARPY_B200_FWD_LOG_SPACE, bit for bit)
  * with its scheduling scratch — the length-sorted sequence order and the work-
  * queue head — in a fixed device array compiled into the library, of
  * 4 * PARPY_B200_NOALLOC_MAX_SEQUENCES + 2560 bytes on every GPU that loads the

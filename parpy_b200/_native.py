@@ -82,6 +82,7 @@ FWD_STREAMING = 1
 FWD_WRITE_ALPHA = 2
 FWD_FIVE_TERM = 4
 FWD_SCALED = 8
+FWD_LOG_SPACE = 16
 
 
 class NativeLibraryMissing(RuntimeError):

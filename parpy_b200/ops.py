@@ -125,9 +125,11 @@ def _forward_flags(opts):
         flags |= _native.FWD_FIVE_TERM
     elif mode == "scaled":
         flags |= _native.FWD_SCALED
+    elif mode == "log_space":
+        flags |= _native.FWD_LOG_SPACE
     elif mode != "auto":
-        raise RuntimeError("opts.b200['forward'] must be 'auto', 'five_term', 'scaled' or 'streaming', "
-                           f"got {mode!r}")
+        raise RuntimeError("opts.b200['forward'] must be 'auto', 'five_term', 'log_space', 'scaled' or "
+                           f"'streaming', got {mode!r}")
     if b.get("write_alpha", False):
         flags |= _native.FWD_WRITE_ALPHA
     return flags

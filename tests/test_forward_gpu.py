@@ -19,7 +19,7 @@ pytestmark = pytest.mark.gpu
 
 REL_TARGET = 1e-4        # library target vs the reference
 REL_ORACLE = 1e-5        # kernel vs fp32 CPU oracle on identical inputs
-FLAGS = {"factored": 0, "five_term": 4, "streaming": 1, "scaled": 8}
+FLAGS = {"factored": 0, "five_term": 4, "streaming": 1, "scaled": 8, "log_space": 16}
 
 
 @pytest.fixture(scope="module")
@@ -87,39 +87,42 @@ def test_7mer_against_oracle_with_final_alpha(native, oracle_mod):
             assert not other.any()
 
 
-def test_7mer_full_config_properties(native):
-    # 7mer benchmark workload: 500 sequences, lengths uniform in [1000, 4000]; size-independent checks.
+@pytest.mark.parametrize("arith", ["default", "log_space"])
+def test_7mer_full_config_properties(native, arith):
+    # 7mer benchmark workload: 500 sequences, lengths uniform in [1000, 4000]; size-independent checks,
+    # for the default (scaled arithmetic on this state space) and for the log-space kernel.
     from parpy_b200 import synthetic
     hmm = synthetic.hmm_model(7)
     seqs = synthetic.hmm_sequences(500, 1000, 4000)
     dh, ds = to_dev(hmm), to_dev(seqs)
-    rc, res, _, _ = cabi_forward(native, dh, ds)
+    fl = FLAGS["log_space"] if arith == "log_space" else 0
+    rc, res, _, _ = cabi_forward(native, dh, ds, fl)
     assert rc == 0, native.error_message()
     full = res.cpu().numpy()
     assert np.isfinite(full).all() and (full < 0).all()
     # determinism: a second run is bit-identical
-    rc, res2, _, _ = cabi_forward(native, dh, ds)
+    rc, res2, _, _ = cabi_forward(native, dh, ds, fl)
     assert np.array_equal(full, res2.cpu().numpy())
     # permutation / batch-composition invariance: every sequence is scored independently
     perm = torch.randperm(500, generator=torch.Generator().manual_seed(5))[:97]
     sub = {"data": seqs["data"][perm].contiguous(), "lens": seqs["lens"][perm].contiguous(),
            "maxlen": seqs["maxlen"], "num_instances": torch.tensor(97)}
-    rc, res3, _, _ = cabi_forward(native, dh, to_dev(sub))
+    rc, res3, _, _ = cabi_forward(native, dh, to_dev(sub), fl)
     assert rc == 0
     assert np.array_equal(res3.cpu().numpy(), full[perm.numpy()])
     # a prefix is at least as likely as the whole sequence (all emissions are log-probabilities)
     half = dict(sub)
     half["lens"] = (sub["lens"] // 2).contiguous()
-    rc, res4, _, _ = cabi_forward(native, dh, to_dev(half))
+    rc, res4, _, _ = cabi_forward(native, dh, to_dev(half), fl)
     assert (res4.cpu().numpy() >= res3.cpu().numpy()).all()
-    # the five-term form agrees with the factored form far inside the tolerance
+    # the five-term form agrees with this arithmetic far inside the tolerance
     rc, res5, _, _ = cabi_forward(native, dh, to_dev(sub), FLAGS["five_term"])
     assert max_rel(res3.cpu().numpy(), res5.cpu().numpy()) <= REL_ORACLE
 
 
 def test_7mer_benchmark_batch_full_length_against_oracle(native, oracle_mod, capsys):
     # The benchmark's own batch (500 sequences, lengths uniform in [1000, 4000], seed 1234) through
-    # the default kernel; the longest, the shortest and six more sequences are scored at full length
+    # the default kernel (the scaled one on this state space); the longest, the shortest and six more sequences are scored at full length
     # by the CPU oracle (benchmarks/forward.py:103-158 restated). fp32 log-space rounding drifts with
     # length, so this is the check at the lengths the throughput figure is quoted on. Tolerance of
     # the reference's own test: test/test_forward.py:176-178 (rtol 1e-5).
@@ -141,14 +144,17 @@ def test_7mer_benchmark_batch_full_length_against_oracle(native, oracle_mod, cap
     assert np.isfinite(got).all()
     err = {"default": max_rel(got[pick], exp)}
     ds = to_dev(sub)
-    for name in ("five_term", "scaled"):
+    for name in ("log_space", "five_term", "scaled"):
         rc, r, _, _ = cabi_forward(native, dh, ds, FLAGS[name])
         assert rc == 0, native.error_message()
         err[name] = max_rel(r.cpu().numpy(), exp)
+        if name == "scaled":     # what a call without flags runs on this state space
+            assert np.array_equal(r.cpu().numpy(), got[pick])
     with capsys.disabled():
         print("\n7mer full-length parity (max rel vs oracle, lengths %d..%d): %s"
               % (lens[pick].min(), lens[pick].max(), ", ".join(f"{k} {v:.2e}" for k, v in err.items())))
     assert err["default"] <= REL_ORACLE
+    assert err["log_space"] <= REL_ORACLE
     assert err["five_term"] <= REL_ORACLE
     # the scaled kernel follows exact arithmetic; its distance from the fp32 oracle is the
     # oracle's own accumulated rounding, which the library target bounds
@@ -265,11 +271,12 @@ def test_packed_arithmetic_is_bit_identical_to_scalar(native, monkeypatch):
 
 
 def test_scaled_variant_against_golden_oracle_and_log_space(native, oracle_mod):
-    # Opt-in extended-range linear arithmetic (PARPY_B200_FWD_SCALED). It tracks a float64
+    # Extended-range linear arithmetic (PARPY_B200_FWD_SCALED). It tracks a float64
     # evaluation to ~1e-8, so its distance from the reference's fp32 golden vectors is the
     # golden vectors' own rounding: 1.5e-5 at worst on the 5mer fixture (read 79), which is inside
     # the library target of 1e-4 but outside the reference test's rtol of 1e-5; that is why it is
-    # not the default.
+    # the default only for state spaces larger than the ones the reference ships golden vectors
+    # for (4096 k-mers and more), and opt-in here.
     hmm, seqs, exp = to_dev(load_model("5mer")), to_dev(load_signals()), load_expected("5mer")
     rc, res, _, _ = cabi_forward(native, hmm, seqs, FLAGS["scaled"])
     assert rc == 0, native.error_message()
@@ -304,6 +311,31 @@ def test_scaled_variant_against_golden_oracle_and_log_space(native, oracle_mod):
     rc, _, _, _ = cabi_forward(native, to_dev(load_model("3mer")), to_dev(load_signals(shortest_reads(2))),
                                FLAGS["scaled"])
     assert rc != 0 and "scaled kernel needs" in native.error_message()
+
+
+def test_default_arithmetic_by_state_space(native, monkeypatch):
+    # Without flags: scaled arithmetic for 4096 k-mers and more, log space below that and whenever
+    # alpha is asked for; PARPY_B200_FWD_DEFAULT=log and the LOG_SPACE flag give log space everywhere.
+    from parpy_b200 import synthetic
+    monkeypatch.delenv("PARPY_B200_FWD_DEFAULT", raising=False)
+    for k, scaled_default in ((5, False), (6, True), (7, True)):
+        hmm, seqs = to_dev(synthetic.hmm_model(k, seed=40 + k)), to_dev(synthetic.hmm_sequences(7, 2, 70, seed=50 + k))
+        out = {}
+        for name, flags in (("none", 0), ("log", FLAGS["log_space"]), ("scaled", FLAGS["scaled"])):
+            rc, res, _, _ = cabi_forward(native, hmm, seqs, flags)
+            assert rc == 0, native.error_message()
+            out[name] = res.cpu().numpy()
+        assert not np.array_equal(out["log"], out["scaled"])          # different rounding somewhere
+        assert np.array_equal(out["none"], out["scaled" if scaled_default else "log"])
+        assert max_rel(out["scaled"], out["log"]) <= REL_ORACLE
+        rc, res, a1, a2 = cabi_forward(native, hmm, seqs, 2, alpha=True)     # alpha requested: log space
+        assert rc == 0 and np.array_equal(res.cpu().numpy(), out["log"])
+        monkeypatch.setenv("PARPY_B200_FWD_DEFAULT", "log")
+        rc, res, _, _ = cabi_forward(native, hmm, seqs)
+        assert rc == 0 and np.array_equal(res.cpu().numpy(), out["log"])
+        monkeypatch.delenv("PARPY_B200_FWD_DEFAULT")
+    rc, _, _, _ = cabi_forward(native, hmm, seqs, FLAGS["log_space"] | FLAGS["scaled"])
+    assert rc != 0 and "exclude each other" in native.error_message()
 
 
 @pytest.mark.parametrize("k,nseq,lo,hi", [(7, 40, 30, 400), (6, 50, 1, 300)])
@@ -344,7 +376,7 @@ def test_8mer_runs_on_a_16_cta_cluster(native, oracle_mod):
     hmm = synthetic.hmm_model(8, seed=8)
     seqs = synthetic.hmm_sequences(3, 1, 16, seed=9)
     exp = oracle_mod.forward(hmm, seqs)
-    for flags in (0, FLAGS["scaled"]):
+    for flags in (0, FLAGS["log_space"], FLAGS["scaled"]):
         rc, res, _, _ = cabi_forward(native, to_dev(hmm), to_dev(seqs), flags)
         assert rc == 0, native.error_message()
         assert max_rel(res.cpu().numpy(), exp) <= REL_ORACLE
@@ -661,17 +693,18 @@ def test_static_schedule_is_a_partition_and_beats_greedy_packing(native, batch, 
 def test_results_do_not_depend_on_the_number_of_resident_clusters(native, monkeypatch):
     from parpy_b200 import synthetic
     hmm, seqs = to_dev(synthetic.hmm_model(6, seed=2)), to_dev(synthetic.hmm_sequences(90, 1, 50, seed=3))
-    rc, base, _, _ = cabi_forward(native, hmm, seqs)
-    assert rc == 0, native.error_message()
+    base = {}
+    for flags in (0, FLAGS["log_space"], FLAGS["scaled"]):
+        rc, base[flags], _, _ = cabi_forward(native, hmm, seqs, flags)
+        assert rc == 0, native.error_message()
+    assert torch.equal(base[0], base[FLAGS["scaled"]])          # the default for 4096 k-mers and more
+    assert max_rel(base[0].cpu().numpy(), base[FLAGS["log_space"]].cpu().numpy()) <= REL_ORACLE
     for n in ("1", "2", "7"):
         monkeypatch.setenv("PARPY_B200_FWD_CLUSTERS", n)
-        for flags in (0, FLAGS["scaled"]):
+        for flags in base:
             rc, res, _, _ = cabi_forward(native, hmm, seqs, flags)
             assert rc == 0, native.error_message()
-            if flags == 0:
-                assert torch.equal(res, base)
-            else:
-                assert max_rel(res.cpu().numpy(), base.cpu().numpy()) <= REL_TARGET
+            assert torch.equal(res, base[flags])
 
 
 def test_out_of_range_observations_are_clamped_and_flagged(native):

@@ -63,6 +63,8 @@ def test_noalloc_forward_7mer_cluster_path(native):
     rc2, ref, _, _ = cabi_forward(native, hmm, seqs)
     assert rc2 == 0
     assert max_rel(got.cpu().numpy(), ref.cpu().numpy()) <= REL
+    rc3, ref_log, _, _ = cabi_forward(native, hmm, seqs, 16)      # PARPY_B200_FWD_LOG_SPACE: the same kernel
+    assert rc3 == 0 and np.array_equal(got.cpu().numpy(), ref_log.cpu().numpy())
 
 
 def test_noalloc_forward_rejects_what_it_cannot_hold(native):
