@@ -178,7 +178,7 @@ __device__ __forceinline__ unsigned long long warp_min_u64(unsigned long long v)
 
 __global__ void __launch_bounds__(1024, 1)
 hmm_schedule(const int64_t *__restrict__ lens, int B, int C, int *__restrict__ order,
-             int *__restrict__ counter, int *__restrict__ seg, int *__restrict__ cluster_of) {
+             int *__restrict__ counter, int *__restrict__ seg, int *__restrict__ cluster_of, int max_rounds) {
     extern __shared__ int s_dyn[];                       // [B] lengths by rank, then two u16 arrays
     __shared__ long long s_load[kMaxBins];
     __shared__ int s_cnt[kMaxBins + 1];
@@ -266,7 +266,7 @@ hmm_schedule(const int64_t *__restrict__ lens, int B, int C, int *__restrict__ o
         // a round costs about as much as a time step of a small model: spend at most an eighth of
         // the steps that perfect balance could save
         const long long gap = top - total / C;
-        budget = static_cast<int>(gap / 8 < 512 ? gap / 8 : 512);
+        budget = static_cast<int>(gap / 8 < max_rounds ? gap / 8 : max_rounds);
     }
     for (int it = 0; it < budget; ++it) {
         if (warp == 0) {
@@ -2036,10 +2036,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_tmem(const FwdPara
             o_next = obs_at(p, obs, t + 1 < T_len ? t + 1 : T_len - 1, bad_obs);
             // the transition columns, in flight while the exchange completes
             float4 t0, t1, t2, t3;
-            tmem_ld4(tm + 4 * (kLayers - RL), t0);
-            tmem_ld4(tm + 4 * (kLayers - RL) + 4, t1);
-            tmem_ld4(tm + 4 * (kLayers - RL) + 8, t2);
-            tmem_ld4(tm + 4 * (kLayers - RL) + 12, t3);
+            tmem_ld16(tm + 4 * (kLayers - RL), t0, t1, t2, t3);
 
             const unsigned buf = (unsigned)(t - 1) % NB;   // buffer that holds the previous step's layer 0
             receive(buf);
@@ -2074,6 +2071,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_tmem(const FwdPara
                 QE[1] = mul2(q1, el2[1]);
                 Eo[0] = mul2(el2[0], own);
                 Eo[1] = mul2(el2[1], own);
+                kt = exponent_of(max3(fmaxf(el2[0].x, el2[0].y), el2[1].x, el2[1].y)) + 4;   // the bound; see below
             }
             // layer 0 first: it is what the other CTAs wait for
             // exp(trans2) of four layers per shared-memory load (the shared-memory pipe bounds this kernel)
@@ -2085,54 +2083,98 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_tmem(const FwdPara
                 x[0][1] = fma2(a, QE[1], mul2(Eo[1], x[1][1]));
             }
             send((unsigned)t % NB, x[0][0].x, x[0][0].y, x[0][1].x, x[0][1].y, Wn);
-            float m = max3(fmaxf(x[0][0].x, x[0][0].y), x[0][1].x, x[0][1].y);
 #pragma unroll
             for (int d = 1; d < RL - 1; ++d) {
                 if (d % 4 == 0) a4 = s_A4[d / 4];
                 const float2 a = A_of(d);
                 x[d][0] = fma2(a, QE[0], mul2(Eo[0], x[d + 1][0]));
                 x[d][1] = fma2(a, QE[1], mul2(Eo[1], x[d + 1][1]));
-                m = max3(m, x[d][0].x, x[d][0].y);
-                m = max3(m, x[d][1].x, x[d][1].y);
             }
-            float4 nxt, nxt2;   // old values of the next layer, fetched one layer ahead
-            tmem_ld4(tm, nxt);      // layer 8 (old)
-            tmem_wait_ld(nxt);
-            tmem_ld4(tm + 4, nxt2); // layer 9 (old)
+            // Layers RL..15 live in tensor memory and are updated in place, two layers per load and per
+            // store: pair p = layers (d, d + 1), d = RL + 2p, needs the old values of layers d + 1 and
+            // d + 2 (the last pair: old layer 15 twice), which one 8-column load brings; the results
+            // replace them in the same registers and leave with one 8-column store. The operands of
+            // pair p + 1 are requested as soon as those of pair p have arrived (a wait covers every
+            // load in flight), so they travel while pair p is computed; a load never covers columns
+            // that a store issued before its wait writes.
+            constexpr int NP = (kLayers - RL) / 2;
+            float4 o0, pr[2][2];
+            tmem_ld4(tm, o0);                       // old layer RL, for the last register layer
+            if (NP > 1) tmem_ld8(tm + 4, pr[0][0], pr[0][1]);
+            else tmem_ld4(tm + 4, pr[0][0]);
+            if (NP > 1) tmem_wait_ld(o0, pr[0][0], pr[0][1]);
+            else tmem_wait_ld(o0, pr[0][0]);
+            if (NP > 2) tmem_ld8(tm + 4 * 3, pr[1][0], pr[1][1]);
+            else if (NP == 2) tmem_ld4(tm + 4 * 3, pr[1][0]);
             {
                 const float2 a = A_of(RL - 1);
-                x[RL - 1][0] = fma2(a, QE[0], mul2(Eo[0], make_float2(nxt.x, nxt.y)));
-                x[RL - 1][1] = fma2(a, QE[1], mul2(Eo[1], make_float2(nxt.z, nxt.w)));
-                m = max3(m, x[RL - 1][0].x, x[RL - 1][0].y);
-                m = max3(m, x[RL - 1][1].x, x[RL - 1][1].y);
+                x[RL - 1][0] = fma2(a, QE[0], mul2(Eo[0], make_float2(o0.x, o0.y)));
+                x[RL - 1][1] = fma2(a, QE[1], mul2(Eo[1], make_float2(o0.z, o0.w)));
             }
 #pragma unroll
-            for (int d = RL; d < kLayers; ++d) {
-                // old value of layer min(d+1, 15); layers 14 and 15 both read old layer 15. Layer d + 1
-                // was requested during layer d - 1; layer d + 2 is requested now, before layer d is
-                // written (a load has completed before anything overwrites its columns).
-                if (d < kLayers - 1) {
-                    float4 &cur = (d & 1) ? nxt : nxt2, &ahead = (d & 1) ? nxt2 : nxt;
-                    tmem_wait_ld(cur);
-                    if (d + 2 < kLayers) tmem_ld4(tm + 4 * (d + 2 - RL), ahead);
+            for (int pp = 0; pp < NP; ++pp) {
+                float4 (&b)[2] = pr[pp & 1];
+                const bool last = pp == NP - 1;
+                if (pp > 0) {
+                    if (last) tmem_wait_ld(b[0]);
+                    else tmem_wait_ld(b[0], b[1]);
+                    if (pp + 2 < NP) tmem_ld8(tm + 4 * (2 * pp + 3), pr[(pp + 1) & 1][0], pr[(pp + 1) & 1][1]);
+                    else if (pp + 2 == NP) tmem_ld4(tm + 4 * (2 * pp + 3), pr[(pp + 1) & 1][0]);
                 }
-                const float4 &old = (d < kLayers - 1) ? ((d & 1) ? nxt : nxt2) : ((d & 1) ? nxt2 : nxt);
-                float2 v0 = make_float2(old.x, old.y), v1 = make_float2(old.z, old.w);
-                if (d >= 14) {
-                    const float c = d == 15 ? p.gamma_lin : p.synthetic_lin;
-                    v0.x *= c; v0.y *= c; v1.x *= c; v1.y *= c;
+                const int d = RL + 2 * pp;
+                if (d % 4 == 0) a4 = s_A4[d / 4];   // RL is even: a pair never straddles a group of four
+                // second layer of the pair first: in the last pair both read old layer 15 (b[0])
+                {
+                    const float4 &old = last ? b[0] : b[1];
+                    float2 v0 = make_float2(old.x, old.y), v1 = make_float2(old.z, old.w);
+                    if (last) {
+                        const float c = p.gamma_lin;
+                        v0.x *= c; v0.y *= c; v1.x *= c; v1.y *= c;
+                    }
+                    const float2 a = A_of(d + 1);
+                    const float2 r0 = fma2(a, QE[0], mul2(Eo[0], v0));
+                    const float2 r1 = fma2(a, QE[1], mul2(Eo[1], v1));
+                    b[1] = make_float4(r0.x, r0.y, r1.x, r1.y);
                 }
-                if (d % 4 == 0) a4 = s_A4[d / 4];
-                const float2 a = A_of(d);
-                const float2 r0 = fma2(a, QE[0], mul2(Eo[0], v0));
-                const float2 r1 = fma2(a, QE[1], mul2(Eo[1], v1));
-                tmem_st4(tm + 4 * (d - RL), make_float4(r0.x, r0.y, r1.x, r1.y));
-                m = max3(m, r0.x, r0.y);
-                m = max3(m, r1.x, r1.y);
+                {
+                    float2 v0 = make_float2(b[0].x, b[0].y), v1 = make_float2(b[0].z, b[0].w);
+                    if (last) {
+                        const float c = p.synthetic_lin;
+                        v0.x *= c; v0.y *= c; v1.x *= c; v1.y *= c;
+                    }
+                    const float2 a = A_of(d);
+                    const float2 r0 = fma2(a, QE[0], mul2(Eo[0], v0));
+                    const float2 r1 = fma2(a, QE[1], mul2(Eo[1], v1));
+                    b[0] = make_float4(r0.x, r0.y, r1.x, r1.y);
+                }
+                tmem_st8(tm + 4 * (2 * pp), b[0], b[1]);
             }
-            kt = exponent_of(m);
             W = Wn;
             tmem_wait_st();   // the next step reads what this one stored
+            // The thread's exponent for the next step follows the largest of its 64 new mantissas. Every
+            // fourth step (and the last two, so that a sequence ends on the exponents the exact maximum
+            // gives) finds it; the steps between use a bound instead: inputs are
+            // below 2 after rescaling, so with transition and duration factors of at most 1 a new value
+            // is below 10 x the largest emission factor. The bound only has to hold loosely (fp32 has
+            // 2^127 of headroom and the true maximum follows within three steps), and power-of-two
+            // rescaling is exact: the values represented do not depend on which exponent was chosen.
+            if ((t & 3) == 0 || t >= T_len - 2) {
+                float m = 0.0f;
+#pragma unroll
+                for (int d = 0; d < RL; ++d) {
+                    m = max3(m, x[d][0].x, x[d][0].y);
+                    m = max3(m, x[d][1].x, x[d][1].y);
+                }
+#pragma unroll
+                for (int d = 0; d < kLayers - RL; d += 2) {
+                    float4 u, v;
+                    tmem_ld8(tm + 4 * d, u, v);
+                    tmem_wait_ld(u, v);
+                    m = max3(m, fmaxf(u.x, u.y), fmaxf(u.z, u.w));
+                    m = max3(m, fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+                }
+                kt = exponent_of(m);
+            }
         }
         receive((unsigned)(T_len - 1) % NB);   // the last round is not used, but it must have landed
 
@@ -2553,8 +2595,10 @@ int32_t launch_schedule(FwdParams *p, const SchedScratch &sc, int clusters, int 
     p->counter = sc.counter;
     p->seg = fixed ? sc.seg : nullptr;
     const size_t smem = fixed ? size_t(p->B) * 8 : 0;
+    int max_rounds = 512;   // repair rounds at most
+    if (const char *env = getenv("PARPY_B200_SCHED_ROUNDS")) max_rounds = atoi(env);
     hmm_schedule<<<1, 1024, smem, stream>>>(p->lens, p->B, fixed ? clusters : 0, sc.order, sc.counter, sc.seg,
-                                             cluster_of);
+                                             cluster_of, max_rounds);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }

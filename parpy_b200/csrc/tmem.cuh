@@ -37,6 +37,20 @@ __device__ __forceinline__ void tmem_st4(unsigned taddr, const float4 &v) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};"
                  ::"r"(taddr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
+// Eight and sixteen consecutive columns with one instruction.
+__device__ __forceinline__ void tmem_ld8(unsigned taddr, float4 &a, float4 &b) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w), "=f"(b.x), "=f"(b.y), "=f"(b.z), "=f"(b.w) : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st8(unsigned taddr, const float4 &a, const float4 &b) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"r"(taddr), "f"(a.x), "f"(a.y), "f"(a.z), "f"(a.w), "f"(b.x), "f"(b.y), "f"(b.z), "f"(b.w) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(unsigned taddr, float4 &a, float4 &b, float4 &c, float4 &d) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w), "=f"(b.x), "=f"(b.y), "=f"(b.z), "=f"(b.w),
+                   "=f"(c.x), "=f"(c.y), "=f"(c.z), "=f"(c.w), "=f"(d.x), "=f"(d.y), "=f"(d.z), "=f"(d.w) : "r"(taddr));
+}
 __device__ __forceinline__ void tmem_ld2(unsigned taddr, float2 &v) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(taddr));
 }
@@ -51,6 +65,15 @@ __device__ __forceinline__ void tmem_wait_ld(float2 &a) {
 }
 __device__ __forceinline__ void tmem_wait_ld(float4 &a) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" : "+f"(a.x), "+f"(a.y), "+f"(a.z), "+f"(a.w)::"memory");
+}
+__device__ __forceinline__ void tmem_wait_ld(float4 &a, float4 &b) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+f"(a.x), "+f"(a.y), "+f"(a.z), "+f"(a.w), "+f"(b.x), "+f"(b.y), "+f"(b.z), "+f"(b.w)::"memory");
+}
+__device__ __forceinline__ void tmem_wait_ld(float4 &a, float4 &b, float4 &c) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+f"(a.x), "+f"(a.y), "+f"(a.z), "+f"(a.w), "+f"(b.x), "+f"(b.y), "+f"(b.z), "+f"(b.w),
+                   "+f"(c.x), "+f"(c.y), "+f"(c.z), "+f"(c.w)::"memory");
 }
 __device__ __forceinline__ void tmem_wait_ld(float4 &a, float4 &b, float4 &c, float4 &d) {
     asm volatile("tcgen05.wait::ld.sync.aligned;"
