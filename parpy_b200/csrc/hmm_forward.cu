@@ -1053,12 +1053,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
             if constexpr (FIN) e = clamp_log_zero(e);
             const float2 ev[2] = {make_float2(e.x, e.y), make_float2(e.z, e.w)};
             float4 t0, t1, t2, t3;   // transition columns
-            if constexpr (TMEM) {    // in flight while the exchange completes
-                tmem_ld4(tm + 4 * (kLayers - RL), t0);
-                tmem_ld4(tm + 4 * (kLayers - RL) + 4, t1);
-                tmem_ld4(tm + 4 * (kLayers - RL) + 8, t2);
-                tmem_ld4(tm + 4 * (kLayers - RL) + 12, t3);
-            }
+            if constexpr (TMEM) tmem_ld16(tm + 4 * (kLayers - RL), t0, t1, t2, t3);   // in flight while the exchange completes
 
             cluster_wait();
             const float *seg = a0s + (buf ? 4 * M : 0) + tid;
@@ -1092,15 +1087,64 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
                 for (int h = 0; h < 2; ++h)
                     a[d][h] = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[h]), a[d + 1][h], ((LG_MASK >> d) & 1u) != 0, FIN, LG6), ev[h]);
             }
-            // layers 7..15: the "next layer" operand comes from shared memory
-            float4 nxt, nxt2;   // TMEM: old values of the next layer, requested one layer ahead
             if constexpr (TMEM) {
-                tmem_ld4(tm, nxt);       // layer 8 (old)
-                tmem_wait_ld(nxt);
-                tmem_ld4(tm + 4, nxt2);  // layer 9 (old)
+                // Layers RL..15 live in tensor memory and are updated in place, two layers per load and
+                // per store: pair p = layers (d, d + 1), d = RL + 2p, needs the old values of layers
+                // d + 1 and d + 2 (the last pair: old layer 15 twice), which one 8-column load brings;
+                // the results replace them in the same registers and leave with one 8-column store.
+                // The operands of pair p + 1 are requested as soon as those of pair p have arrived (a
+                // wait covers every load in flight), so they travel while pair p is computed; a load
+                // never covers columns that a store issued before its wait writes.
+                constexpr int NP = (kLayers - RL) / 2;
+                float4 o0, pr[2][2];
+                tmem_ld4(tm, o0);                       // old layer RL, for the last register layer
+                if (NP > 1) tmem_ld8(tm + 4, pr[0][0], pr[0][1]);
+                else tmem_ld4(tm + 4, pr[0][0]);
+                if (NP > 1) tmem_wait_ld(o0, pr[0][0], pr[0][1]);
+                else tmem_wait_ld(o0, pr[0][0]);
+                if (NP > 2) tmem_ld8(tm + 4 * 3, pr[1][0], pr[1][1]);
+                else if (NP == 2) tmem_ld4(tm + 4 * 3, pr[1][0]);
+                {
+                    const float2 w = s_t2[RL - 1];
+                    a[RL - 1][0] = add2(lse2_pair(((POLY_MASK >> (RL - 1)) & 1u) != 0, add2(w, q[0]),
+                                                  make_float2(o0.x, o0.y), ((LG_MASK >> (RL - 1)) & 1u) != 0, FIN, LG6), ev[0]);
+                    a[RL - 1][1] = add2(lse2_pair(((POLY_MASK >> (RL - 1)) & 1u) != 0, add2(w, q[1]),
+                                                  make_float2(o0.z, o0.w), ((LG_MASK >> (RL - 1)) & 1u) != 0, FIN, LG6), ev[1]);
+                }
+#pragma unroll
+                for (int pp = 0; pp < NP; ++pp) {
+                    float4 (&b)[2] = pr[pp & 1];
+                    const bool last = pp == NP - 1;
+                    if (pp > 0) {
+                        if (last) tmem_wait_ld(b[0]);
+                        else tmem_wait_ld(b[0], b[1]);
+                        if (pp + 2 < NP) tmem_ld8(tm + 4 * (2 * pp + 3), pr[(pp + 1) & 1][0], pr[(pp + 1) & 1][1]);
+                        else if (pp + 2 == NP) tmem_ld4(tm + 4 * (2 * pp + 3), pr[(pp + 1) & 1][0]);
+                    }
+                    const int d = RL + 2 * pp;
+                    // second layer of the pair first: in the last pair both read old layer 15 (b[0])
+                    {
+                        const float4 &old = last ? b[0] : b[1];
+                        float2 v0 = make_float2(old.x, old.y), v1 = make_float2(old.z, old.w);
+                        if (last) { v0.x += gamma2; v0.y += gamma2; v1.x += gamma2; v1.y += gamma2; }
+                        const float2 w = s_t2[d + 1];
+                        const float2 r0 = add2(lse2_pair(((POLY_MASK >> (d + 1)) & 1u) != 0, add2(w, q[0]), v0, ((LG_MASK >> (d + 1)) & 1u) != 0, FIN, LG6), ev[0]);
+                        const float2 r1 = add2(lse2_pair(((POLY_MASK >> (d + 1)) & 1u) != 0, add2(w, q[1]), v1, ((LG_MASK >> (d + 1)) & 1u) != 0, FIN, LG6), ev[1]);
+                        b[1] = make_float4(r0.x, r0.y, r1.x, r1.y);
+                    }
+                    {
+                        float2 v0 = make_float2(b[0].x, b[0].y), v1 = make_float2(b[0].z, b[0].w);
+                        if (last) { v0.x += syn2; v0.y += syn2; v1.x += syn2; v1.y += syn2; }
+                        const float2 w = s_t2[d];
+                        const float2 r0 = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[0]), v0, ((LG_MASK >> d) & 1u) != 0, FIN, LG6), ev[0]);
+                        const float2 r1 = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[1]), v1, ((LG_MASK >> d) & 1u) != 0, FIN, LG6), ev[1]);
+                        b[0] = make_float4(r0.x, r0.y, r1.x, r1.y);
+                    }
+                    tmem_st8(tm + 4 * (2 * pp), b[0], b[1]);
+                }
             } else {
-                nxt = As[tid];           // layer 8 (old)
-            }
+            // layers RL..15: the "next layer" operand comes from shared memory
+            float4 nxt = As[tid];           // layer RL (old)
             {
                 const float2 w = s_t2[RL - 1];
                 a[RL - 1][0] = add2(lse2_pair(((POLY_MASK >> (RL - 1)) & 1u) != 0, add2(w, q[0]),
@@ -1111,19 +1155,8 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
 #pragma unroll
             for (int d = RL; d < kLayers; ++d) {
                 // old alpha[min(d+1,15)]; layers 14 and 15 both read old layer 15
-                if constexpr (TMEM) {
-                    // layer d + 1 was requested during layer d - 1; layer d + 2 is requested now, before
-                    // layer d is written (a load has completed before anything overwrites its columns)
-                    if (d < kLayers - 1) {
-                        float4 &cur = (d & 1) ? nxt : nxt2, &ahead = (d & 1) ? nxt2 : nxt;
-                        tmem_wait_ld(cur);
-                        if (d + 2 < kLayers) tmem_ld4(tm + 4 * (d + 2 - RL), ahead);
-                    }
-                } else {
-                    if (d < kLayers - 1) nxt = As[(d + 1 - RL) * NT + tid];
-                }
-                const float4 &old = !TMEM ? nxt : (d < kLayers - 1) ? ((d & 1) ? nxt : nxt2) : ((d & 1) ? nxt2 : nxt);
-                float2 v0 = make_float2(old.x, old.y), v1 = make_float2(old.z, old.w);
+                if (d < kLayers - 1) nxt = As[(d + 1 - RL) * NT + tid];
+                float2 v0 = make_float2(nxt.x, nxt.y), v1 = make_float2(nxt.z, nxt.w);
                 if (d >= 14) {
                     const float c = d == 15 ? gamma2 : syn2;
                     v0.x += c; v0.y += c; v1.x += c; v1.y += c;
@@ -1131,8 +1164,8 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
                 const float2 w = s_t2[d];
                 const float2 r0 = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[0]), v0, ((LG_MASK >> d) & 1u) != 0, FIN, LG6), ev[0]);
                 const float2 r1 = add2(lse2_pair(((POLY_MASK >> d) & 1u) != 0, add2(w, q[1]), v1, ((LG_MASK >> d) & 1u) != 0, FIN, LG6), ev[1]);
-                if constexpr (TMEM) tmem_st4(tm + 4 * (d - RL), make_float4(r0.x, r0.y, r1.x, r1.y));
-                else As[(d - RL) * NT + tid] = make_float4(r0.x, r0.y, r1.x, r1.y);
+                As[(d - RL) * NT + tid] = make_float4(r0.x, r0.y, r1.x, r1.y);
+            }
             }
             if constexpr (TMEM) tmem_wait_st();   // the next step reads what this one stored
             buf ^= 1u;
