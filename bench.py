@@ -280,7 +280,7 @@ def main():
                 return all_seqs, None
             parts = dist.partition(global_lens, world, clusters)
             local, _ = dist.shard_sequences(all_seqs, rank, world, clusters)
-            return local, parts
+            return local, dist.gather_plan(parts, torch.device("cuda", local_rank))
         local = synthetic.hmm_sequences(args.batch, args.min_len, args.max_len, seed=SEED,
                                         data_seed=None if rank == 0 else SEED + 17 * rank)
         return local, None
@@ -315,7 +315,7 @@ def main():
             if scaling == "weak":
                 td.all_gather(gather_buf, local_result)
             else:
-                dist.gather_results(local_result, global_lens, parts=parts)
+                dist.gather_results(local_result, plan=parts)
 
         def step_device():
             hmm_mod.forward_kernel(dev_hmm, dev_seqs, result, a1, a2, opts=opts)

@@ -214,22 +214,48 @@ def _gather_blocks(local, sizes, group=None):
     return [gathered[r][:int(sizes[r])] for r in range(world)]
 
 
-def gather_results(local_result, lens, group=None, clusters_per_rank=None, parts=None):
+def gather_plan(parts, device):
+    """What :func:`gather_results` needs beyond the partition, prepared once: the
+    padded block width and, on ``device``, the position of every sequence in the
+    concatenation of the ranks' padded blocks. A caller that gathers after every
+    step builds it once; the gather is then one collective and one index kernel,
+    with no host-to-device traffic."""
+    import torch
+    sizes = [int(len(p)) for p in parts]
+    width = max(sizes) if sizes else 0
+    total = sum(sizes)
+    perm = np.empty(total, dtype=np.int64)
+    for r, p in enumerate(parts):
+        perm[np.asarray(p, dtype=np.int64)] = r * width + np.arange(len(p), dtype=np.int64)
+    return {"sizes": sizes, "width": width, "perm": torch.from_numpy(perm).to(device)}
+
+
+def gather_results(local_result, lens=None, group=None, clusters_per_rank=None, parts=None, plan=None):
     """All-gathers the per-sequence results of every rank and returns them in
     the original sequence order. ``lens`` are the global lengths (host), from
     which every rank re-derives the partition (pass the same
     ``clusters_per_rank`` as to :func:`shard_sequences`); a caller that gathers
-    repeatedly may pass the partition itself as ``parts``."""
+    repeatedly passes the partition as ``parts`` or, better, a
+    :func:`gather_plan` as ``plan``."""
     import torch
     import torch.distributed as td
     world = td.get_world_size(group)
-    if parts is None:
-        parts = partition(lens, world, clusters_per_rank)
-    blocks = _gather_blocks(local_result, [len(p) for p in parts], group)
-    out = torch.empty(sum(len(p) for p in parts), dtype=local_result.dtype, device=local_result.device)
-    for r, p in enumerate(parts):
-        out[torch.from_numpy(p).to(out.device)] = blocks[r]
-    return out
+    if plan is None:
+        if parts is None:
+            parts = partition(lens, world, clusters_per_rank)
+        plan = gather_plan(parts, local_result.device)
+    width = plan["width"]
+    if local_result.shape[0] == width and local_result.is_contiguous():
+        padded = local_result
+    else:
+        padded = torch.zeros(width, dtype=local_result.dtype, device=local_result.device)
+        padded[:local_result.shape[0]] = local_result
+    flat = torch.empty(world * width, dtype=local_result.dtype, device=local_result.device)
+    try:
+        td.all_gather_into_tensor(flat, padded, group=group)
+    except (RuntimeError, NotImplementedError):      # a backend without the flat form
+        td.all_gather(list(flat.view(world, width).unbind(0)), padded, group=group)
+    return flat.index_select(0, plan["perm"])
 
 
 # ---- row blocks (CSR SpMV, SDDMM) and vector slices (reductions) ------------------------

@@ -338,6 +338,29 @@ def test_default_arithmetic_by_state_space(native, monkeypatch):
     assert rc != 0 and "exclude each other" in native.error_message()
 
 
+@pytest.mark.parametrize("k,scale,nseq,lo,hi", [(6, 8.0, 6, 50, 400), (6, 16.0, 6, 50, 400), (7, 8.0, 4, 30, 200),
+                                                (6, 8.0, 2, 8000, 12000)])
+def test_peaky_tables_and_long_sequences(native, oracle_mod, k, scale, nseq, lo, hi):
+    # Tables with a wide dynamic range (emission log-probabilities down to -60 / -120, transition
+    # rows dominated by one successor) and sequences of 10^4 steps, on the state spaces whose
+    # default is the scaled kernel: neighbouring k-mers of a thread then differ by many orders of
+    # magnitude, which is what its per-thread exponent has to absorb. Same bar as everywhere.
+    from parpy_b200 import synthetic
+    hmm = synthetic.hmm_model(k, seed=70 + k)
+    g = torch.Generator().manual_seed(99)
+    hmm["output_prob"] = torch.log_softmax(scale * torch.randn(101, 4 ** k, generator=g), dim=0).contiguous()
+    hmm["trans1"] = torch.log_softmax(4.0 * torch.randn(4 ** k, 4, generator=g), dim=1).contiguous()
+    assert float(hmm["output_prob"].min()) < -7.0 * scale
+    seqs = synthetic.hmm_sequences(nseq, lo, hi, seed=80 + k)
+    exp = oracle_mod.forward(hmm, seqs)
+    for flags in (0, FLAGS["scaled"], FLAGS["log_space"]):
+        rc, res, _, _ = cabi_forward(native, to_dev(hmm), to_dev(seqs), flags)
+        assert rc == 0, native.error_message()
+        assert max_rel(res.cpu().numpy(), exp) <= REL_ORACLE, flags
+    rc = ctypes.c_uint32(0)
+    assert native.lib().parpy_b200_forward_status(ctypes.byref(rc)) == 0 and rc.value == 0
+
+
 @pytest.mark.parametrize("k,nseq,lo,hi", [(7, 40, 30, 400), (6, 50, 1, 300)])
 def test_scaled_layouts_agree_bit_for_bit(native, monkeypatch, k, nseq, lo, hi):
     # The scaled kernel in its layouts: clusters of 512-thread CTAs with all 16 layers in
