@@ -167,13 +167,13 @@ __device__ __forceinline__ float lse5_reference(float p1, float p2, float p3, fl
 // the repair brings that below 0.1 %. Output: `order` holds the sequence ids grouped
 // by bin (longest first inside a bin) and seg[c] .. seg[c+1] delimit bin c.
 // Batches above kSortLimit fall back to a work queue in input order (seg unused).
+// Smallest 64-bit key of the warp: the smallest high word, then the smallest low word among the
+// lanes that hold it (two hardware reductions instead of five rounds of 64-bit shuffles).
 __device__ __forceinline__ unsigned long long warp_min_u64(unsigned long long v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const unsigned long long w = __shfl_xor_sync(0xffffffffu, v, o);
-        v = w < v ? w : v;
-    }
-    return v;
+    const unsigned hi = static_cast<unsigned>(v >> 32);
+    const unsigned mh = __reduce_min_sync(0xffffffffu, hi);
+    const unsigned ml = __reduce_min_sync(0xffffffffu, hi == mh ? static_cast<unsigned>(v) : 0xffffffffu);
+    return (static_cast<unsigned long long>(mh) << 32) | ml;
 }
 
 __global__ void __launch_bounds__(1024, 1)
@@ -183,6 +183,7 @@ hmm_schedule(const int64_t *__restrict__ lens, int B, int C, int *__restrict__ o
     __shared__ long long s_load[kMaxBins];
     __shared__ int s_cnt[kMaxBins + 1];
     __shared__ unsigned short s_alist[256];
+    __shared__ unsigned char s_chunk[kSortLimit / 32];   // members of the fullest bin per chunk of 32 ranks
     __shared__ unsigned long long s_red[32];
     __shared__ int s_a, s_na, s_done;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -231,8 +232,27 @@ hmm_schedule(const int64_t *__restrict__ lens, int B, int C, int *__restrict__ o
     for (int c = tid; c < C; c += blockDim.x) s_load[c] = 0;
     __syncthreads();
 
-    // greedy packing, one warp: item r to the least loaded bin (lowest bin among equals)
-    if (warp == 0) {
+    // greedy packing, one warp: item r to the least loaded bin (lowest bin among equals). Up to 64 bins
+    // (two per lane) the sums stay in registers; the general path keeps them in shared memory.
+    if (warp == 0 && C <= 64) {
+        long long l0 = 0, l1 = 0;   // sums of bins lane and lane + 32
+        for (int r = 0; r < B; ++r) {
+            int bin;
+            if (r < C) {
+                bin = r;
+            } else {
+                const unsigned long long k0 = lane < C ? ((static_cast<unsigned long long>(l0) << 10) | unsigned(lane)) : ~0ull;
+                const unsigned long long k1 = lane + 32 < C ? ((static_cast<unsigned long long>(l1) << 10) | unsigned(lane + 32)) : ~0ull;
+                bin = static_cast<int>(warp_min_u64(k0 < k1 ? k0 : k1) & 1023u);
+            }
+            const int len = s_len[r];
+            if (bin == lane) l0 += len;
+            if (bin == lane + 32) l1 += len;
+            if (lane == 0) s_bin[r] = static_cast<unsigned short>(bin);
+        }
+        if (lane < C) s_load[lane] = l0;
+        if (lane + 32 < C) s_load[lane + 32] = l1;
+    } else if (warp == 0) {
         for (int r = 0; r < B; ++r) {
             int bin;
             if (r < C) {
@@ -277,23 +297,37 @@ hmm_schedule(const int64_t *__restrict__ lens, int B, int C, int *__restrict__ o
                 key = k < key ? k : key;
             }
             const int a = static_cast<int>(warp_min_u64(key) & 1023u);
-            int n = 0;
-            for (int r0 = 0; r0 < B && n < 256; r0 += 32) {
-                const int r = r0 + lane;
-                const bool in = r < B && s_bin[r] == a;
-                const unsigned m = __ballot_sync(0xffffffffu, in);
-                const int pos = n + __popc(m & ((1u << lane) - 1u));
-                if (in && pos < 256) s_alist[pos] = static_cast<unsigned short>(r);
-                n += __popc(m);
-            }
             if (lane == 0) {
                 s_a = a;
-                s_na = n < 256 ? n : 256;
                 s_done = 0;
             }
         }
         __syncthreads();
-        const int a = s_a, na = s_na;
+        const int a = s_a;
+        // its members in rank order (the first 256): every warp lists those of its own chunks of 32
+        // ranks, a warp's position in the list is the number of members in the chunks before its own
+        for (int c0 = warp; c0 * 32 < B; c0 += 32) {
+            const int r = c0 * 32 + lane;
+            const unsigned m = __ballot_sync(0xffffffffu, r < B && s_bin[r] == a);
+            if (lane == 0) s_chunk[c0] = static_cast<unsigned char>(__popc(m));
+        }
+        __syncthreads();
+        for (int c0 = warp; c0 * 32 < B; c0 += 32) {
+            int before = 0;
+            for (int c = lane; c < c0; c += 32) before += s_chunk[c];
+            before = __reduce_add_sync(0xffffffffu, before);
+            const int r = c0 * 32 + lane;
+            const bool in = r < B && s_bin[r] == a;
+            const unsigned m = __ballot_sync(0xffffffffu, in);
+            const int pos = before + __popc(m & ((1u << lane) - 1u));
+            if (in && pos < 256) s_alist[pos] = static_cast<unsigned short>(r);
+            if (c0 == (B - 1) / 32 && lane == 0) {
+                const int n = before + __popc(m);
+                s_na = n < 256 ? n : 256;
+            }
+        }
+        __syncthreads();
+        const int na = s_na;
         const long long La = s_load[a];
         // candidates: exchange x (fullest bin) with a shorter y of bin b, or move x to bin b;
         // key = new larger sum of the two bins, then a deterministic tie-break
