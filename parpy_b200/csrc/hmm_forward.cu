@@ -1,11 +1,15 @@
-// Log-space HMM forward algorithm over a k-mer x 16-duration-layer state space
-// for sm_100a. Two implementations behind one entry point:
+// HMM forward algorithm over a k-mer x 16-duration-layer state space for
+// sm_100a. Implementations behind one entry point:
 //
-//  * resident kernel  — a persistent thread-block cluster owns one sequence at
-//    a time; every thread keeps the 16 duration layers of its k-mers in
-//    registers for the whole sequence, only layer 0 (K floats) is exchanged per
-//    time step through distributed shared memory, with one split
-//    barrier.cluster arrive/wait per step hidden behind layers 1..15.
+//  * resident kernels — a persistent thread-block cluster owns one sequence at
+//    a time; every thread keeps the 16 duration layers of its k-mers on chip
+//    (registers, tensor memory) for the whole sequence, only layer 0 (K floats)
+//    is exchanged per time step through distributed shared memory. In log
+//    space (the reference's arithmetic: hmm_forward_packed and its twins, one
+//    split barrier.cluster arrive/wait per step hidden behind layers 1..15) or
+//    on probabilities with a per-thread base-2 exponent (hmm_forward_scaled*:
+//    two multiply-adds per state, st.async + mbarrier exchange), which is what
+//    a call without options runs for 4096 k-mers and more.
 //  * streaming kernel — alpha ping-pongs through caller scratch in global
 //    memory, one launch per time step, the reference's literal five-term
 //    log-sum-exp. Covers state spaces the resident kernel cannot hold and is
@@ -2529,7 +2533,7 @@ ResidentKernel pick_kernel(const Plan &pl, bool five) {
         bool masks = false;
         if (const char *mk = getenv("PARPY_B200_FWD_MASKS")) masks = sscanf(mk, "%x:%x", &ex, &lg) == 2;
         if (packed && pl.tmem) {
-            // Default for 4096 k-mers and more. Measured on the benchmark workload (state-steps/s):
+            // The log-space kernel for 4096 k-mers and more. Measured on the benchmark workload (state-steps/s):
             // logarithm of layers 2,3,5,6,7,9,10,11,13,14,15 as polynomial, 4 layers in registers
             // 1.911e12; same with 8 in registers 1.905e12, 6: 1.891e12; layers 1,2,3,5,... (12) 1.897e12;
             // exponential of the even layers but 0 as polynomial and no logarithm (the earlier
