@@ -163,8 +163,18 @@ int32_t parpy_b200_forward_schedule(const int64_t *lens, int64_t num_instances, 
  * clamped. Bit 1: an observation byte >= n_obs was clamped (parpy_b200_forward_ex).
  * Bit 2: a bounded wait for another CTA's values ran out inside a kernel (scaled
  * kernel, st.async exchange); the results of the calls since the last read are
- * not valid. */
+ * not valid. A caller that never reads the word still learns of bit 2: the
+ * kernel also sets a word in pinned host memory (one per device, allocated by the
+ * first forward call on it), and every later forward_kernel / parpy_b200_forward*
+ * call on the device returns an error that says so, without launching, until the
+ * status has been read. */
 int32_t parpy_b200_forward_status(uint32_t *status);
+/* Launches one 32-thread CTA that waits, with the scaled kernel's bounded wait,
+ * on a barrier nothing completes; after `polls` (0..2^20) polls it gives up and
+ * raises bit 2 of the forward status word. Touches no caller data. Lets a caller
+ * (or a test) see the give-up path reach parpy_b200_forward_status without any
+ * kernel being starved. No counterpart in the reference. */
+int32_t parpy_b200_forward_wait_probe(int32_t polls, void *stream);
 
 /* Forward pass for callers that must not trigger a device allocation.
  * No counterpart in the reference: its generated host stub allocates and frees

@@ -71,6 +71,7 @@ SIGNATURES = {
                                       c_i64, c_i64, c_i64, c_ptr, c_i64, c_ptr]),
     "parpy_b200_viterbi_status": (c_i32, [c_ptr]),
     "parpy_b200_viterbi_wait_probe": (c_i32, [c_i32, c_ptr]),
+    "parpy_b200_forward_wait_probe": (c_i32, [c_i32, c_ptr]),
 }
 
 REDUCE_SUM, REDUCE_PROD, REDUCE_MAX, REDUCE_MIN = 0, 1, 2, 3

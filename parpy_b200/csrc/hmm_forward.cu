@@ -80,7 +80,18 @@ struct FwdParams {
     float synthetic;
     float gamma_lin;            // exp(gamma), exp(synthetic_248): scaled kernel only
     float synthetic_lin;
+    unsigned *host_flag;        // pinned host word set when a bounded wait runs out (NULL: none)
 };
+
+// A bounded wait ran out: status bit 2 on the device and, where the library has one, a word in
+// pinned host memory that the next forward call on the device checks before it launches anything.
+__device__ __forceinline__ void flag_wait_timeout(unsigned *host_flag) {
+    atomicOr(&g_status, 4u);
+    if (host_flag != nullptr) {
+        *reinterpret_cast<volatile unsigned *>(host_flag) = 1u;
+        __threadfence_system();
+    }
+}
 
 // Observation byte t of a sequence, kept inside the emission table: a value past the last
 // row is clamped and remembered in `bad` (no branch in the time loop; the caller raises the
@@ -1950,8 +1961,8 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_split(const FwdPar
 // only the layer-0 exchange. Arithmetic and results are those of hmm_forward_scaled_split.
 // Bounded wait on a CTA-local mbarrier phase (st.async exchange). False: gave up.
 constexpr int kFwdWaitLimit = 1 << 22;
-__device__ __forceinline__ bool fwd_mbar_wait(unsigned mbar, unsigned parity) {
-    for (int i = 0; i < kFwdWaitLimit; ++i) {
+__device__ __forceinline__ bool fwd_mbar_wait(unsigned mbar, unsigned parity, int limit = kFwdWaitLimit) {
+    for (int i = 0; i < limit; ++i) {
         unsigned ok;
         asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
                      "selp.u32 %0, 1, 0, p;\n\t}"
@@ -1959,6 +1970,22 @@ __device__ __forceinline__ bool fwd_mbar_wait(unsigned mbar, unsigned parity) {
         if (ok) return true;
     }
     return false;
+}
+
+// One CTA that waits, with the kernel's own bounded wait, on a barrier nothing completes: the wait
+// runs out after `polls` polls and status bit 2 is raised exactly as in hmm_forward_scaled_tmem. No
+// other CTA, no data in flight; used to check that a wait that gives up reaches the host.
+__global__ void fwd_wait_probe(int polls, unsigned *host_flag) {
+    __shared__ __align__(8) unsigned long long mbar;
+    const unsigned addr = smem_u32(&mbar);
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(addr));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (!fwd_mbar_wait(addr, 0u, polls) && threadIdx.x == 0) flag_wait_timeout(host_flag);
+    __syncthreads();
+    if (threadIdx.x == 0) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(addr) : "memory");
 }
 
 // RL: layers kept in registers (4, 6 or 8); the others live in tensor memory. ASYNC (clusters of
@@ -2048,7 +2075,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_tmem(const FwdPara
         if constexpr (ASYNC) {
             if (!dead && !fwd_mbar_wait(mbar0 + 8u * b2, (phase >> b2) & 1u)) {
                 dead = true;
-                atomicOr(&g_status, 4u);
+                flag_wait_timeout(p.host_flag);
             }
             phase ^= 1u << b2;
         } else {
@@ -2674,6 +2701,30 @@ int32_t launch_schedule(FwdParams *p, const SchedScratch &sc, int clusters, int 
     return PB_OK;
 }
 
+// One word of pinned host memory per device that a kernel sets when a bounded wait runs out
+// (flag_wait_timeout). The forward entry looks at it before launching: a call whose exchange
+// timed out returned without an error (launches are asynchronous), so the next call on the device
+// reports it instead of letting invalid results pass silently; reading the status word clears it.
+// Allocated on the first call per device; without it (allocation refused) only the status word is left.
+unsigned *host_timeout_flag(int device) {
+    static std::mutex mu;
+    static unsigned *flags[64] = {};
+    static bool tried[64] = {};
+    if (device < 0 || device >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!tried[device]) {
+        tried[device] = true;
+        void *ptr = nullptr;
+        if (cudaHostAlloc(&ptr, sizeof(unsigned), cudaHostAllocPortable | cudaHostAllocMapped) == cudaSuccess) {
+            flags[device] = static_cast<unsigned *>(ptr);
+            *flags[device] = 0u;
+        } else {
+            (void)cudaGetLastError();
+        }
+    }
+    return flags[device];
+}
+
 // Arithmetic of a call that names none (flags without SCALED / LOG_SPACE / FIVE_TERM / STREAMING /
 // WRITE_ALPHA) on 4096 k-mers and more: the scaled kernel. On the benchmark batch at full length it is
 // 2.3e-6 from the fp32 oracle where the log-space kernel is 1.5e-6 (the oracle's own distance from a
@@ -2741,6 +2792,11 @@ int32_t forward_impl(float gamma, const float *initial_prob, int64_t num_states,
     p.gamma_lin = expf(gamma);
     p.synthetic_lin = expf(synthetic_248);
     p.write_alpha = write_alpha ? 1 : 0;
+    p.host_flag = host_timeout_flag(dev.device);
+    PB_REQUIRE(p.host_flag == nullptr || *reinterpret_cast<volatile unsigned *>(p.host_flag) == 0u,
+               "forward: a bounded wait inside an earlier forward kernel on this device ran out, so results "
+               "computed since the last parpy_b200_forward_status read are not valid; read the status word "
+               "(that clears this condition) and repeat those calls");
 
     Plan pl;
     bool resident = !streaming_forced && make_plan(K, &pl, !five, scaled);
@@ -2886,7 +2942,19 @@ int32_t parpy_b200_forward_status(uint32_t *status) {
     PB_CUDA(cudaDeviceSynchronize());
     PB_CUDA(cudaMemcpyFromSymbol(&v, g_status, sizeof(v)));
     PB_CUDA(cudaMemcpyToSymbol(g_status, &zero, sizeof(zero)));
+    int device = -1;
+    PB_CUDA(cudaGetDevice(&device));
+    if (unsigned *flag = host_timeout_flag(device)) *reinterpret_cast<volatile unsigned *>(flag) = 0u;
     *status = v;
+    return PB_OK;
+}
+
+int32_t parpy_b200_forward_wait_probe(int32_t polls, void *stream) {
+    PB_REQUIRE(polls >= 0 && polls <= (1 << 20), "forward_wait_probe: polls=%d outside 0..2^20", polls);
+    int device = -1;
+    PB_CUDA(cudaGetDevice(&device));
+    fwd_wait_probe<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(polls, host_timeout_flag(device));
+    PB_CUDA(cudaGetLastError());
     return PB_OK;
 }
 

@@ -732,6 +732,35 @@ def test_results_do_not_depend_on_the_number_of_resident_clusters(native, monkey
             assert torch.equal(res, base[flags])
 
 
+def test_a_forward_wait_that_gives_up_reaches_the_host(native):
+    # The scaled kernel's waits for its neighbours' layer-0 values are bounded; when one runs out
+    # the kernel raises status bit 2 instead of hanging. Here a probe CTA waits on a barrier nothing
+    # completes (no other CTA involved, nothing in flight), gives up after 64 polls, and the host
+    # sees the bit; a forward pass that follows is healthy and leaves the word clean.
+    from parpy_b200 import hmm as hmm_mod, synthetic
+    clean = {"length_clamped": False, "observation_clamped": False, "wait_timed_out": False}
+    hmm_mod.forward_status()
+    assert hmm_mod.forward_status() == clean
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert native.lib().parpy_b200_forward_wait_probe(64, stream) == 0, native.error_message()
+    assert hmm_mod.forward_status() == dict(clean, wait_timed_out=True)
+    assert hmm_mod.forward_status() == clean                                  # read-and-clear
+    hmm, seqs = to_dev(synthetic.hmm_model(6, seed=3)), to_dev(synthetic.hmm_sequences(9, 5, 80, seed=4))
+    # A caller that never reads the status word still learns of it: the kernel also sets a word in
+    # pinned host memory, and the next forward call on the device refuses to launch until the status
+    # has been read.
+    assert native.lib().parpy_b200_forward_wait_probe(0, stream) == 0
+    torch.cuda.synchronize()
+    rc, _, _, _ = cabi_forward(native, hmm, seqs)
+    assert rc != 0 and "ran out" in native.error_message()
+    assert hmm_mod.forward_status() == dict(clean, wait_timed_out=True)
+    rc, a, _, _ = cabi_forward(native, hmm, seqs)
+    rc2, b, _, _ = cabi_forward(native, hmm, seqs, FLAGS["log_space"])
+    assert rc == 0 and rc2 == 0 and max_rel(a.cpu().numpy(), b.cpu().numpy()) <= REL_ORACLE
+    assert hmm_mod.forward_status() == clean
+    assert native.lib().parpy_b200_forward_wait_probe(-1, stream) != 0 and "outside" in native.error_message()
+
+
 def test_out_of_range_observations_are_clamped_and_flagged(native):
     # A byte that is not a row of the emission table (>= n_obs) inside a sequence: with n_obs given
     # the kernels read row n_obs - 1 instead of memory past the table and raise status bit 1.
