@@ -13,7 +13,15 @@ from .options import CompileOptions
 @jit
 def forward_kernel(hmm, seqs, result, alpha1, alpha2):
     """result[i] = log-likelihood of sequence i under the k-mer/duration HMM.
-    Bound to the native kernel; this body is never run."""
+    Bound to the native kernel; this body is never run.
+
+    ``opts.b200 = {"forward": mode}`` chooses the arithmetic: ``"auto"``
+    (default: the scaled kernel for 4096 k-mers and more, the log-space kernel
+    below that and whenever alpha is requested), ``"log_space"``, ``"scaled"``,
+    ``"five_term"`` (the reference's literal operand order) or ``"streaming"``
+    (one launch per time step, alpha in the caller's scratch);
+    ``{"write_alpha": True}`` stores every sequence's final alpha vector in
+    ``alpha1`` / ``alpha2`` as the reference leaves it."""
 
 
 def forward_parpy(hmm, seqs, nthreads=None, opts=None, alpha=None):
