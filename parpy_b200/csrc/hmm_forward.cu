@@ -81,6 +81,7 @@ struct FwdParams {
     float gamma_lin;            // exp(gamma), exp(synthetic_248): scaled kernel only
     float synthetic_lin;
     unsigned *host_flag;        // pinned host word set when a bounded wait runs out (NULL: none)
+    const float *output_lin;    // exp(output_prob) in library scratch: scaled tensor-memory kernel only (NULL: none)
 };
 
 // A bounded wait ran out: status bit 2 on the device and, where the library has one, a word in
@@ -1972,6 +1973,15 @@ __device__ __forceinline__ bool fwd_mbar_wait(unsigned mbar, unsigned parity, in
     return false;
 }
 
+// exp() of every entry of the emission table, for the scaled kernel: the same fast_exp it would
+// take per use (4 per thread and step), taken once per entry here. n4 = number of float4.
+__global__ void __launch_bounds__(256) hmm_exp_table(const float4 *__restrict__ in, float4 *__restrict__ out, long long n4) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+        const float4 v = __ldg(in + i);
+        out[i] = make_float4(fast_exp(v.x), fast_exp(v.y), fast_exp(v.z), fast_exp(v.w));
+    }
+}
+
 // One CTA that waits, with the kernel's own bounded wait, on a barrier nothing completes: the wait
 // runs out after `polls` polls and status bit 2 is raised exactly as in hmm_forward_scaled_tmem. No
 // other CTA, no data in flight; used to check that a wait that gives up reaches the host.
@@ -1995,7 +2005,8 @@ __global__ void fwd_wait_probe(int polls, unsigned *host_flag) {
 // k-mers it consumes, so a CTA can run ahead of threads elsewhere in the cluster; with up to 8
 // CTAs a writer of round r is only ordered after every thread's read of round r - 4, hence four
 // buffers and four mbarriers. Every wait is bounded; one that runs out raises status bit 2.
-template <int RL, bool ASYNC>
+// LIN: emission factors come from the table of exponentials in p.output_lin.
+template <int RL, bool ASYNC, bool LIN = false>
 __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_tmem(const FwdParams p) {
     static_assert(RL >= 4 && RL <= 8 && RL % 2 == 0, "register layers");
     extern __shared__ __align__(16) float smem_dyn[];
@@ -2084,6 +2095,9 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_tmem(const FwdPara
     };
     const unsigned cl_addr = smem_u32(s_cl);
     const unsigned cli_addr = smem_u32(s_cl_i);
+    // emission factors: from the table of exponentials a prologue kernel left in library scratch
+    // (same exponential, taken once per table entry instead of once per use), else from the log table
+    const float *etab = LIN ? p.output_lin : p.output_prob;
 
     first_position(p, CS, tid, &s_seq);
     for (;;) {
@@ -2107,8 +2121,9 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_tmem(const FwdPara
         {
             const int o0 = obs_at(p, obs, 0, bad_obs);
             o_next = obs_at(p, obs, T_len > 1 ? 1 : 0, bad_obs);
-            const float4 e0 = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o0 * K + g));
-            const float el[4] = {fast_exp(e0.x), fast_exp(e0.y), fast_exp(e0.z), fast_exp(e0.w)};
+            const float4 e0 = __ldg(reinterpret_cast<const float4 *>(etab + (long long)o0 * K + g));
+            const float el[4] = {LIN ? e0.x : fast_exp(e0.x), LIN ? e0.y : fast_exp(e0.y),
+                                 LIN ? e0.z : fast_exp(e0.z), LIN ? e0.w : fast_exp(e0.w)};
             float m = 0.0f;
 #pragma unroll
             for (int d = 0; d < kLayers; ++d) {
@@ -2130,7 +2145,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_tmem(const FwdPara
 
         for (int t = 1; t < T_len; ++t) {
             // this step's emission slice (in flight while the exchange completes); the observation after it
-            const float4 e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o_next * K + g));
+            const float4 e = __ldg(reinterpret_cast<const float4 *>(etab + (long long)o_next * K + g));
             o_next = obs_at(p, obs, t + 1 < T_len ? t + 1 : T_len - 1, bad_obs);
             // the transition columns, in flight while the exchange completes
             float4 t0, t1, t2, t3;
@@ -2164,7 +2179,8 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_tmem(const FwdPara
                                   fma2(make_float2(t1.x, t1.y), y1, mul2(make_float2(t0.x, t0.y), y0))));
                 const float2 q1 = fma2(make_float2(t3.z, t3.w), y3, fma2(make_float2(t2.z, t2.w), y2,
                                   fma2(make_float2(t1.z, t1.w), y1, mul2(make_float2(t0.z, t0.w), y0))));
-                const float2 el2[2] = {make_float2(fast_exp(e.x), fast_exp(e.y)), make_float2(fast_exp(e.z), fast_exp(e.w))};
+                const float2 el2[2] = {LIN ? make_float2(e.x, e.y) : make_float2(fast_exp(e.x), fast_exp(e.y)),
+                                       LIN ? make_float2(e.z, e.w) : make_float2(fast_exp(e.z), fast_exp(e.w))};
                 QE[0] = mul2(q0, el2[0]);
                 QE[1] = mul2(q1, el2[1]);
                 Eo[0] = mul2(el2[0], own);
@@ -2423,6 +2439,7 @@ struct Plan {
     bool scaled = false; // extended-range linear arithmetic instead of log space
     bool cta = false;    // one 256-thread CTA per sequence, packed arithmetic (K = 1024)
     bool tmem = false;   // scaled split layout with layers 8..15 and transition columns in tensor memory
+    bool exptab = false; // scaled tensor-memory kernel reads exp(output_prob) from a table prepared per call
 };
 
 // Picks (k-mers per thread, threads per CTA, CTAs per cluster) with
@@ -2508,6 +2525,7 @@ ResidentKernel pick_kernel(const Plan &pl, bool five) {
         // 4 / barrier 4.22e12, 8 / barrier 4.14e12; shared memory instead of tensor memory 3.77e12.
         bool async_x = pl.cs >= 2 && pl.cs <= 8;
         if (const char *env = getenv("PARPY_B200_SCALED_ASYNC")) async_x = async_x && atoi(env) != 0;
+        if (async_x && pl.exptab && rl != 4 && rl != 8) return hmm_forward_scaled_tmem<6, true, true>;
         if (async_x) return rl == 4 ? hmm_forward_scaled_tmem<4, true> : rl == 8 ? hmm_forward_scaled_tmem<8, true> : hmm_forward_scaled_tmem<6, true>;
         return rl == 4 ? hmm_forward_scaled_tmem<4, false> : rl == 8 ? hmm_forward_scaled_tmem<8, false> : hmm_forward_scaled_tmem<6, false>;
     }
@@ -2807,6 +2825,10 @@ int32_t forward_impl(float gamma, const float *initial_prob, int64_t num_states,
     PB_REQUIRE(!scaled || (resident && pl.kpt == 4),
                "forward: the scaled kernel needs at least 1024 k-mers (num_states=%lld)", (long long)num_states);
     if (resident) finish_plan(&pl, five, scaled);
+    // scaled tensor-memory kernel with a known table height: exponentials of the emission table once per
+    // call (6.6 MB for the 7-mer table, a few microseconds) instead of four per thread and step
+    if (resident)
+        pl.exptab = pl.scaled && pl.tmem && n_obs >= 1 && n_obs <= 256 && getenv("PARPY_B200_SCALED_EXPTAB_OFF") == nullptr;
     if (resident) {
         PB_REQUIRE(pl.kpt == 1 || (pb::aligned16(initial_prob) && pb::aligned16(output_prob) &&
                                    pb::aligned16(trans1) &&
@@ -2829,6 +2851,17 @@ int32_t forward_impl(float gamma, const float *initial_prob, int64_t num_states,
         if (rc) return rc;
         rc = launch_schedule(&p, sched_layout(ws, sched_bytes(p.B) - kSchedTailBytes), clusters, nullptr, stream);
         if (rc) return rc;
+        if (pl.exptab) {
+            void *tab = nullptr;
+            const long long n4 = n_obs * K / 4;
+            rc = pb::workspace((size_t)n4 * sizeof(float4), &tab, stream, 5);
+            if (rc) return rc;
+            const int blocks = (int)std::min<long long>((n4 + 255) / 256, 148 * 8);
+            hmm_exp_table<<<blocks, 256, 0, stream>>>(reinterpret_cast<const float4 *>(output_prob),
+                                                      static_cast<float4 *>(tab), n4);
+            PB_CUDA(cudaGetLastError());
+            p.output_lin = static_cast<const float *>(tab);
+        }
         cfg.gridDim = dim3(pl.cs * clusters, 1, 1);
         cfg.stream = stream;
         PB_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
