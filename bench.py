@@ -415,7 +415,10 @@ def main():
             "config": workload_config(args, world),
             "e2e": {"value": work * args.steps / e2e_s, "unit": UNIT,
                     "h2d_bytes_per_step": int(head["h2d"]), "d2h_bytes_per_step": int(head["d2h"])},
-            "gpu_launches": 2 * args.steps * world,
+            # per step and rank: the schedule kernel, the forward kernel and, for the scaled kernel, the
+            # prologue that writes the exponentials of the emission table
+            "gpu_launches": (3 if args.variant in ("auto", "scaled") and args.kmer >= 6
+                             and "PARPY_B200_SCALED_EXPTAB_OFF" not in os.environ else 2) * args.steps * world,
             "clocks": head["clocks"],
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": ncu_traffic_bytes(args, head["h2d"]),
