@@ -2020,7 +2020,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_tmem(const FwdPara
     __shared__ __align__(8) unsigned long long s_mbar[4];
 
     const int tid = threadIdx.x;
-    const int NT = blockDim.x;
+    constexpr int NT = 1024;            // this layout always runs 1024 threads per CTA (make_plan)
     const unsigned rank = cluster_ctarank();
     const unsigned CS = cluster_nctarank();
     const int K = p.K;
@@ -2525,7 +2525,7 @@ ResidentKernel pick_kernel(const Plan &pl, bool five) {
         // 4 / barrier 4.22e12, 8 / barrier 4.14e12; shared memory instead of tensor memory 3.77e12.
         bool async_x = pl.cs >= 2 && pl.cs <= 8;
         if (const char *env = getenv("PARPY_B200_SCALED_ASYNC")) async_x = async_x && atoi(env) != 0;
-        if (async_x && pl.exptab && rl != 4 && rl != 8) return hmm_forward_scaled_tmem<6, true, true>;
+        if (async_x && pl.exptab && rl != 8) return rl == 4 ? hmm_forward_scaled_tmem<4, true, true> : hmm_forward_scaled_tmem<6, true, true>;
         if (async_x) return rl == 4 ? hmm_forward_scaled_tmem<4, true> : rl == 8 ? hmm_forward_scaled_tmem<8, true> : hmm_forward_scaled_tmem<6, true>;
         return rl == 4 ? hmm_forward_scaled_tmem<4, false> : rl == 8 ? hmm_forward_scaled_tmem<8, false> : hmm_forward_scaled_tmem<6, false>;
     }
