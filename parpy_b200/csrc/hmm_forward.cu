@@ -1014,7 +1014,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
     __shared__ unsigned s_tmem;        // base address of the CTA's tensor memory (TMEM)
 
     const int tid = threadIdx.x;
-    const int NT = blockDim.x;
+    constexpr int NT = 1024;            // this layout always runs 1024 threads per CTA (make_plan)
     const unsigned rank = cluster_ctarank();
     const unsigned CS = cluster_nctarank();
     const int K = p.K;
@@ -1717,7 +1717,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_split(const FwdPar
     __shared__ float4 s_A4[kLayers / 4];  // exp(trans2[d]), four layers per 16-byte load
 
     const int tid = threadIdx.x;
-    const int NT = blockDim.x;
+    constexpr int NT = 1024;            // this layout always runs 1024 threads per CTA (make_plan)
     const unsigned rank = cluster_ctarank();
     const unsigned CS = cluster_nctarank();
     const int K = p.K;

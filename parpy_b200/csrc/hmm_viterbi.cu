@@ -232,7 +232,7 @@ __global__ void __launch_bounds__(MAXT, 1) hmm_viterbi_resident(const VitParams 
     __shared__ unsigned s_cl_i[16];
 
     const int tid = threadIdx.x;
-    const int NT = blockDim.x;
+    const int NT = TM ? 1024 : static_cast<int>(blockDim.x);   // the tensor-memory layout always runs 1024 threads (vit_plan)
     const unsigned rank = cluster_ctarank();
     const unsigned CS = cluster_nctarank();
     // One CTA per sequence (small state spaces): the hardware cluster barrier is replaced by
