@@ -1327,9 +1327,9 @@ __global__ void __launch_bounds__(256, 1) hmm_forward_packed_cta(const FwdParams
     __shared__ float2 s_t2[kLayers];   // (trans2[d], trans2[d])
 
     const int tid = threadIdx.x;
-    const int NT = blockDim.x;          // K / 4
-    const int K = p.K;
-    const int Kq = K >> 2;
+    constexpr int NT = 256;             // K / 4: this layout exists for K = 1024 only (make_plan)
+    constexpr int K = 1024;
+    constexpr int Kq = K >> 2;
     const int g = tid * 4;              // first k-mer
     const int lane = tid & 31, warp = tid >> 5, nwarps = (NT + 31) >> 5;
 
