@@ -1,5 +1,7 @@
 """Host-side behaviour of the call surface: option types, kernel resolution,
 argument validation and the sharding helpers. No GPU needed."""
+import os
+
 import numpy as np
 import pytest
 
@@ -105,6 +107,16 @@ def test_forward_option_flags():
     o.b200 = {"forward": "five_term", "write_alpha": True}
     assert ops._forward_flags(o) == _native.FWD_FIVE_TERM | _native.FWD_WRITE_ALPHA
     assert ops.forward_wants_alpha(o)
+    for mode, flag in (("log_space", _native.FWD_LOG_SPACE), ("scaled", _native.FWD_SCALED),
+                       ("streaming", _native.FWD_STREAMING), ("auto", _native.FWD_AUTO)):
+        o.b200 = {"forward": mode}
+        assert ops._forward_flags(o) == flag
+    # the values are the header's
+    header = open(os.path.join(os.path.dirname(__file__), "..", "include", "parpy_b200.h")).read()
+    for name, value in (("LOG_SPACE", _native.FWD_LOG_SPACE), ("SCALED", _native.FWD_SCALED),
+                        ("FIVE_TERM", _native.FWD_FIVE_TERM), ("WRITE_ALPHA", _native.FWD_WRITE_ALPHA),
+                        ("STREAMING", _native.FWD_STREAMING)):
+        assert f"#define PARPY_B200_FWD_{name} {value}u" in header
     o.b200 = {"forward": "bogus"}
     with pytest.raises(RuntimeError, match="must be"):
         ops._forward_flags(o)
