@@ -200,18 +200,25 @@ def shard_sequences(seqs, rank, world, clusters_per_rank=None):
 
 def _gather_blocks(local, sizes, group=None):
     """All-gathers one block per rank (``sizes[r]`` leading entries of rank r's
-    block are valid) with a single collective: blocks are padded to the largest
-    size. Returns the list of valid blocks in rank order."""
+    block are valid) with a single collective into one flat buffer: blocks are
+    padded to the largest size. Returns the list of valid blocks in rank order
+    (views of that buffer)."""
     import torch
     import torch.distributed as td
     world = td.get_world_size(group)
     width = int(max(sizes)) if len(sizes) else 0
-    shape = (width,) + tuple(local.shape[1:])
-    padded = torch.zeros(shape, dtype=local.dtype, device=local.device)
-    padded[:local.shape[0]] = local
-    gathered = [torch.empty_like(padded) for _ in range(world)]
-    td.all_gather(gathered, padded, group=group)
-    return [gathered[r][:int(sizes[r])] for r in range(world)]
+    tail = tuple(local.shape[1:])
+    if local.shape[0] == width and local.is_contiguous():
+        padded = local
+    else:
+        padded = torch.zeros((width,) + tail, dtype=local.dtype, device=local.device)
+        padded[:local.shape[0]] = local
+    flat = torch.empty((world * width,) + tail, dtype=local.dtype, device=local.device)
+    try:
+        td.all_gather_into_tensor(flat, padded, group=group)
+    except (RuntimeError, NotImplementedError):      # a backend without the flat form
+        td.all_gather(list(flat.view((world, width) + tail).unbind(0)), padded, group=group)
+    return [flat[r * width:r * width + int(sizes[r])] for r in range(world)]
 
 
 def gather_plan(parts, device):
