@@ -26,6 +26,7 @@
 
 #include <algorithm>
 #include <cstring>
+#include <type_traits>
 #include <mutex>
 
 #include "../../include/parpy_b200.h"
@@ -2143,7 +2144,11 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_tmem(const FwdPara
         }
         send(0u, x[0][0].x, x[0][0].y, x[0][1].x, x[0][1].y, W);
 
-        for (int t = 1; t < T_len; ++t) {
+        // One time step; Q = (t - 1) mod 4 is a compile-time constant (the loop below is unrolled four
+        // times), so the exchange buffers, their mbarriers and the phase bits are addressed with
+        // immediates and the every-fourth-step maximum needs no test.
+        auto step = [&](const int t, auto qtag) {
+            constexpr unsigned Q = decltype(qtag)::value;
             // this step's emission slice (in flight while the exchange completes); the observation after it
             const float4 e = __ldg(reinterpret_cast<const float4 *>(etab + (long long)o_next * K + g));
             o_next = obs_at(p, obs, t + 1 < T_len ? t + 1 : T_len - 1, bad_obs);
@@ -2151,7 +2156,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_tmem(const FwdPara
             float4 t0, t1, t2, t3;
             tmem_ld16(tm + 4 * (kLayers - RL), t0, t1, t2, t3);
 
-            const unsigned buf = (unsigned)(t - 1) % NB;   // buffer that holds the previous step's layer 0
+            constexpr unsigned buf = Q % NB;   // buffer that holds the previous step's layer 0
             receive(buf);
             const float *px = a0x + buf * 4 * M + tid;
             const int *pw = a0w + buf * M + (tid >> 2);
@@ -2196,7 +2201,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_tmem(const FwdPara
                 x[0][0] = fma2(a, QE[0], mul2(Eo[0], x[1][0]));
                 x[0][1] = fma2(a, QE[1], mul2(Eo[1], x[1][1]));
             }
-            send((unsigned)t % NB, x[0][0].x, x[0][0].y, x[0][1].x, x[0][1].y, Wn);
+            send((Q + 1u) % NB, x[0][0].x, x[0][0].y, x[0][1].x, x[0][1].y, Wn);
 #pragma unroll
             for (int d = 1; d < RL - 1; ++d) {
                 if (d % 4 == 0) a4 = s_A4[d / 4];
@@ -2272,7 +2277,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_tmem(const FwdPara
             // is below 10 x the largest emission factor. The bound only has to hold loosely (fp32 has
             // 2^127 of headroom and the true maximum follows within three steps), and power-of-two
             // rescaling is exact: the values represented do not depend on which exponent was chosen.
-            if ((t & 3) == 0 || t >= T_len - 2) {
+            if (Q == 3u || t >= T_len - 2) {
                 float m = 0.0f;
 #pragma unroll
                 for (int d = 0; d < RL; ++d) {
@@ -2289,6 +2294,18 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_tmem(const FwdPara
                 }
                 kt = exponent_of(m);
             }
+        };
+        {
+            int t = 1;
+            for (; t + 3 < T_len; t += 4) {
+                step(t, std::integral_constant<unsigned, 0u>{});
+                step(t + 1, std::integral_constant<unsigned, 1u>{});
+                step(t + 2, std::integral_constant<unsigned, 2u>{});
+                step(t + 3, std::integral_constant<unsigned, 3u>{});
+            }
+            if (t < T_len) step(t, std::integral_constant<unsigned, 0u>{});
+            if (t + 1 < T_len) step(t + 1, std::integral_constant<unsigned, 1u>{});
+            if (t + 2 < T_len) step(t + 2, std::integral_constant<unsigned, 2u>{});
         }
         receive((unsigned)(T_len - 1) % NB);   // the last round is not used, but it must have landed
 
