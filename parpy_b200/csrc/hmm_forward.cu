@@ -1093,11 +1093,13 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
             }
             if constexpr (TMEM) tmem_wait_st();
         }
-        unsigned buf = 0;
         st_cluster_v4(dst0, a[0][0].x, a[0][0].y, a[0][1].x, a[0][1].y);
         cluster_arrive();
 
-        for (int t = 1; t < T_len; ++t) {
+        // One time step; buf = (t - 1) & 1, the buffer that holds the previous step's layer 0, is a compile-time
+        // constant (the loop below is unrolled twice), so both buffers are addressed with immediates.
+        auto step = [&](const int t, auto btag) {
+            constexpr unsigned buf = decltype(btag)::value;
             // this step's emission slice; the observation after it
             e = __ldg(reinterpret_cast<const float4 *>(p.output_prob + (long long)o_next * K + g));
             o_next = obs_at(p, obs, t + 1 < T_len ? t + 1 : T_len - 1, bad_obs);
@@ -1219,7 +1221,15 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_packed(const FwdParams p)
             }
             }
             if constexpr (TMEM) tmem_wait_st();   // the next step reads what this one stored
-            buf ^= 1u;
+
+        };
+        {
+            int t = 1;
+            for (; t + 1 < T_len; t += 2) {
+                step(t, std::integral_constant<unsigned, 0u>{});
+                step(t + 1, std::integral_constant<unsigned, 1u>{});
+            }
+            if (t < T_len) step(t, std::integral_constant<unsigned, 0u>{});
         }
         cluster_wait();
 
