@@ -29,6 +29,10 @@ def cabi_forward(native, hmm, seqs, flags=0, alpha=False, entry="parpy_b200_forw
     if entry == "parpy_b200_forward":
         rc = lib.parpy_b200_forward(*common, P(res.data_ptr()), pa1, pa2, flags,
                                     P(torch.cuda.current_stream().cuda_stream))
+    elif entry == "parpy_b200_forward_ex":      # the same with the table height given (n_obs after output_prob)
+        rc = lib.parpy_b200_forward_ex(*common[:4], int(hmm["output_prob"].shape[0]), *common[4:],
+                                       P(res.data_ptr()), pa1, pa2, flags,
+                                       P(torch.cuda.current_stream().cuda_stream))
     elif entry == "forward_kernel":
         rc = lib.forward_kernel(*common, P(res.data_ptr()), pa1, pa2)
     elif entry == "forward_kernel_scratch_first":

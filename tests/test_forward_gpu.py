@@ -732,6 +732,21 @@ def test_results_do_not_depend_on_the_number_of_resident_clusters(native, monkey
             assert torch.equal(res, base[flags])
 
 
+def test_table_height_given_or_not_same_bits(native):
+    # parpy_b200_forward_ex knows the height of the emission table; for the scaled kernel a prologue then
+    # writes the exponentials of the whole table once per call and the kernel reads factors instead of
+    # taking the exponential per use. Same exponential, so the results are the same bits as through
+    # parpy_b200_forward, which cannot know how many rows the table has.
+    from parpy_b200 import synthetic
+    for k in (5, 6, 7):
+        hmm, seqs = to_dev(synthetic.hmm_model(k, seed=60 + k)), to_dev(synthetic.hmm_sequences(11, 2, 90, seed=70 + k))
+        for flags in (0, FLAGS["scaled"], FLAGS["log_space"]):
+            rc, a, _, _ = cabi_forward(native, hmm, seqs, flags)
+            rc2, b, _, _ = cabi_forward(native, hmm, seqs, flags, entry="parpy_b200_forward_ex")
+            assert rc == 0 and rc2 == 0, native.error_message()
+            assert torch.equal(a, b), (k, flags)
+
+
 def test_a_forward_wait_that_gives_up_reaches_the_host(native):
     # The scaled kernel's waits for its neighbours' layer-0 values are bounded; when one runs out
     # the kernel raises status bit 2 instead of hanging. Here a probe CTA waits on a barrier nothing
