@@ -200,6 +200,7 @@ hmm_schedule(const int64_t *__restrict__ lens, int B, int C, int *__restrict__ o
     __shared__ long long s_load[kMaxBins];
     __shared__ int s_cnt[kMaxBins + 1];
     __shared__ unsigned short s_alist[256];
+    __shared__ int s_alen[256];                           // lengths of the listed members
     __shared__ unsigned char s_chunk[kSortLimit / 32];   // members of the fullest bin per chunk of 32 ranks
     __shared__ unsigned long long s_red[32];
     __shared__ int s_a, s_na, s_done;
@@ -337,7 +338,10 @@ hmm_schedule(const int64_t *__restrict__ lens, int B, int C, int *__restrict__ o
             const bool in = r < B && s_bin[r] == a;
             const unsigned m = __ballot_sync(0xffffffffu, in);
             const int pos = before + __popc(m & ((1u << lane) - 1u));
-            if (in && pos < 256) s_alist[pos] = static_cast<unsigned short>(r);
+            if (in && pos < 256) {
+                s_alist[pos] = static_cast<unsigned short>(r);
+                s_alen[pos] = s_len[r];
+            }
             if (c0 == (B - 1) / 32 && lane == 0) {
                 const int n = before + __popc(m);
                 s_na = n < 256 ? n : 256;
@@ -349,6 +353,46 @@ hmm_schedule(const int64_t *__restrict__ lens, int B, int C, int *__restrict__ o
         // candidates: exchange x (fullest bin) with a shorter y of bin b, or move x to bin b;
         // key = new larger sum of the two bins, then a deterministic tie-break
         unsigned long long best = ~0ull;
+        if (total < (1ll << 30)) {
+            // every sum fits 31 bits: the same search on 32-bit values, the key kept as (sum, tie-break)
+            const int La32 = static_cast<int>(La);
+            unsigned bm = 0xffffffffu, blo = 0xffffffffu;
+            for (int y = tid; y < B; y += blockDim.x) {
+                const int b = s_bin[y];
+                const int Lb = static_cast<int>(s_load[b]);
+                const int d = La32 - Lb;
+                if (b == a || d < 2) continue;
+                const int ly = s_len[y];
+                for (int i = 0; i < na; ++i) {
+                    const int dd = s_alen[i] - ly;
+                    if (dd > 0 && dd < d) {
+                        const unsigned m = static_cast<unsigned>(max(La32 - dd, Lb + dd));
+                        const unsigned lo = (unsigned(y) << 12) | unsigned(s_alist[i]);
+                        if (m < bm || (m == bm && lo < blo)) {
+                            bm = m;
+                            blo = lo;
+                        }
+                    }
+                }
+            }
+            for (int b = tid; b < C; b += blockDim.x) {
+                const int Lb = static_cast<int>(s_load[b]);
+                const int d = La32 - Lb;
+                if (b == a || d < 2) continue;
+                for (int i = 0; i < na; ++i) {
+                    const int lx = s_alen[i];
+                    if (lx < d) {
+                        const unsigned m = static_cast<unsigned>(max(La32 - lx, Lb + lx));
+                        const unsigned lo = (1u << 24) | (unsigned(b) << 12) | unsigned(s_alist[i]);
+                        if (m < bm || (m == bm && lo < blo)) {
+                            bm = m;
+                            blo = lo;
+                        }
+                    }
+                }
+            }
+            if (bm != 0xffffffffu) best = (static_cast<unsigned long long>(bm) << 25) | blo;
+        } else {
         for (int y = tid; y < B; y += blockDim.x) {
             const int b = s_bin[y];
             const long long d = La - s_load[b];
@@ -379,6 +423,7 @@ hmm_schedule(const int64_t *__restrict__ lens, int B, int C, int *__restrict__ o
                     best = k < best ? k : best;
                 }
             }
+        }
         }
         best = warp_min_u64(best);
         if (lane == 0) s_red[warp] = best;
