@@ -106,7 +106,7 @@ int32_t forward_kernel_scratch_first(float gamma, float *initial_prob, int64_t n
  * on log-probabilities. Mathematically the same quantity; rounding differs: this
  * form agrees with a float64 evaluation to ~1e-8 relative, while fp32 log space
  * (the reference's arithmetic) is itself 1e-6..1e-4 away from float64. States
- * more than 2^-126 below the largest of their thread's 64 states count as log 0
+ * more than about 2^-110 below the largest of their thread's 64 states count as log 0
  * (visible only in alpha written with WRITE_ALPHA). Its layer-0 exchange waits on
  * mbarriers with a bounded number of polls; a wait that runs out raises bit 2 of
  * the status word (parpy_b200_forward_status). */

@@ -2818,11 +2818,11 @@ unsigned *host_timeout_flag(int device) {
 // Arithmetic of a call that names none (flags without SCALED / LOG_SPACE / FIVE_TERM / STREAMING /
 // WRITE_ALPHA) on 4096 k-mers and more: the scaled kernel. On the benchmark batch at full length it is
 // 2.3e-6 from the fp32 oracle where the log-space kernel is 1.5e-6 (the oracle's own distance from a
-// float64 evaluation is of that order), and it scores the batch 2.3 times as fast. State spaces of
+// float64 evaluation is of that order), and it scores the batch 2.7 times as fast. State spaces of
 // 1024 k-mers and fewer keep log-space arithmetic: the reference ships golden vectors for them and its
 // own test asks for rtol 1e-5 against fp32 log-space results, which rounding-for-rounding agreement
 // needs. A call that asks for alpha gets log space too (the scaled kernel flushes states more than
-// 2^-126 below their thread's largest to log 0). PARPY_B200_FWD_DEFAULT=log restores log space everywhere.
+// about 2^-110 below their thread's largest to log 0). PARPY_B200_FWD_DEFAULT=log restores log space everywhere.
 bool default_is_scaled() {
     if (const char *env = getenv("PARPY_B200_FWD_DEFAULT")) return strcmp(env, "log") != 0;
     return true;
