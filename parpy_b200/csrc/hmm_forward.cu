@@ -2272,6 +2272,7 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_tmem(const FwdPara
             // load in flight), so they travel while pair p is computed; a load never covers columns
             // that a store issued before its wait writes.
             constexpr int NP = (kLayers - RL) / 2;
+            float mt = 0.0f;   // largest new mantissa among the tensor-memory layers (Q == 3 only)
             float4 o0, pr[2][2];
             tmem_ld4(tm, o0);                       // old layer RL, for the last register layer
             if (NP > 1) tmem_ld8(tm + 4, pr[0][0], pr[0][1]);
@@ -2322,6 +2323,10 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_tmem(const FwdPara
                     b[0] = make_float4(r0.x, r0.y, r1.x, r1.y);
                 }
                 tmem_st8(tm + 4 * (2 * pp), b[0], b[1]);
+                if constexpr (Q == 3u) {   // the step that takes the exact maximum: the upper layers on their way out
+                    mt = max3(mt, fmaxf(b[0].x, b[0].y), fmaxf(b[0].z, b[0].w));
+                    mt = max3(mt, fmaxf(b[1].x, b[1].y), fmaxf(b[1].z, b[1].w));
+                }
             }
             W = Wn;
             tmem_wait_st();   // the next step reads what this one stored
@@ -2333,19 +2338,21 @@ __global__ void __launch_bounds__(1024, 1) hmm_forward_scaled_tmem(const FwdPara
             // 2^127 of headroom and the true maximum follows within three steps), and power-of-two
             // rescaling is exact: the values represented do not depend on which exponent was chosen.
             if (Q == 3u || t >= T_len - 2) {
-                float m = 0.0f;
+                float m = mt;
 #pragma unroll
                 for (int d = 0; d < RL; ++d) {
                     m = max3(m, x[d][0].x, x[d][0].y);
                     m = max3(m, x[d][1].x, x[d][1].y);
                 }
+                if constexpr (Q != 3u) {   // one of the last two steps: the upper layers are read back
 #pragma unroll
-                for (int d = 0; d < kLayers - RL; d += 2) {
-                    float4 u, v;
-                    tmem_ld8(tm + 4 * d, u, v);
-                    tmem_wait_ld(u, v);
-                    m = max3(m, fmaxf(u.x, u.y), fmaxf(u.z, u.w));
-                    m = max3(m, fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+                    for (int d = 0; d < kLayers - RL; d += 2) {
+                        float4 u, v;
+                        tmem_ld8(tm + 4 * d, u, v);
+                        tmem_wait_ld(u, v);
+                        m = max3(m, fmaxf(u.x, u.y), fmaxf(u.z, u.w));
+                        m = max3(m, fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+                    }
                 }
                 kt = exponent_of(m);
             }
